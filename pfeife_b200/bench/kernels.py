@@ -1,0 +1,135 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m pfeife_b200.bench.kernels [--which gemm,norm,adamw] [--json out.jsonl]
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed between timed
+launches by writing a 256 MiB buffer, median of `--iters`.  Fractions are against the measured
+peaks in MEASURED_PEAKS.json at the repository root when present ("of measured"), else against
+the fallback 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+class Timer:
+    def __init__(self, iters=10):
+        self.iters = iters
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.median(ts)
+
+
+def bench_gemm(timer, out):
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    shapes = [  # (name, M, N, K, a_mn, b_mn)
+        ("vitg_qkv_fwd", 6168, 4224, 1408, False, False),
+        ("vitg_fc1_fwd", 6168, 6144, 1408, False, False),
+        ("vitg_fc2_fwd", 6168, 1408, 6144, False, False),
+        ("vitg_fc1_dgrad", 6168, 1408, 6144, False, True),
+        ("vitg_fc1_wgrad", 6144, 1408, 6168, True, True),
+        ("llama_ffn_fwd", 2048, 11008, 4096, False, False),
+        ("square_8192", 8192, 8192, 8192, False, False),
+    ]
+    for name, M, N, K, a_mn, b_mn in shapes:
+        for dtype in (torch.bfloat16,):
+            a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(dtype)
+            b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(dtype)
+            c = torch.empty(M, N, device="cuda", dtype=dtype)
+            ms = timer(lambda: kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c))
+            A = a.t() if a_mn else a
+            Bt = b if b_mn else b.t()
+            ms_ref = timer(lambda: torch.matmul(A, Bt, out=c))
+            tfl = 2.0 * M * N * K / ms / 1e9
+            out({"kernel": "gemm_tcgen05", "case": name, "M": M, "N": N, "K": K, "ms": ms,
+                 "tflops": tfl, "frac_peak": tfl / tf, "peak_ref": tag,
+                 "torch_matmul_ms": ms_ref, "vs_torch": ms_ref / ms})
+
+
+def bench_norm(timer, out):
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    for rows, N in ((6168 * 8, 1408), (2048 * 16, 4096)):
+        x = torch.randn(rows, N, device="cuda").to(torch.bfloat16)
+        g = torch.ones(N, device="cuda")
+        b = torch.zeros(N, device="cuda")
+        ms = timer(lambda: kx.norm_fwd(x, g, b, 1e-5, False))
+        gb = 2 * x.numel() * 2 / 1e9
+        out({"kernel": "layernorm_fwd", "rows": rows, "N": N, "ms": ms, "gbs": gb / ms * 1e3,
+             "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
+        y, h, mean, rstd = kx.norm_fwd(x, g, b, 1e-5, False)
+        ms = timer(lambda: kx.norm_bwd(x, h, g, mean, rstd, False))
+        gb = 3 * x.numel() * 2 / 1e9
+        out({"kernel": "layernorm_bwd", "rows": rows, "N": N, "ms": ms, "gbs": gb / ms * 1e3,
+             "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
+
+
+def bench_adamw(timer, out):
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    n = 256 << 20
+    p, g, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = timer(lambda: kx.adamw(p, g, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8,
+                                weight_decay=0.01, step=1, lp=lp))
+    gb = n * (4 * 4 + 4 * 4 + 2) / 1e9
+    out({"kernel": "adamw_fused", "n": n, "ms": ms, "gbs": gb / ms * 1e3,
+         "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--which", default="gemm,norm,adamw")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args(argv)
+    sink = open(a.json, "w") if a.json else None
+
+    def out(rec):
+        line = json.dumps(rec)
+        print(line, flush=True)
+        if sink:
+            sink.write(line + "\n")
+
+    timer = Timer(a.iters)
+    table = {"gemm": bench_gemm, "norm": bench_norm, "adamw": bench_adamw}
+    for k in a.which.split(","):
+        table[k](timer, out)
+    from pfeife_b200.ops import kernels as kx
+    kx.check_status()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

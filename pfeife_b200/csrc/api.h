@@ -1,0 +1,77 @@
+// C ABI of the sm_100a kernel library (libpfeife_b200_kernels.so).  Every entry point takes raw
+// device pointers plus a CUDA stream handle (as void*), launches asynchronously on that stream
+// and returns 0, a positive cudaError_t, or a negative argument error:
+//   -1 unsupported dtype, -2 misaligned pointer / pitch, -3 size beyond a kernel limit,
+//   -100/-101 tensor-map encoding failed.
+// dtype codes: 0 = fp32, 1 = fp16, 2 = bf16.
+#pragma once
+#ifdef __cplusplus
+#define PF_DECL extern "C"
+#else
+#define PF_DECL
+#endif
+
+// ---- gemm_sm100.cu : C[M,N] = epi(alpha * A . B^T), tcgen05 / TMEM / TMA
+PF_DECL int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int a_mn, int b_mn, int in_dtype, int out_dtype,
+                    const void* bias, int bias_dtype, const void* residual, long long ldr,
+                    void* aux, long long ldaux, int epilogue, int accumulate, float alpha,
+                    int* status, int sm_count, int tile_n, void* stream);
+
+// ---- elementwise.cu
+PF_DECL int pf_elementwise(const void* a, const void* b, void* out, long long n, int op, int dtype,
+                           int sm_count, void* stream);
+PF_DECL int pf_glu_fwd(const void* gu, void* out, long long rows, int H, int gelu, int dtype,
+                       int sm_count, void* stream);
+PF_DECL int pf_glu_bwd(const void* gu, const void* dout, void* dgu, long long rows, int H,
+                       int gelu, int dtype, int sm_count, void* stream);
+PF_DECL int pf_axpy_f32(void* dst, const void* src, long long n, float scale, int accumulate,
+                        int src_dtype, int sm_count, void* stream);
+PF_DECL int pf_cast(const void* src, void* dst, long long n, int src_dtype, int dst_dtype,
+                    int sm_count, void* stream);
+PF_DECL int pf_colsum(const void* x, void* out_f32, long long rows, int cols, long long ld,
+                      int dtype, int sm_count, void* stream);
+PF_DECL int pf_transpose16(const void* src, void* dst, int rows, int cols, long long ld_src,
+                           long long ld_dst, void* stream);
+
+// ---- norm.cu
+PF_DECL int pf_norm_fwd(const void* x, const void* res, const void* gamma, const void* beta,
+                        void* y, void* h_out, void* mean, void* rstd, long long rows, int N,
+                        float eps, int rms, int dtype, void* stream);
+PF_DECL int pf_norm_bwd_ctas(long long rows, int sm_count);
+PF_DECL int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const void* mean,
+                        const void* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                        void* scratch, long long rows, int N, int rms, int accumulate, int dtype,
+                        int sm_count, void* stream);
+
+// ---- optim.cu
+PF_DECL int pf_nonfinite(const void* g, long long n, void* found_inf, int sm_count, void* stream);
+PF_DECL int pf_adamw(void* p, void* g, void* m, void* v, void* lp, long long n,
+                     const void* found_inf, const void* loss_scale, float lr, float beta1,
+                     float beta2, float eps, float weight_decay, int step, float grad_scale,
+                     int adamw, int zero_grad, int lp_dtype, int sm_count, void* stream);
+PF_DECL int pf_sgd(void* p, void* g, void* mom, void* lp, long long n, const void* found_inf,
+                   const void* loss_scale, float lr, float momentum, float dampening,
+                   float weight_decay, int nesterov, int first_step, float grad_scale,
+                   int zero_grad, int lp_dtype, int sm_count, void* stream);
+PF_DECL int pf_loss_scale_update(void* state, void* found_inf, float growth, float backoff,
+                                 int interval, void* stream);
+
+// ---- loss_embed.cu
+PF_DECL int pf_ce_fwd(const void* logits, const void* target, void* loss, void* lse,
+                      long long rows, int V, long long ld, long long ignore_index, int dtype,
+                      void* stream);
+PF_DECL int pf_ce_bwd(const void* logits, const void* target, const void* lse, const void* gscale,
+                      void* dlogits, long long rows, int V, long long ld, long long ignore_index,
+                      int dtype, void* stream);
+PF_DECL int pf_mse_fwd(const void* a, const void* b, void* out_f32, long long n, int dtype,
+                       int sm_count, void* stream);
+PF_DECL int pf_mse_bwd(const void* a, const void* b, const void* gout_f32, void* da, long long n,
+                       int dtype, int sm_count, void* stream);
+PF_DECL int pf_embed_fwd(const void* table, const void* ids, void* out, long long tokens, int D,
+                         long long vocab, int table_dtype, int out_dtype, void* stream);
+PF_DECL int pf_embed_bwd(const void* dout, const void* ids, void* dtable_f32, long long tokens,
+                         int D, long long vocab, int dtype, void* stream);
+PF_DECL int pf_rope(const void* x, void* out, const void* cos_t, const void* sin_t, long long B,
+                    int S, int H, int D, long long stride_b, long long stride_s,
+                    long long stride_h, int inverse, int dtype, int sm_count, void* stream);

@@ -1,0 +1,307 @@
+// LayerNorm and RMSNorm, forward and backward, one CTA per row with the row held in registers
+// (16-byte loads, two block reductions).  The forward can fuse the residual add of a
+// pre-norm transformer block:  h = x + res ;  y = norm(h) * gamma (+ beta).
+// The backward writes dx (optionally + the gradient that flows around the norm through the
+// residual branch) and per-CTA partial sums of dgamma / dbeta into a scratch buffer that a
+// second small kernel folds into the fp32 parameter gradients.
+#include "common.cuh"
+#include "api.h"
+
+namespace pf {
+
+constexpr int NORM_MAX_VEC = 4;   // 16-byte vectors per thread: N <= 256 * 4 * 8 = 8192 (16-bit)
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < THREADS / 32) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// rms != 0 -> RMSNorm (no mean subtraction, no beta)
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ gamma,
+                const float* __restrict__ beta, T* __restrict__ y, T* __restrict__ h_out,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int N, float eps,
+                int rms) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int nvec = N / V;
+  const T* xr = x + row * N;
+  float vals[NORM_MAX_VEC][V];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    if (idx < nvec) {
+      uint4 q = reinterpret_cast<const uint4*>(xr)[idx];
+      const T* e = reinterpret_cast<const T*>(&q);
+      if (res) {
+        uint4 qr = reinterpret_cast<const uint4*>(res + row * N)[idx];
+        const T* er = reinterpret_cast<const T*>(&qr);
+        uint4 qh;
+        T* eh = reinterpret_cast<T*>(&qh);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          // round the residual stream to its storage type first so fwd and bwd agree
+          eh[j] = from_f32<T>(to_f32<T>(e[j]) + to_f32<T>(er[j]));
+          vals[i][j] = to_f32<T>(eh[j]);
+        }
+        if (h_out) reinterpret_cast<uint4*>(h_out + row * N)[idx] = qh;
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) vals[i][j] = to_f32<T>(e[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += vals[i][j];
+    }
+  }
+  float mean = 0.f;
+  if (!rms) mean = block_sum<THREADS>(s, red) / N;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    if (idx < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float d = vals[i][j] - mean;
+        sq += d * d;
+      }
+    }
+  }
+  const float var = block_sum<THREADS>(sq, red) / N;
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    if (idx < nvec) {
+      uint4 q;
+      T* e = reinterpret_cast<T*>(&q);
+      const float4* g4 = reinterpret_cast<const float4*>(gamma + idx * V);
+      float g[V], b[V];
+#pragma unroll
+      for (int j = 0; j < V / 4; ++j) {
+        float4 t = __ldg(g4 + j);
+        g[4 * j] = t.x; g[4 * j + 1] = t.y; g[4 * j + 2] = t.z; g[4 * j + 3] = t.w;
+      }
+      if (beta) {
+        const float4* b4 = reinterpret_cast<const float4*>(beta + idx * V);
+#pragma unroll
+        for (int j = 0; j < V / 4; ++j) {
+          float4 t = __ldg(b4 + j);
+          b[4 * j] = t.x; b[4 * j + 1] = t.y; b[4 * j + 2] = t.z; b[4 * j + 3] = t.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float o = (vals[i][j] - mean) * rstd * g[j];
+        if (beta) o += b[j];
+        e[j] = from_f32<T>(o);
+      }
+      reinterpret_cast<uint4*>(y + row * N)[idx] = q;
+    }
+  }
+}
+
+// Backward.  Grid = G persistent CTAs striding over rows; each thread keeps dgamma/dbeta
+// partials for its own columns and writes them to scratch[blockIdx][2][N] at the end.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* __restrict__ gamma,
+                const float* __restrict__ mean, const float* __restrict__ rstd,
+                const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ scratch,
+                long long rows, int N, int rms) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float red[32];
+  const int nvec = N / V;
+  float dg[NORM_MAX_VEC][V], db[NORM_MAX_VEC][V], g[NORM_MAX_VEC][V];
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      dg[i][j] = 0.f; db[i][j] = 0.f;
+      g[i][j] = (idx < nvec) ? gamma[idx * V + j] : 0.f;
+    }
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mu = rms ? 0.f : mean[row];
+    const float rs = rstd[row];
+    float xh[NORM_MAX_VEC][V], dyv[NORM_MAX_VEC][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int idx = threadIdx.x + i * THREADS;
+      if (idx < nvec) {
+        uint4 qd = reinterpret_cast<const uint4*>(dy + row * N)[idx];
+        uint4 qh = reinterpret_cast<const uint4*>(h + row * N)[idx];
+        const T* ed = reinterpret_cast<const T*>(&qd);
+        const T* eh = reinterpret_cast<const T*>(&qh);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float d = to_f32<T>(ed[j]);
+          const float xhat = (to_f32<T>(eh[j]) - mu) * rs;
+          xh[i][j] = xhat;
+          dyv[i][j] = d * g[i][j];
+          dg[i][j] += d * xhat;
+          db[i][j] += d;
+          s1 += dyv[i][j];
+          s2 += dyv[i][j] * xhat;
+        }
+      }
+    }
+    float m1 = 0.f;
+    if (!rms) m1 = block_sum<THREADS>(s1, red) / N;
+    const float m2 = block_sum<THREADS>(s2, red) / N;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int idx = threadIdx.x + i * THREADS;
+      if (idx < nvec) {
+        uint4 q;
+        T* e = reinterpret_cast<T*>(&q);
+        uint4 qr;
+        const T* er = reinterpret_cast<const T*>(&qr);
+        if (dres) qr = reinterpret_cast<const uint4*>(dres + row * N)[idx];
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float o = rs * (dyv[i][j] - m1 - xh[i][j] * m2);
+          if (dres) o += to_f32<T>(er[j]);
+          e[j] = from_f32<T>(o);
+        }
+        reinterpret_cast<uint4*>(dx + row * N)[idx] = q;
+      }
+    }
+  }
+  float* sg = scratch + (long long)blockIdx.x * 2 * N;
+  float* sb = sg + N;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    if (idx < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        sg[idx * V + j] = dg[i][j];
+        sb[idx * V + j] = db[i][j];
+      }
+    }
+  }
+}
+
+// dgamma[c] (+)= sum_g scratch[g][0][c] ; dbeta likewise
+__global__ void __launch_bounds__(256)
+norm_bwd_finish_kernel(const float* __restrict__ scratch, float* __restrict__ dgamma,
+                       float* __restrict__ dbeta, int G, int N, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float a = 0.f, b = 0.f;
+  for (int g = 0; g < G; ++g) {
+    a += scratch[(long long)g * 2 * N + c];
+    b += scratch[(long long)g * 2 * N + N + c];
+  }
+  dgamma[c] = accumulate ? dgamma[c] + a : a;
+  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+}
+
+template <typename T>
+static int norm_fwd_launch(const void* x, const void* res, const float* gamma, const float* beta,
+                           void* y, void* h_out, float* mean, float* rstd, long long rows, int N,
+                           float eps, int rms, cudaStream_t st) {
+  constexpr int V = 16 / sizeof(T);
+  if (N % V) return -2;
+  const int nvec = N / V;
+  if (nvec <= 128 * NORM_MAX_VEC)
+    norm_fwd_kernel<T, 128><<<(unsigned)rows, 128, 0, st>>>((const T*)x, (const T*)res, gamma,
+        beta, (T*)y, (T*)h_out, mean, rstd, N, eps, rms);
+  else if (nvec <= 256 * NORM_MAX_VEC)
+    norm_fwd_kernel<T, 256><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (const T*)res, gamma,
+        beta, (T*)y, (T*)h_out, mean, rstd, N, eps, rms);
+  else if (nvec <= 1024 * NORM_MAX_VEC)
+    norm_fwd_kernel<T, 1024><<<(unsigned)rows, 1024, 0, st>>>((const T*)x, (const T*)res, gamma,
+        beta, (T*)y, (T*)h_out, mean, rstd, N, eps, rms);
+  else
+    return -3;
+  return 0;
+}
+
+template <typename T>
+static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, const float* mean,
+                           const float* rstd, const void* dres, void* dx, float* scratch, int G,
+                           long long rows, int N, int rms, cudaStream_t st) {
+  constexpr int V = 16 / sizeof(T);
+  if (N % V) return -2;
+  const int nvec = N / V;
+  if (nvec <= 128 * NORM_MAX_VEC)
+    norm_bwd_kernel<T, 128><<<G, 128, 0, st>>>((const T*)dy, (const T*)h, gamma, mean, rstd,
+        (const T*)dres, (T*)dx, scratch, rows, N, rms);
+  else if (nvec <= 256 * NORM_MAX_VEC)
+    norm_bwd_kernel<T, 256><<<G, 256, 0, st>>>((const T*)dy, (const T*)h, gamma, mean, rstd,
+        (const T*)dres, (T*)dx, scratch, rows, N, rms);
+  else if (nvec <= 1024 * NORM_MAX_VEC)
+    norm_bwd_kernel<T, 1024><<<G, 1024, 0, st>>>((const T*)dy, (const T*)h, gamma, mean, rstd,
+        (const T*)dres, (T*)dx, scratch, rows, N, rms);
+  else
+    return -3;
+  return 0;
+}
+
+}  // namespace pf
+
+using namespace pf;
+
+PF_API int pf_norm_fwd(const void* x, const void* res, const void* gamma, const void* beta,
+                       void* y, void* h_out, void* mean, void* rstd, long long rows, int N,
+                       float eps, int rms, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int r = -1;
+  switch (dtype) {
+    case PF_F32: r = norm_fwd_launch<float>(x, res, (const float*)gamma, (const float*)beta, y, h_out, (float*)mean, (float*)rstd, rows, N, eps, rms, st); break;
+    case PF_F16: r = norm_fwd_launch<__half>(x, res, (const float*)gamma, (const float*)beta, y, h_out, (float*)mean, (float*)rstd, rows, N, eps, rms, st); break;
+    case PF_BF16: r = norm_fwd_launch<__nv_bfloat16>(x, res, (const float*)gamma, (const float*)beta, y, h_out, (float*)mean, (float*)rstd, rows, N, eps, rms, st); break;
+  }
+  if (r) return r;
+  PF_CHECK_LAUNCH();
+  return 0;
+}
+
+// Number of CTAs (= rows of the scratch buffer) the backward uses for `rows` rows.
+PF_API int pf_norm_bwd_ctas(long long rows, int sm_count) {
+  long long g = (long long)(sm_count > 0 ? sm_count : 148) * 2;
+  if (g > rows) g = rows;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+// scratch: fp32 [pf_norm_bwd_ctas(rows)][2][N], contents on entry irrelevant.
+PF_API int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const void* mean,
+                       const void* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                       void* scratch, long long rows, int N, int rms, int accumulate, int dtype,
+                       int sm_count, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int G = pf_norm_bwd_ctas(rows, sm_count);
+  int r = -1;
+  switch (dtype) {
+    case PF_F32: r = norm_bwd_launch<float>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
+    case PF_F16: r = norm_bwd_launch<__half>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
+    case PF_BF16: r = norm_bwd_launch<__nv_bfloat16>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
+  }
+  if (r) return r;
+  PF_CHECK_LAUNCH();
+  norm_bwd_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>((const float*)scratch, (float*)dgamma,
+                                                          (float*)dbeta, G, N, accumulate);
+  PF_CHECK_LAUNCH();
+  return 0;
+}

@@ -1,0 +1,329 @@
+"""Thin tensor-level wrappers over the C ABI of the kernel library (no autograd here).
+
+Each function validates shapes, allocates outputs with torch (so memory comes from the caching
+allocator of the current stream) and launches on the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import c_f, c_ll, check, dt, ptr, sm_count, stream
+
+# GEMM epilogue codes (gemm_sm100.cu)
+EPI_NONE, EPI_GELU, EPI_DGELU, EPI_GELU_TANH, EPI_DGELU_TANH, EPI_SILU = 0, 1, 2, 3, 4, 5
+# elementwise op codes (elementwise.cu)
+EW_GELU, EW_GELU_TANH, EW_SILU, EW_COPY = 0, 1, 2, 3
+EW_DGELU, EW_DGELU_TANH, EW_DSILU = 10, 11, 12
+EW_ADD, EW_MUL, EW_SILU_MUL, EW_GELU_MUL = 20, 21, 30, 31
+
+_status = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """int32[1] per device; kernels record the first bounded-wait failure here (0 = ok)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _status[idx]
+
+
+def check_status(device=None) -> None:
+    """Synchronising read of the status word; raises if any kernel gave up on a wait."""
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        raise _lib.KernelError(f"a kernel reported status {code} (bounded wait ran out)")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         aux: Optional[torch.Tensor] = None, epilogue: int = EPI_NONE, accumulate: bool = False,
+         alpha: float = 1.0, tile_n: int = 0) -> torch.Tensor:
+    """out[M,N] = epi(alpha * A . B^T).
+
+    a: [M,K] (K-major) or [K,M] when ``a_mn``; b: [N,K] (K-major) or [K,N] when ``b_mn``.
+    Inputs are fp16 or bf16 2-D tensors with unit inner stride and 16-byte aligned pitch.
+    """
+    L = _lib.lib()
+    assert a.dim() == 2 and b.dim() == 2 and a.dtype == b.dtype
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"reduction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    if residual is not None:
+        assert residual.shape == (M, N) and residual.dtype == out.dtype and residual.stride(1) == 1
+    if aux is not None:
+        assert aux.shape == (M, N) and aux.dtype == out.dtype and aux.stride(1) == 1
+    code = L.pf_gemm(ptr(a), ptr(b), ptr(out), M, N, K, c_ll(a.stride(0)), c_ll(b.stride(0)),
+                     c_ll(out.stride(0)), int(a_mn), int(b_mn), dt(a.dtype), dt(out.dtype),
+                     ptr(bias), dt(bias.dtype) if bias is not None else 0, ptr(residual),
+                     c_ll(residual.stride(0) if residual is not None else 0), ptr(aux),
+                     c_ll(aux.stride(0) if aux is not None else 0), epilogue, int(accumulate),
+                     c_f(alpha), ptr(status_word(a.device)), sm_count(a.device), tile_n, stream())
+    check(code, "pf_gemm")
+    return out
+
+
+def elementwise(op: int, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    L = _lib.lib()
+    a = a.contiguous()
+    if b is not None:
+        b = b.contiguous()
+        assert b.shape == a.shape and b.dtype == a.dtype
+    if out is None:
+        out = torch.empty_like(a)
+    check(L.pf_elementwise(ptr(a), ptr(b), ptr(out), c_ll(a.numel()), op, dt(a.dtype),
+                           sm_count(a.device), stream()), "pf_elementwise")
+    return out
+
+
+def glu_fwd(gu: torch.Tensor, gelu: bool) -> torch.Tensor:
+    L = _lib.lib()
+    gu = gu.contiguous()
+    H = gu.shape[-1] // 2
+    out = torch.empty(gu.shape[:-1] + (H,), dtype=gu.dtype, device=gu.device)
+    rows = gu.numel() // (2 * H)
+    check(L.pf_glu_fwd(ptr(gu), ptr(out), c_ll(rows), H, int(gelu), dt(gu.dtype),
+                       sm_count(gu.device), stream()), "pf_glu_fwd")
+    return out
+
+
+def glu_bwd(gu: torch.Tensor, dout: torch.Tensor, gelu: bool) -> torch.Tensor:
+    L = _lib.lib()
+    gu = gu.contiguous()
+    dout = dout.contiguous()
+    H = gu.shape[-1] // 2
+    dgu = torch.empty_like(gu)
+    rows = gu.numel() // (2 * H)
+    check(L.pf_glu_bwd(ptr(gu), ptr(dout), ptr(dgu), c_ll(rows), H, int(gelu), dt(gu.dtype),
+                       sm_count(gu.device), stream()), "pf_glu_bwd")
+    return dgu
+
+
+def axpy_f32(dst: torch.Tensor, src: torch.Tensor, scale: float = 1.0,
+             accumulate: bool = True) -> torch.Tensor:
+    L = _lib.lib()
+    assert dst.dtype == torch.float32 and dst.is_contiguous() and dst.numel() == src.numel()
+    src = src.contiguous()
+    check(L.pf_axpy_f32(ptr(dst), ptr(src), c_ll(src.numel()), c_f(scale), int(accumulate),
+                        dt(src.dtype), sm_count(src.device), stream()), "pf_axpy_f32")
+    return dst
+
+
+def cast(src: torch.Tensor, dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    L = _lib.lib()
+    src = src.contiguous()
+    if out is None:
+        out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    check(L.pf_cast(ptr(src), ptr(out), c_ll(src.numel()), dt(src.dtype), dt(dtype),
+                    sm_count(src.device), stream()), "pf_cast")
+    return out
+
+
+def colsum(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[c] += sum over rows of x[r, c]; ``out`` fp32, zero-filled when not given."""
+    L = _lib.lib()
+    assert x.dim() == 2 and x.stride(1) == 1
+    if out is None:
+        out = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+    check(L.pf_colsum(ptr(x), ptr(out), c_ll(x.shape[0]), x.shape[1], c_ll(x.stride(0)),
+                      dt(x.dtype), sm_count(x.device), stream()), "pf_colsum")
+    return out
+
+
+def transpose16(x: torch.Tensor) -> torch.Tensor:
+    L = _lib.lib()
+    assert x.dim() == 2 and x.element_size() == 2 and x.stride(1) == 1
+    out = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)
+    check(L.pf_transpose16(ptr(x), ptr(out), x.shape[0], x.shape[1], c_ll(x.stride(0)),
+                           c_ll(out.stride(0)), stream()), "pf_transpose16")
+    return out
+
+
+def norm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float,
+             rms: bool, residual: Optional[torch.Tensor] = None
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (y, h, mean, rstd); h = x + residual (h is x itself when residual is None)."""
+    L = _lib.lib()
+    N = x.shape[-1]
+    x2 = x.contiguous().view(-1, N)
+    rows = x2.shape[0]
+    y = torch.empty_like(x2)
+    res2 = residual.contiguous().view(-1, N) if residual is not None else None
+    h = torch.empty_like(x2) if residual is not None else x2
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    g = gamma if gamma.dtype == torch.float32 else gamma.float()
+    b = None if beta is None else (beta if beta.dtype == torch.float32 else beta.float())
+    check(L.pf_norm_fwd(ptr(x2), ptr(res2), ptr(g), ptr(b), ptr(y),
+                        ptr(h) if residual is not None else ptr(None), ptr(mean), ptr(rstd),
+                        c_ll(rows), N, c_f(eps), int(rms), dt(x.dtype), stream()), "pf_norm_fwd")
+    return y.view(x.shape), h.view(x.shape), mean, rstd
+
+
+def norm_bwd_scratch_shape(rows: int, N: int, device=None) -> Tuple[int, int, int]:
+    L = _lib.lib()
+    return (L.pf_norm_bwd_ctas(c_ll(rows), sm_count(device)), 2, N)
+
+
+def norm_bwd(dy: torch.Tensor, h: torch.Tensor, gamma: torch.Tensor, mean: torch.Tensor,
+             rstd: torch.Tensor, rms: bool, dres: Optional[torch.Tensor] = None,
+             dgamma: Optional[torch.Tensor] = None, dbeta: Optional[torch.Tensor] = None,
+             accumulate: bool = False, want_dbeta: bool = True
+             ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    L = _lib.lib()
+    N = h.shape[-1]
+    dy2 = dy.contiguous().view(-1, N)
+    h2 = h.contiguous().view(-1, N)
+    rows = h2.shape[0]
+    dres2 = dres.contiguous().view(-1, N) if dres is not None else None
+    dx = torch.empty_like(h2)
+    g = gamma if gamma.dtype == torch.float32 else gamma.float()
+    if dgamma is None:
+        dgamma = torch.empty(N, dtype=torch.float32, device=h.device)
+        accumulate = False
+    if dbeta is None and want_dbeta and not rms:
+        dbeta = torch.empty(N, dtype=torch.float32, device=h.device)
+    scratch = torch.empty(norm_bwd_scratch_shape(rows, N, h.device), dtype=torch.float32,
+                          device=h.device)
+    check(L.pf_norm_bwd(ptr(dy2), ptr(h2), ptr(g), ptr(mean), ptr(rstd), ptr(dres2), ptr(dx),
+                        ptr(dgamma), ptr(dbeta), ptr(scratch), c_ll(rows), N, int(rms),
+                        int(accumulate), dt(h.dtype), sm_count(h.device), stream()), "pf_norm_bwd")
+    return dx.view(h.shape), dgamma, dbeta
+
+
+def nonfinite(g: torch.Tensor, found_inf: torch.Tensor) -> None:
+    L = _lib.lib()
+    assert g.dtype == torch.float32 and g.is_contiguous()
+    check(L.pf_nonfinite(ptr(g), c_ll(g.numel()), ptr(found_inf), sm_count(g.device), stream()),
+          "pf_nonfinite")
+
+
+def adamw(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *, lr: float,
+          beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
+          grad_scale: float = 1.0, decoupled: bool = True, zero_grad: bool = True,
+          lp: Optional[torch.Tensor] = None, found_inf: Optional[torch.Tensor] = None,
+          loss_scale: Optional[torch.Tensor] = None) -> None:
+    L = _lib.lib()
+    for t in (p, g, m, v):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == p.numel()
+    check(L.pf_adamw(ptr(p), ptr(g), ptr(m), ptr(v), ptr(lp), c_ll(p.numel()), ptr(found_inf),
+                     ptr(loss_scale), c_f(lr), c_f(beta1), c_f(beta2), c_f(eps),
+                     c_f(weight_decay), int(step), c_f(grad_scale), int(decoupled),
+                     int(zero_grad), dt(lp.dtype) if lp is not None else 0, sm_count(p.device),
+                     stream()), "pf_adamw")
+
+
+def sgd(p: torch.Tensor, g: torch.Tensor, mom: Optional[torch.Tensor], *, lr: float,
+        momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
+        nesterov: bool = False, first_step: bool = False, grad_scale: float = 1.0,
+        zero_grad: bool = True, lp: Optional[torch.Tensor] = None,
+        found_inf: Optional[torch.Tensor] = None,
+        loss_scale: Optional[torch.Tensor] = None) -> None:
+    L = _lib.lib()
+    check(L.pf_sgd(ptr(p), ptr(g), ptr(mom), ptr(lp), c_ll(p.numel()), ptr(found_inf),
+                   ptr(loss_scale), c_f(lr), c_f(momentum), c_f(dampening), c_f(weight_decay),
+                   int(nesterov), int(first_step), c_f(grad_scale), int(zero_grad),
+                   dt(lp.dtype) if lp is not None else 0, sm_count(p.device), stream()), "pf_sgd")
+
+
+def loss_scale_update(state: torch.Tensor, found_inf: torch.Tensor, growth: float = 2.0,
+                      backoff: float = 0.5, interval: int = 2000) -> None:
+    L = _lib.lib()
+    check(L.pf_loss_scale_update(ptr(state), ptr(found_inf), c_f(growth), c_f(backoff),
+                                 int(interval), stream()), "pf_loss_scale_update")
+
+
+def ce_fwd(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100
+           ) -> Tuple[torch.Tensor, torch.Tensor]:
+    L = _lib.lib()
+    assert logits.dim() == 2 and logits.stride(1) == 1 and target.dtype == torch.int64
+    rows, V = logits.shape
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    check(L.pf_ce_fwd(ptr(logits), ptr(target.contiguous()), ptr(loss), ptr(lse), c_ll(rows), V,
+                      c_ll(logits.stride(0)), c_ll(ignore_index), dt(logits.dtype), stream()),
+          "pf_ce_fwd")
+    return loss, lse
+
+
+def ce_bwd(logits: torch.Tensor, target: torch.Tensor, lse: torch.Tensor,
+           gscale: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    L = _lib.lib()
+    rows, V = logits.shape
+    d = torch.empty_like(logits)
+    check(L.pf_ce_bwd(ptr(logits), ptr(target.contiguous()), ptr(lse), ptr(gscale), ptr(d),
+                      c_ll(rows), V, c_ll(logits.stride(0)), c_ll(ignore_index),
+                      dt(logits.dtype), stream()), "pf_ce_bwd")
+    return d
+
+
+def mse_fwd(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    L = _lib.lib()
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty(1, dtype=torch.float32, device=a.device)
+    check(L.pf_mse_fwd(ptr(a), ptr(b), ptr(out), c_ll(a.numel()), dt(a.dtype),
+                       sm_count(a.device), stream()), "pf_mse_fwd")
+    return out
+
+
+def mse_bwd(a: torch.Tensor, b: torch.Tensor, gout: torch.Tensor) -> torch.Tensor:
+    L = _lib.lib()
+    a, b = a.contiguous(), b.contiguous()
+    da = torch.empty_like(a)
+    check(L.pf_mse_bwd(ptr(a), ptr(b), ptr(gout.float().contiguous()), ptr(da), c_ll(a.numel()),
+                       dt(a.dtype), sm_count(a.device), stream()), "pf_mse_bwd")
+    return da
+
+
+def embed_fwd(table: torch.Tensor, ids: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    L = _lib.lib()
+    ids_c = ids.contiguous()
+    D = table.shape[1]
+    out = torch.empty(ids.shape + (D,), dtype=out_dtype, device=table.device)
+    check(L.pf_embed_fwd(ptr(table), ptr(ids_c), ptr(out), c_ll(ids_c.numel()), D,
+                         c_ll(table.shape[0]), dt(table.dtype), dt(out_dtype), stream()),
+          "pf_embed_fwd")
+    return out
+
+
+def embed_bwd(dout: torch.Tensor, ids: torch.Tensor, dtable: torch.Tensor) -> torch.Tensor:
+    L = _lib.lib()
+    assert dtable.dtype == torch.float32 and dtable.is_contiguous()
+    dout = dout.contiguous()
+    ids_c = ids.contiguous()
+    check(L.pf_embed_bwd(ptr(dout), ptr(ids_c), ptr(dtable), c_ll(ids_c.numel()),
+                         dtable.shape[1], c_ll(dtable.shape[0]), dt(dout.dtype), stream()),
+          "pf_embed_bwd")
+    return dtable
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool = False
+         ) -> torch.Tensor:
+    """x: [B, S, H, D] with unit stride on D; cos/sin: fp32 [S, D/2]."""
+    L = _lib.lib()
+    assert x.dim() == 4 and x.stride(3) == 1
+    B, S, H, D = x.shape
+    out = torch.empty_like(x)
+    assert out.stride() == x.stride() or x.is_contiguous()
+    if out.stride() != x.stride():
+        x = x.contiguous()
+    check(L.pf_rope(ptr(x), ptr(out), ptr(cos.contiguous()), ptr(sin.contiguous()), c_ll(B), S, H,
+                    D, c_ll(x.stride(0)), c_ll(x.stride(1)), c_ll(x.stride(2)), int(inverse),
+                    dt(x.dtype), sm_count(x.device), stream()), "pf_rope")
+    return out
