@@ -1,0 +1,705 @@
+"""Differentiable ops backed by the sm_100a kernels.
+
+Every op is a ``torch.library`` custom op (opaque to dynamo, so captured stage graphs carry it
+as one node) with
+  * a CUDA implementation that calls the native kernels (no eager fallback on GPU for 16-bit
+    tensors; fp32 tensors on CUDA, which no benchmark configuration uses, take the ATen path),
+  * a CPU implementation in plain PyTorch, which is the numerical oracle of the tests and what
+    the CPU/gloo pipeline tests execute,
+  * a shape-only fake implementation, and
+  * an autograd formula whose backward is again a custom op.
+
+Mixed precision: parameters stay fp32 ("master"); ``register_param`` attaches a 16-bit shadow
+and an fp32 gradient-bucket view to a master tensor.  ``linear`` then reads the shadow, and its
+wgrad GEMM accumulates straight into the bucket from the epilogue (returning no autograd
+gradient for the weight), which is what the fused data-parallel reduce consumes.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from . import _lib
+from . import kernels as kx
+
+ACT_NONE, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3
+_ACT_NAMES = {None: 0, "none": 0, "gelu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "silu": 3}
+
+
+# --------------------------------------------------------------------------- parameter registry
+@dataclass
+class ParamSlot:
+    lp: Optional[Tensor] = None          # 16-bit shadow of the master weight
+    main_grad: Optional[Tensor] = None   # fp32 view into the flat gradient bucket
+
+
+_PARAMS: Dict[int, ParamSlot] = {}
+
+
+def register_param(master: Tensor, lp: Optional[Tensor] = None,
+                   main_grad: Optional[Tensor] = None) -> None:
+    _PARAMS[master.data_ptr()] = ParamSlot(lp, main_grad)
+    if lp is not None:
+        _PARAMS[lp.data_ptr()] = ParamSlot(lp, main_grad)
+
+
+def unregister_params() -> None:
+    _PARAMS.clear()
+
+
+def _slot(t: Tensor) -> Optional[ParamSlot]:
+    return _PARAMS.get(t.data_ptr())
+
+
+def compute_dtype(x: Tensor) -> torch.dtype:
+    """dtype GEMM-like ops run in: the autocast dtype when autocast is on, else x's dtype."""
+    dev = "cuda" if x.is_cuda else "cpu"
+    if torch.is_autocast_enabled(dev):
+        return torch.get_autocast_dtype(dev)
+    return x.dtype
+
+
+def _weight_as(w: Tensor, dtype: torch.dtype) -> Tensor:
+    """`w` in `dtype`: itself, its registered 16-bit shadow, or a cast copy."""
+    if w.dtype == dtype:
+        return w
+    s = _slot(w)
+    if s is not None and s.lp is not None and s.lp.dtype == dtype:
+        return s.lp
+    return kx.cast(w, dtype) if w.is_cuda else w.to(dtype)
+
+
+def _native(x: Tensor) -> bool:
+    return x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+
+
+def _act_ref(z: Tensor, act: int) -> Tensor:
+    if act == ACT_GELU:
+        return F.gelu(z)
+    if act == ACT_GELU_TANH:
+        return F.gelu(z, approximate="tanh")
+    if act == ACT_SILU:
+        return F.silu(z)
+    return z
+
+
+def _dact_ref(z: Tensor, act: int) -> Tensor:
+    """Closed-form activation derivative in fp32 (autograd is unavailable inside an op)."""
+    x = z.detach().float()
+    if act == ACT_GELU:
+        cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
+        pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
+        return cdf + x * pdf
+    if act == ACT_GELU_TANH:
+        u = 0.7978845608028654 * (x + 0.044715 * x ** 3)
+        t = torch.tanh(u)
+        du = 0.7978845608028654 * (1.0 + 3 * 0.044715 * x * x)
+        return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * du
+    if act == ACT_SILU:
+        sg = torch.sigmoid(x)
+        return sg * (1.0 + x * (1.0 - sg))
+    return torch.ones_like(x)
+
+
+def _pad_k(t: Tensor, mult: int = 8) -> Tensor:
+    k = t.shape[-1]
+    pad = (-k) % mult
+    return F.pad(t, (0, pad)) if pad else t
+
+
+def _rows(x: Tensor) -> Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    return x2
+
+
+# =========================================================================== linear
+@torch.library.custom_op("pfeife::linear_fwd", mutates_args=())
+def linear_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], residual: Optional[Tensor],
+               act: int) -> Tuple[Tensor, Tensor]:
+    cd = compute_dtype(x)
+    N = w.shape[0]
+    out_shape = x.shape[:-1] + (N,)
+    if x.is_cuda and cd in (torch.float16, torch.bfloat16):
+        x2 = _rows(x if x.dtype == cd else kx.cast(x, cd))
+        w2 = _weight_as(w, cd)
+        if x2.shape[1] % 8:
+            x2, w2 = _pad_k(x2), _pad_k(w2)
+        r2 = None
+        if residual is not None:
+            r2 = _rows(residual if residual.dtype == cd else kx.cast(residual, cd))
+        M = x2.shape[0]
+        y = torch.empty((M, N), dtype=cd, device=x.device)
+        aux = torch.empty((M, N), dtype=cd, device=x.device) if act else None
+        epi = {ACT_NONE: kx.EPI_NONE, ACT_GELU: kx.EPI_GELU, ACT_GELU_TANH: kx.EPI_GELU_TANH,
+               ACT_SILU: kx.EPI_SILU}[act]
+        kx.gemm(x2, w2, out=y, bias=bias, residual=r2, aux=aux, epilogue=epi)
+        return y.view(out_shape), (aux.view(out_shape) if act else x.new_empty(0))
+    # reference path (CPU, or fp32 on CUDA)
+    xw = x.to(cd)
+    z = F.linear(xw, w.to(cd), None if bias is None else bias.to(cd))
+    y = _act_ref(z, act)
+    if residual is not None:
+        y = y + residual.to(cd)
+    return y, (z if act else x.new_empty(0))
+
+
+@linear_fwd.register_fake
+def _(x, w, bias, residual, act):
+    cd = compute_dtype(x)
+    y = x.new_empty(x.shape[:-1] + (w.shape[0],), dtype=cd)
+    return y, (torch.empty_like(y) if act else x.new_empty(0))
+
+
+@torch.library.custom_op("pfeife::linear_bwd", mutates_args=())
+def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx: bool,
+               need_dw: bool, need_db: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """-> (dx, dw, db); an output that is not needed, or that was accumulated directly into a
+    registered gradient bucket, comes back as an empty tensor."""
+    cd = dy.dtype
+    N, K = w.shape
+    empty = dy.new_empty(0)
+    slot = _slot(w)
+    if dy.is_cuda and cd in (torch.float16, torch.bfloat16):
+        dy2 = _rows(dy)
+        if act:
+            kop = {ACT_GELU: kx.EW_DGELU, ACT_GELU_TANH: kx.EW_DGELU_TANH, ACT_SILU: kx.EW_DSILU}[act]
+            dy2 = kx.elementwise(kop, dy2, _rows(aux))
+        dx = dw = db = empty
+        if need_dx:
+            w2 = _weight_as(w, cd)
+            if N % 8 == 0 and K % 8 == 0:
+                dx = kx.gemm(dy2, w2, b_mn=True).view(x.shape[:-1] + (K,))
+            else:
+                dx = (dy2 @ w2).view(x.shape[:-1] + (K,))
+        if need_dw:
+            x2 = _rows(x if x.dtype == cd else kx.cast(x, cd))
+            ok = N % 8 == 0 and K % 8 == 0
+            if slot is not None and slot.main_grad is not None and ok:
+                kx.gemm(dy2, x2, a_mn=True, b_mn=True, out=slot.main_grad.view(N, K),
+                        accumulate=True)
+            elif ok:
+                dw = kx.gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
+            else:
+                dw = dy2.float().t() @ x2.float()
+            if dw.numel() and w.dtype != torch.float32:
+                dw = dw.to(w.dtype)
+        if need_db:
+            db = kx.colsum(dy2)
+        return dx, dw, db
+    dz = dy if not act else (dy.float() * _dact_ref(aux, act)).to(cd)
+    dz2 = dz.reshape(-1, N)
+    dx = (dz2 @ w.to(cd)).view(x.shape[:-1] + (K,)) if need_dx else empty
+    dw = (dz2.float().t() @ x.reshape(-1, K).float()).to(w.dtype) if need_dw else empty
+    db = dz2.float().sum(0) if need_db else empty
+    return dx, dw, db
+
+
+@linear_bwd.register_fake
+def _(dy, x, w, aux, act, need_dx, need_dw, need_db):
+    e = dy.new_empty(0)
+    dx = dy.new_empty(x.shape[:-1] + (w.shape[1],)) if need_dx else e
+    slot_acc = False
+    dw = torch.empty_like(w) if need_dw and not slot_acc else e
+    db = dy.new_empty(w.shape[0], dtype=torch.float32) if need_db else e
+    return dx, dw, db
+
+
+def _linear_setup(ctx, inputs, output):
+    x, w, bias, residual, act = inputs
+    y, aux = output
+    ctx.save_for_backward(x, w, aux)
+    ctx.act = act
+    ctx.has_bias = bias is not None
+    ctx.bias_dtype = bias.dtype if bias is not None else None
+    ctx.has_res = residual is not None
+    ctx.res_dtype = residual.dtype if residual is not None else None
+    ctx.x_dtype = x.dtype
+
+
+def _linear_backward(ctx, dy, daux):
+    x, w, aux = ctx.saved_tensors
+    need = ctx.needs_input_grad
+    dy = dy.contiguous()
+    dx, dw, db = linear_bwd(dy, x, w, aux, ctx.act, need[0], need[1], ctx.has_bias and need[2])
+    gx = dx.to(ctx.x_dtype) if need[0] else None
+    gw = dw if (need[1] and dw.numel()) else None
+    gb = db.to(ctx.bias_dtype) if (ctx.has_bias and need[2]) else None
+    gr = dy.to(ctx.res_dtype) if (ctx.has_res and need[3]) else None
+    return gx, gw, gb, gr, None
+
+
+linear_fwd.register_autograd(_linear_backward, setup_context=_linear_setup)
+
+
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
+           activation: Optional[str] = None, residual: Optional[Tensor] = None) -> Tensor:
+    """act(x @ weight.T + bias) + residual, one GEMM launch with a fused epilogue."""
+    return linear_fwd(x, weight, bias, residual, _ACT_NAMES[activation])[0]
+
+
+# =========================================================================== fused MLP
+@torch.library.custom_op("pfeife::mlp_fwd", mutates_args=())
+def mlp_fwd(x: Tensor, w1: Tensor, b1: Optional[Tensor], w2: Tensor, b2: Optional[Tensor],
+            residual: Optional[Tensor], act: int) -> Tuple[Tensor, Tensor, Tensor]:
+    """y = act(x W1^T + b1) W2^T + b2 (+ residual); also returns z1 (pre-activation) and a1."""
+    a1, z1 = linear_fwd(x, w1, b1, None, act)
+    y, _ = linear_fwd(a1, w2, b2, residual, ACT_NONE)
+    return y, z1, a1
+
+
+@mlp_fwd.register_fake
+def _(x, w1, b1, w2, b2, residual, act):
+    cd = compute_dtype(x)
+    h = x.new_empty(x.shape[:-1] + (w1.shape[0],), dtype=cd)
+    return x.new_empty(x.shape[:-1] + (w2.shape[0],), dtype=cd), h, torch.empty_like(h)
+
+
+@torch.library.custom_op("pfeife::mlp_bwd", mutates_args=())
+def mlp_bwd(dy: Tensor, x: Tensor, w1: Tensor, w2: Tensor, z1: Tensor, a1: Tensor, act: int,
+            need_dx: bool, has_b1: bool, has_b2: bool
+            ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """-> (dx, dw1, db1, dw2, db2).  On the native path the dgrad GEMM of the second layer
+    applies act'(z1) in its epilogue, so dz1 is produced without an elementwise pass."""
+    cd = dy.dtype
+    empty = dy.new_empty(0)
+    H, K = w1.shape
+    N = w2.shape[0]
+    if dy.is_cuda and cd in (torch.float16, torch.bfloat16) and act in (ACT_GELU, ACT_GELU_TANH) \
+            and H % 8 == 0 and K % 8 == 0 and N % 8 == 0:
+        dy2, z2, a2 = _rows(dy), _rows(z1), _rows(a1)
+        w2c = _weight_as(w2, cd)
+        epi = kx.EPI_DGELU if act == ACT_GELU else kx.EPI_DGELU_TANH
+        dz1 = kx.gemm(dy2, w2c, b_mn=True, aux=z2, epilogue=epi)          # [M, H]
+        _, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, False, True, has_b2)
+        dx, dw1, db1 = linear_bwd(dz1.view(z1.shape), x, w1, empty, ACT_NONE, need_dx, True, has_b1)
+        return dx, dw1, db1, dw2, db2
+    da1, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, True, True, has_b2)
+    dx, dw1, db1 = linear_bwd(da1, x, w1, z1, act, need_dx, True, has_b1)
+    return dx, dw1, db1, dw2, db2
+
+
+@mlp_bwd.register_fake
+def _(dy, x, w1, w2, z1, a1, act, need_dx, has_b1, has_b2):
+    e = dy.new_empty(0)
+    f32 = torch.float32
+    return (torch.empty_like(x, dtype=dy.dtype) if need_dx else e, torch.empty_like(w1),
+            dy.new_empty(w1.shape[0], dtype=f32) if has_b1 else e, torch.empty_like(w2),
+            dy.new_empty(w2.shape[0], dtype=f32) if has_b2 else e)
+
+
+def _mlp_setup(ctx, inputs, output):
+    x, w1, b1, w2, b2, residual, act = inputs
+    y, z1, a1 = output
+    ctx.save_for_backward(x, w1, w2, z1, a1)
+    ctx.act = act
+    ctx.meta = (x.dtype, None if b1 is None else b1.dtype, None if b2 is None else b2.dtype,
+                None if residual is None else residual.dtype)
+
+
+def _mlp_backward(ctx, dy, dz1_unused, da1_unused):
+    x, w1, w2, z1, a1 = ctx.saved_tensors
+    xd, b1d, b2d, rd = ctx.meta
+    need = ctx.needs_input_grad
+    dy = dy.contiguous()
+    dx, dw1, db1, dw2, db2 = mlp_bwd(dy, x, w1, w2, z1, a1, ctx.act, need[0], b1d is not None,
+                                     b2d is not None)
+    return (dx.to(xd) if need[0] else None,
+            dw1 if dw1.numel() else None,
+            db1.to(b1d) if b1d is not None else None,
+            dw2 if dw2.numel() else None,
+            db2.to(b2d) if b2d is not None else None,
+            dy.to(rd) if (rd is not None and need[5]) else None,
+            None)
+
+
+mlp_fwd.register_autograd(_mlp_backward, setup_context=_mlp_setup)
+
+
+def mlp(x: Tensor, w1: Tensor, b1: Optional[Tensor], w2: Tensor, b2: Optional[Tensor],
+        activation: str = "gelu", residual: Optional[Tensor] = None) -> Tensor:
+    """Transformer feed-forward block: two GEMMs, activation fused into the first epilogue,
+    residual into the second, activation derivative into the dgrad epilogue."""
+    return mlp_fwd(x, w1, b1, w2, b2, residual, _ACT_NAMES[activation])[0]
+
+
+# =========================================================================== norms
+@torch.library.custom_op("pfeife::norm_fwd", mutates_args=())
+def norm_fwd(x: Tensor, gamma: Tensor, beta: Optional[Tensor], residual: Optional[Tensor],
+             eps: float, rms: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    """-> (y, h, mean, rstd) with h = x + residual (h aliases nothing: it is x's clone-free
+    stand-in only on the fake/CPU path, always a fresh tensor when residual is given)."""
+    N = x.shape[-1]
+    if _native(x) or (x.is_cuda and x.dtype == torch.float32 and N % 4 == 0):
+        y, h, mean, rstd = kx.norm_fwd(x, gamma, beta, eps, rms, residual)
+        if residual is None:
+            h = x.new_empty(0)
+        return y, h, mean, rstd
+    hf = x.float() if residual is None else (x.float() + residual.float()).to(x.dtype).float()
+    if rms:
+        mean = hf.new_zeros(hf.shape[:-1]).reshape(-1)
+        rstd = torch.rsqrt(hf.pow(2).mean(-1) + eps).reshape(-1)
+        y = hf * rstd.view(hf.shape[:-1] + (1,)) * gamma.float()
+    else:
+        mean = hf.mean(-1).reshape(-1)
+        var = hf.var(-1, unbiased=False).reshape(-1)
+        rstd = torch.rsqrt(var + eps)
+        y = (hf - mean.view(hf.shape[:-1] + (1,))) * rstd.view(hf.shape[:-1] + (1,)) * gamma.float()
+        if beta is not None:
+            y = y + beta.float()
+    h = hf.to(x.dtype) if residual is not None else x.new_empty(0)
+    return y.to(x.dtype), h, mean, rstd
+
+
+@norm_fwd.register_fake
+def _(x, gamma, beta, residual, eps, rms):
+    rows = x.numel() // x.shape[-1]
+    st = x.new_empty(rows, dtype=torch.float32)
+    return (torch.empty_like(x), torch.empty_like(x) if residual is not None else x.new_empty(0),
+            st, torch.empty_like(st))
+
+
+@torch.library.custom_op("pfeife::norm_bwd", mutates_args=())
+def norm_bwd(dy: Tensor, dh: Optional[Tensor], h: Tensor, gamma: Tensor, mean: Tensor,
+             rstd: Tensor, rms: bool, has_beta: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """-> (dx [= dh_total], dgamma fp32, dbeta fp32).  `dh` is the gradient arriving through
+    the residual-stream output, added in the same pass."""
+    N = h.shape[-1]
+    if _native(h) or (h.is_cuda and h.dtype == torch.float32 and N % 4 == 0):
+        dx, dg, db = kx.norm_bwd(dy, h, gamma, mean, rstd, rms, dres=dh, want_dbeta=has_beta)
+        return dx, dg, (db if (db is not None and has_beta) else dy.new_empty(0, dtype=torch.float32))
+    hf = h.float()
+    shp = hf.shape[:-1] + (1,)
+    xhat = (hf - (0 if rms else mean.view(shp))) * rstd.view(shp)
+    dyf = dy.float()
+    g = gamma.float()
+    dyg = dyf * g
+    m2 = (dyg * xhat).mean(-1, keepdim=True)
+    m1 = 0 if rms else dyg.mean(-1, keepdim=True)
+    dx = rstd.view(shp) * (dyg - m1 - xhat * m2)
+    if dh is not None:
+        dx = dx + dh.float()
+    dg = (dyf * xhat).reshape(-1, N).sum(0)
+    db = dyf.reshape(-1, N).sum(0) if has_beta else dy.new_empty(0, dtype=torch.float32)
+    return dx.to(h.dtype), dg, db
+
+
+@norm_bwd.register_fake
+def _(dy, dh, h, gamma, mean, rstd, rms, has_beta):
+    N = h.shape[-1]
+    return (torch.empty_like(h), h.new_empty(N, dtype=torch.float32),
+            h.new_empty(N if has_beta else 0, dtype=torch.float32))
+
+
+def _norm_setup(ctx, inputs, output):
+    x, gamma, beta, residual, eps, rms = inputs
+    y, h, mean, rstd = output
+    ctx.save_for_backward(x if residual is None else h, gamma, mean, rstd)
+    ctx.rms = rms
+    ctx.meta = (gamma.dtype, None if beta is None else beta.dtype, residual is not None,
+                x.dtype, None if residual is None else residual.dtype)
+
+
+def _norm_backward(ctx, dy, dh, dmean, drstd):
+    h, gamma, mean, rstd = ctx.saved_tensors
+    gd, bd, has_res, xd, rd = ctx.meta
+    dh_in = dh.contiguous() if (has_res and dh is not None) else None
+    dx, dg, db = norm_bwd(dy.contiguous(), dh_in, h, gamma, mean, rstd, ctx.rms, bd is not None)
+    return (dx.to(xd), dg.to(gd), db.to(bd) if bd is not None else None,
+            dx.to(rd) if has_res else None, None, None)
+
+
+norm_fwd.register_autograd(_norm_backward, setup_context=_norm_setup)
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float = 1e-5,
+               residual: Optional[Tensor] = None):
+    """LayerNorm over the last dim.  With ``residual`` returns ``(y, h)``, h = x + residual."""
+    y, h, _, _ = norm_fwd(x, weight, bias, residual, eps, False)
+    return (y, h) if residual is not None else y
+
+
+def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6, residual: Optional[Tensor] = None):
+    y, h, _, _ = norm_fwd(x, weight, None, residual, eps, True)
+    return (y, h) if residual is not None else y
+
+
+# =========================================================================== activations
+@torch.library.custom_op("pfeife::act_fwd", mutates_args=())
+def act_fwd(x: Tensor, act: int) -> Tensor:
+    if _native(x):
+        op = {ACT_GELU: kx.EW_GELU, ACT_GELU_TANH: kx.EW_GELU_TANH, ACT_SILU: kx.EW_SILU}[act]
+        return kx.elementwise(op, x).view(x.shape)
+    return _act_ref(x, act)
+
+
+@act_fwd.register_fake
+def _(x, act):
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("pfeife::act_bwd", mutates_args=())
+def act_bwd(dy: Tensor, x: Tensor, act: int) -> Tensor:
+    if _native(x):
+        op = {ACT_GELU: kx.EW_DGELU, ACT_GELU_TANH: kx.EW_DGELU_TANH, ACT_SILU: kx.EW_DSILU}[act]
+        return kx.elementwise(op, dy.contiguous(), x).view(x.shape)
+    return (dy.float() * _dact_ref(x, act)).to(x.dtype)
+
+
+@act_bwd.register_fake
+def _(dy, x, act):
+    return torch.empty_like(x)
+
+
+act_fwd.register_autograd(
+    lambda ctx, dy: (act_bwd(dy, ctx.saved_tensors[0], ctx.act), None),
+    setup_context=lambda ctx, inputs, output: (ctx.save_for_backward(inputs[0]),
+                                               setattr(ctx, "act", inputs[1])))
+
+
+def gelu(x: Tensor, approximate: str = "none") -> Tensor:
+    return act_fwd(x, ACT_GELU_TANH if approximate == "tanh" else ACT_GELU)
+
+
+def silu(x: Tensor) -> Tensor:
+    return act_fwd(x, ACT_SILU)
+
+
+@torch.library.custom_op("pfeife::glu_fwd", mutates_args=())
+def glu_fwd(gu: Tensor, gelu_gate: bool) -> Tensor:
+    if _native(gu) and (gu.shape[-1] // 2) % 8 == 0:
+        return kx.glu_fwd(gu, gelu_gate)
+    H = gu.shape[-1] // 2
+    g, u = gu[..., :H].float(), gu[..., H:].float()
+    return ((F.gelu(g) if gelu_gate else F.silu(g)) * u).to(gu.dtype)
+
+
+@glu_fwd.register_fake
+def _(gu, gelu_gate):
+    return gu.new_empty(gu.shape[:-1] + (gu.shape[-1] // 2,))
+
+
+@torch.library.custom_op("pfeife::glu_bwd", mutates_args=())
+def glu_bwd(dout: Tensor, gu: Tensor, gelu_gate: bool) -> Tensor:
+    if _native(gu) and (gu.shape[-1] // 2) % 8 == 0:
+        return kx.glu_bwd(gu, dout, gelu_gate)
+    H = gu.shape[-1] // 2
+    g, u, d = gu[..., :H].float(), gu[..., H:].float(), dout.float()
+    act = ACT_GELU if gelu_gate else ACT_SILU
+    dg = d * u * _dact_ref(g, act)
+    du = d * _act_ref(g, act)
+    return torch.cat([dg, du], -1).to(gu.dtype)
+
+
+@glu_bwd.register_fake
+def _(dout, gu, gelu_gate):
+    return torch.empty_like(gu)
+
+
+glu_fwd.register_autograd(
+    lambda ctx, dy: (glu_bwd(dy.contiguous(), ctx.saved_tensors[0], ctx.gelu_gate), None),
+    setup_context=lambda ctx, inputs, output: (ctx.save_for_backward(inputs[0]),
+                                               setattr(ctx, "gelu_gate", inputs[1])))
+
+
+def swiglu(gate_up: Tensor) -> Tensor:
+    """silu(gate) * up on a fused [..., 2H] projection (gate first)."""
+    return glu_fwd(gate_up, False)
+
+
+def geglu(gate_up: Tensor) -> Tensor:
+    """gelu(gate) * up on a fused [..., 2H] projection (gate first)."""
+    return glu_fwd(gate_up, True)
+
+
+# =========================================================================== losses
+@torch.library.custom_op("pfeife::ce_fwd", mutates_args=())
+def ce_fwd(logits: Tensor, target: Tensor, ignore_index: int) -> Tuple[Tensor, Tensor]:
+    """-> (per-row loss fp32, per-row log-sum-exp fp32); logits [rows, V]."""
+    if logits.is_cuda:
+        return kx.ce_fwd(logits.contiguous(), target, ignore_index)
+    lf = logits.float()
+    lse = torch.logsumexp(lf, -1)
+    return F.cross_entropy(lf, target, reduction="none", ignore_index=ignore_index), lse
+
+
+@ce_fwd.register_fake
+def _(logits, target, ignore_index):
+    r = logits.new_empty(logits.shape[0], dtype=torch.float32)
+    return r, torch.empty_like(r)
+
+
+@torch.library.custom_op("pfeife::ce_bwd", mutates_args=())
+def ce_bwd(dloss: Tensor, logits: Tensor, target: Tensor, lse: Tensor, ignore_index: int) -> Tensor:
+    if logits.is_cuda:
+        return kx.ce_bwd(logits.contiguous(), target, lse, dloss.float().contiguous(), ignore_index)
+    p = torch.exp(logits.float() - lse[:, None])
+    valid = target != ignore_index
+    onehot = torch.zeros_like(p)
+    onehot[valid, target[valid]] = 1.0
+    return ((p - onehot) * (dloss.float() * valid)[:, None]).to(logits.dtype)
+
+
+@ce_bwd.register_fake
+def _(dloss, logits, target, lse, ignore_index):
+    return torch.empty_like(logits)
+
+
+def _ce_setup(ctx, inputs, output):
+    logits, target, ignore_index = inputs
+    ctx.save_for_backward(logits, target, output[1])
+    ctx.ignore_index = ignore_index
+
+
+ce_fwd.register_autograd(
+    lambda ctx, dloss, dlse: (ce_bwd(dloss.contiguous(), ctx.saved_tensors[0], ctx.saved_tensors[1],
+                                     ctx.saved_tensors[2], ctx.ignore_index), None, None),
+    setup_context=_ce_setup)
+
+
+def cross_entropy(logits: Tensor, target: Tensor, ignore_index: int = -100,
+                  reduction: str = "mean") -> Tensor:
+    """Fused log-softmax + NLL over the last dim; the probabilities are never materialised in
+    the forward and the backward is one pass over the logits."""
+    V = logits.shape[-1]
+    loss, _ = ce_fwd(logits.reshape(-1, V), target.reshape(-1), ignore_index)
+    if reduction == "none":
+        return loss.view(target.shape)
+    if reduction == "sum":
+        return loss.sum()
+    valid = (target.reshape(-1) != ignore_index).sum().clamp(min=1)
+    return loss.sum() / valid
+
+
+@torch.library.custom_op("pfeife::mse_fwd", mutates_args=())
+def mse_fwd(a: Tensor, b: Tensor) -> Tensor:
+    if _native(a) or (a.is_cuda and a.dtype == torch.float32):
+        return kx.mse_fwd(a, b.to(a.dtype)).view(())
+    return F.mse_loss(a.float(), b.float())
+
+
+@mse_fwd.register_fake
+def _(a, b):
+    return a.new_empty((), dtype=torch.float32)
+
+
+@torch.library.custom_op("pfeife::mse_bwd", mutates_args=())
+def mse_bwd(g: Tensor, a: Tensor, b: Tensor) -> Tensor:
+    if _native(a) or (a.is_cuda and a.dtype == torch.float32):
+        return kx.mse_bwd(a, b.to(a.dtype), g.reshape(1)).view(a.shape)
+    return (2.0 * (a.float() - b.float()) * g.float() / a.numel()).to(a.dtype)
+
+
+@mse_bwd.register_fake
+def _(g, a, b):
+    return torch.empty_like(a)
+
+
+mse_fwd.register_autograd(
+    lambda ctx, g: (mse_bwd(g, *ctx.saved_tensors), None),
+    setup_context=lambda ctx, inputs, output: ctx.save_for_backward(inputs[0], inputs[1]))
+
+
+def mse_loss(a: Tensor, b: Tensor) -> Tensor:
+    return mse_fwd(a, b)
+
+
+# =========================================================================== embedding / rope
+@torch.library.custom_op("pfeife::embed_fwd", mutates_args=())
+def embed_fwd(ids: Tensor, table: Tensor, out_dtype: torch.dtype) -> Tensor:
+    if table.is_cuda:
+        t = table
+        if t.dtype != out_dtype and t.dtype != torch.float32:
+            t = t.float()
+        return kx.embed_fwd(t, ids, out_dtype)
+    return F.embedding(ids, table).to(out_dtype)
+
+
+@embed_fwd.register_fake
+def _(ids, table, out_dtype):
+    return table.new_empty(ids.shape + (table.shape[1],), dtype=out_dtype)
+
+
+@torch.library.custom_op("pfeife::embed_bwd", mutates_args=())
+def embed_bwd(dout: Tensor, ids: Tensor, table: Tensor) -> Tensor:
+    """-> fp32 gradient table (empty when it was accumulated into a registered bucket)."""
+    slot = _slot(table)
+    if table.is_cuda:
+        if slot is not None and slot.main_grad is not None:
+            kx.embed_bwd(dout, ids, slot.main_grad.view(table.shape))
+            return dout.new_empty(0, dtype=torch.float32)
+        g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        return kx.embed_bwd(dout, ids, g)
+    g = torch.zeros(table.shape, dtype=torch.float32)
+    return g.index_add_(0, ids.reshape(-1), dout.reshape(-1, table.shape[1]).float())
+
+
+@embed_bwd.register_fake
+def _(dout, ids, table):
+    return table.new_empty(table.shape, dtype=torch.float32)
+
+
+def _embed_backward(ctx, dout):
+    ids, table = ctx.saved_tensors
+    g = embed_bwd(dout.contiguous(), ids, table)
+    return None, (g.to(table.dtype) if g.numel() else None), None
+
+
+embed_fwd.register_autograd(
+    _embed_backward,
+    setup_context=lambda ctx, inputs, output: ctx.save_for_backward(inputs[0], inputs[1]))
+
+
+def embedding(ids: Tensor, table: Tensor, out_dtype: Optional[torch.dtype] = None) -> Tensor:
+    if out_dtype is None:
+        out_dtype = compute_dtype(table)
+    return embed_fwd(ids, table, out_dtype)
+
+
+@torch.library.custom_op("pfeife::rope_apply", mutates_args=())
+def rope_apply(x: Tensor, cos: Tensor, sin: Tensor, inverse: bool) -> Tensor:
+    """x [B, S, H, D]; cos/sin fp32 [S, D/2]; half-split pairing (i, i + D/2)."""
+    if _native(x) or (x.is_cuda and x.dtype == torch.float32):
+        return kx.rope(x if x.stride(-1) == 1 else x.contiguous(), cos.float(), sin.float(), inverse)
+    D = x.shape[-1]
+    xf = x.float()
+    x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
+    c = cos.float()[None, :, None, :]
+    s = sin.float()[None, :, None, :]
+    if inverse:
+        s = -s
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+
+
+@rope_apply.register_fake
+def _(x, cos, sin, inverse):
+    return torch.empty_like(x)
+
+
+def _rope_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[1], inputs[2])
+    ctx.inverse = inputs[3]
+
+
+rope_apply.register_autograd(
+    lambda ctx, dy: (rope_apply(dy.contiguous(), ctx.saved_tensors[0], ctx.saved_tensors[1],
+                                not ctx.inverse), None, None, None),
+    setup_context=_rope_setup)
+
+
+def rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    return rope_apply(x, cos, sin, False)
+
+
+def rope_tables(seq_len: int, head_dim: int, theta: float = 10000.0, device=None
+                ) -> Tuple[Tensor, Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32)
+                           / head_dim))
+    ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
+    return ang.cos(), ang.sin()
