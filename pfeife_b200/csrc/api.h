@@ -11,6 +11,10 @@
 #define PF_DECL
 #endif
 
+// ---- device.cu
+PF_DECL int pf_bind_device(int device);
+PF_DECL int pf_device_count();
+
 // ---- gemm_sm100.cu : C[M,N] = epi(alpha * A . B^T), tcgen05 / TMEM / TMA
 PF_DECL int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                     long long ldb, long long ldc, int a_mn, int b_mn, int in_dtype, int out_dtype,

@@ -345,7 +345,7 @@ int make_tmap_2d_16bit(CUtensorMap* map, const void* base, int fmt, long long in
                    2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -101;
+  return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
 }
 
 template <typename OutT, int BN, int STAGES>
@@ -420,4 +420,11 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     case PF_BF16: return PF_GEMM_DISPATCH(__nv_bfloat16);
   }
   return -1;
+}
+
+// Diagnostic: result of encoding a 2-D 16-bit tensor map with the given geometry (0 = ok).
+PF_API int pf_tmap_probe(const void* base, long long inner, long long outer, long long ld,
+                         int box_inner, int box_outer) {
+  CUtensorMap m;
+  return make_tmap_2d_16bit(&m, base, 1, inner, outer, ld, box_inner, box_outer);
 }

@@ -1,0 +1,241 @@
+"""Graph bench: per-segment latency and memory of a captured graph on one device.
+
+Behavioural counterpart of pfeife/local/graph_bench.py:172-625 and the three interpreters of
+pfeife/graph/computation_graph.py:487-1450, folded into one node-by-node executor:
+  * pass 1 runs the graph once with autograd on, recording per segment the growth of live
+    memory (``act_mem``) and the transient peak (``temp_mem``) from allocator statistics, and
+    keeps the model output for the caller;
+  * pass 2 repeats the forward ``TIME_WARM_ITER + TIME_CHECK_ITER`` times with one CUDA event
+    pair per segment (one device sync per iteration, none per segment);
+  * pass 3 times whole forward vs forward+backward to get ``fb_ratio`` (clamped to >= 1);
+  * optionally the optimizer step is timed on the real parameters and apportioned to segments
+    by parameter bytes.
+On CPU the same executor uses ``perf_counter`` and tensor sizes.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.fx as fx
+
+from ..utils import get_logger
+from .capture import CapturedGraph
+from .comp_graph import CompGraph, _tensor_leaves
+
+TIME_WARM_ITER = 2
+TIME_CHECK_ITER = 5
+
+
+def gen_amp_context(device: torch.device, dtype: Optional[torch.dtype]):
+    if dtype is None:
+        return contextlib.nullcontext()
+    return torch.autocast(device_type=device.type, dtype=dtype)
+
+
+def _last_uses(gm: fx.GraphModule) -> Dict[str, List[str]]:
+    """node name -> values that die right after it (freed by the executor)."""
+    last: Dict[str, str] = {}
+    for n in gm.graph.nodes:
+        for a in n.all_input_nodes:
+            last[a.name] = n.name
+    out: Dict[str, List[str]] = {}
+    for v, user in last.items():
+        out.setdefault(user, []).append(v)
+    return out
+
+
+class SegmentExecutor:
+    """Runs a captured graph node by node, calling ``on_segment_start/end`` at segment
+    boundaries."""
+
+    def __init__(self, graph: CompGraph):
+        self.graph = graph
+        self.gm = graph.captured.gm
+        self.frees = _last_uses(self.gm)
+        self.nodes = list(self.gm.graph.nodes)
+
+    def run(self, args: Sequence[Any], on_start=None, on_end=None, keep_all: bool = False) -> Any:
+        env: Dict[str, Any] = {}
+        it = iter(args)
+        cur_seg = -1
+        seg_of = self.graph.seg_of
+        for n in self.nodes:
+            if n.op == "placeholder":
+                env[n.name] = next(it)
+                continue
+            if n.op == "output":
+                if cur_seg >= 0 and on_end:
+                    on_end(cur_seg)
+                return fx.node.map_arg(n.args[0], lambda a: env[a.name])
+            seg = seg_of[n.name]
+            if seg != cur_seg:
+                if cur_seg >= 0 and on_end:
+                    on_end(cur_seg)
+                if on_start:
+                    on_start(seg)
+                cur_seg = seg
+            a = fx.node.map_arg(n.args, lambda x: env[x.name])
+            k = fx.node.map_arg(n.kwargs, lambda x: env[x.name])
+            if n.op == "call_function":
+                env[n.name] = n.target(*a, **k)
+            elif n.op == "call_method":
+                env[n.name] = getattr(a[0], n.target)(*a[1:], **k)
+            elif n.op == "call_module":
+                env[n.name] = self.gm.get_submodule(n.target)(*a, **k)
+            elif n.op == "get_attr":
+                obj = self.gm
+                for atom in n.target.split("."):
+                    obj = getattr(obj, atom)
+                env[n.name] = obj
+            if not keep_all:
+                for v in self.frees.get(n.name, ()):
+                    if v in env and self.gm.graph is not None:
+                        del env[v]
+        raise RuntimeError("graph has no output node")
+
+
+def _sum_outputs(out: Any) -> Optional[torch.Tensor]:
+    total = None
+    for t in _tensor_leaves(out if not isinstance(out, dict) else list(out.values())):
+        if t.dtype.is_floating_point and t.requires_grad:
+            s = t.float().sum()
+            total = s if total is None else total + s
+    return total
+
+
+def measure_optimizer(graph: CompGraph, option, device: torch.device) -> float:
+    """Times ``TIME_CHECK_ITER`` optimizer steps on the graph's parameters (gradients set to
+    zeros) and apportions the mean to segments by parameter bytes.  Returns the mean in ms."""
+    params = [i.tensor for i in graph.captured.params if i.tensor.requires_grad]
+    if not params:
+        return 0.0
+    opt = option.make_optimizer(params)
+    for p in params:
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+    saved = [p.detach().clone() for p in params]
+    sync = torch.cuda.synchronize if device.type == "cuda" else (lambda: None)
+    for _ in range(TIME_WARM_ITER):
+        opt.step()
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(TIME_CHECK_ITER):
+        opt.step()
+    sync()
+    ms = (time.perf_counter() - t0) * 1e3 / TIME_CHECK_ITER
+    with torch.no_grad():
+        for p, s in zip(params, saved):
+            p.copy_(s)
+            p.grad = None
+    total = sum(n.param_bytes for n in graph.nodes) or 1
+    for n in graph.nodes:
+        n.optim_time = ms * n.param_bytes / total
+    return ms
+
+
+def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: torch.device,
+                         option) -> Tuple[CompGraph, Any]:
+    """Profiles `captured` with call arguments `args` (placeholder order) on `device`.
+
+    Returns the profiled graph and the output of one real forward (so the probing call of the
+    user's ``exec_fn`` can continue into its loss and backward)."""
+    log = get_logger()
+    graph = CompGraph(captured)
+    ex = SegmentExecutor(graph)
+    is_cuda = device.type == "cuda"
+    amp = lambda: gen_amp_context(device, option.mixed_precision)
+
+    cached = option.graph_bench and os.path.exists(option.graph_bench)
+    # ---- pass 1: one real forward with memory statistics
+    mem_before: Dict[int, int] = {}
+    if is_cuda:
+        torch.cuda.synchronize(device)
+
+        def on_start(seg):
+            torch.cuda.reset_peak_memory_stats(device)
+            mem_before[seg] = torch.cuda.memory_allocated(device)
+
+        def on_end(seg):
+            now = torch.cuda.memory_allocated(device)
+            peak = torch.cuda.max_memory_allocated(device)
+            node = graph.nodes[seg]
+            node.act_mem = max(0, now - mem_before[seg])
+            node.temp_mem = max(node.act_mem, peak - mem_before[seg])
+    else:
+        on_start = on_end = None
+    with amp():
+        output = ex.run(args, None if cached else on_start, None if cached else on_end)
+    if cached:
+        graph.load_graph_data(option.graph_bench)
+        log.info("loaded graph bench from %s: %s", option.graph_bench, graph.summary())
+        return graph, output
+
+    # ---- pass 2: per-segment forward timing
+    n_seg = len(graph.nodes)
+    acc = [0.0] * n_seg
+    for it in range(TIME_WARM_ITER + TIME_CHECK_ITER):
+        timed = it >= TIME_WARM_ITER
+        if is_cuda:
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(n_seg)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(n_seg)]
+            with torch.no_grad(), amp():
+                ex.run(args, lambda s: starts[s].record(), lambda s: ends[s].record())
+            torch.cuda.synchronize(device)
+            if timed:
+                for s in range(n_seg):
+                    acc[s] += starts[s].elapsed_time(ends[s])
+        else:
+            t: Dict[int, float] = {}
+            with torch.no_grad(), amp():
+                ex.run(args, lambda s: t.__setitem__(s, time.perf_counter()),
+                       lambda s: acc.__setitem__(s, acc[s] + (time.perf_counter() - t[s]) * 1e3
+                                                 if timed else acc[s]))
+    for s in range(n_seg):
+        graph.nodes[s].comp_time = max(acc[s] / TIME_CHECK_ITER, 1e-4)
+
+    # ---- pass 3: forward vs backward wall clock
+    sync = (lambda: torch.cuda.synchronize(device)) if is_cuda else (lambda: None)
+    fwd_ms = bwd_ms = 0.0
+    for it in range(TIME_WARM_ITER + TIME_CHECK_ITER):
+        sync()
+        t0 = time.perf_counter()
+        with amp():
+            out = ex.run(args)
+        loss = _sum_outputs(out)
+        sync()
+        t1 = time.perf_counter()
+        if loss is not None:
+            loss.backward()
+        sync()
+        t2 = time.perf_counter()
+        if it >= TIME_WARM_ITER:
+            fwd_ms += (t1 - t0) * 1e3
+            bwd_ms += (t2 - t1) * 1e3
+    for i in captured.params:
+        i.tensor.grad = None
+    graph.fb_ratio = max(1.0, bwd_ms / fwd_ms) if fwd_ms > 0 else 2.0
+    log.info("forward: %.4f ms, backward: %.4f ms", fwd_ms / TIME_CHECK_ITER,
+             bwd_ms / TIME_CHECK_ITER)
+
+    if not option.no_bench_optimizer:
+        measure_optimizer(graph, option, device)
+    if option.graph_bench:
+        graph.save_graph_data(option.graph_bench)
+    return graph, output
+
+
+def gen_comp_graph_cpu(captured: CapturedGraph, args: Sequence[Any], option
+                       ) -> Tuple[CompGraph, Any]:
+    """Unit-time profile for CPU tests: every segment costs 1 ms forward, ``fb_ratio`` 2
+    (pfeife/local/graph_bench.py:125-144)."""
+    graph = CompGraph(captured)
+    with gen_amp_context(torch.device("cpu"), option.mixed_precision):
+        output = SegmentExecutor(graph).run(args)
+    for n in graph.nodes:
+        n.comp_time = 1.0
+    graph.fb_ratio = 2.0
+    return graph, output

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from pathlib import Path
 from typing import Optional
 
@@ -79,7 +80,23 @@ def ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
+_tls = threading.local()
+
+
+def bind_thread(device_index: Optional[int] = None) -> None:
+    """Makes sure the calling thread has the device's context bound inside the library's own
+    CUDA runtime (threads created by PyTorch, such as autograd workers, arrive without one)."""
+    idx = torch.cuda.current_device() if device_index is None else device_index
+    if getattr(_tls, "dev", None) != idx:
+        code = lib().pf_bind_device(int(idx))
+        if code != 0:
+            raise KernelError(f"pf_bind_device({idx}): CUDA error {code}")
+        _tls.dev = idx
+
+
 def stream() -> ctypes.c_void_p:
+    """Current torch stream handle; also binds the calling thread to the current device."""
+    bind_thread()
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -101,6 +118,8 @@ def check(code: int, what: str) -> None:
         reasons = {-1: "unsupported dtype", -2: "misaligned pointer or pitch",
                    -3: "size beyond kernel limit", -100: "tensor-map encoder unavailable",
                    -101: "tensor-map encoding failed"}
+        if code <= -1000:
+            raise KernelError(f"{what}: tensor-map encoding failed (CUresult {-code - 1000})")
         raise KernelError(f"{what}: {reasons.get(code, code)}")
     _launches += 1
 

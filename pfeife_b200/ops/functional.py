@@ -171,7 +171,7 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
         if act:
             kop = {ACT_GELU: kx.EW_DGELU, ACT_GELU_TANH: kx.EW_DGELU_TANH, ACT_SILU: kx.EW_DSILU}[act]
             dy2 = kx.elementwise(kop, dy2, _rows(aux))
-        dx = dw = db = empty
+        dx, dw, db = dy.new_empty(0), dy.new_empty(0), dy.new_empty(0)
         if need_dx:
             w2 = _weight_as(w, cd)
             if N % 8 == 0 and K % 8 == 0:
@@ -195,9 +195,9 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
         return dx, dw, db
     dz = dy if not act else (dy.float() * _dact_ref(aux, act)).to(cd)
     dz2 = dz.reshape(-1, N)
-    dx = (dz2 @ w.to(cd)).view(x.shape[:-1] + (K,)) if need_dx else empty
-    dw = (dz2.float().t() @ x.reshape(-1, K).float()).to(w.dtype) if need_dw else empty
-    db = dz2.float().sum(0) if need_db else empty
+    dx = (dz2 @ w.to(cd)).view(x.shape[:-1] + (K,)) if need_dx else dy.new_empty(0)
+    dw = (dz2.float().t() @ x.reshape(-1, K).float()).to(w.dtype) if need_dw else dy.new_empty(0)
+    db = dz2.float().sum(0) if need_db else dy.new_empty(0)
     return dx, dw, db
 
 
@@ -703,3 +703,87 @@ def rope_tables(seq_len: int, head_dim: int, theta: float = 10000.0, device=None
                            / head_dim))
     ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
     return ang.cos(), ang.sin()
+
+
+# =========================================================================== attention
+def _sdpa_ref(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float
+              ) -> Tuple[Tensor, Tensor]:
+    """fp32 reference: q,k,v [B, S, H, D] -> (o [B, Sq, H, D], lse [B, H, Sq])."""
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        sq, sk = s.shape[-2:]
+        mask = torch.ones(sq, sk, dtype=torch.bool, device=s.device).tril(sk - sq)
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - lse[..., None])
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3)
+    return o.to(q.dtype), lse
+
+
+@torch.library.custom_op("pfeife::attn_fwd", mutates_args=())
+def attn_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float) -> Tuple[Tensor, Tensor]:
+    """Flash attention forward.  q [B, Sq, H, D], k/v [B, Sk, H, D] (any strides with a unit
+    inner stride) -> (o [B, Sq, H, D] contiguous, lse fp32 [B, H, Sq])."""
+    if _native(q) and kx.attention_supported(q, k, v):
+        return kx.attn_fwd(q, k, v, causal, scale)
+    o, lse = _sdpa_ref(q, k, v, causal, scale)
+    return o.contiguous(), lse.contiguous()
+
+
+@attn_fwd.register_fake
+def _(q, k, v, causal, scale):
+    B, Sq, H, D = q.shape
+    return q.new_empty((B, Sq, H, D)), q.new_empty((B, H, Sq), dtype=torch.float32)
+
+
+@torch.library.custom_op("pfeife::attn_bwd", mutates_args=())
+def attn_bwd(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, causal: bool,
+             scale: float) -> Tuple[Tensor, Tensor, Tensor]:
+    if _native(q) and kx.attention_supported(q, k, v):
+        return kx.attn_bwd(do, q, k, v, o, lse, causal, scale)
+    qf, kf, vf, dof = (t.float().permute(0, 2, 1, 3) for t in (q, k, v, do))
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        sq, sk = s.shape[-2:]
+        mask = torch.ones(sq, sk, dtype=torch.bool, device=s.device).tril(sk - sq)
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.exp(s - lse[..., None])
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    delta = (dof * o.float().permute(0, 2, 1, 3)).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    back = lambda t, like: t.permute(0, 2, 1, 3).to(like.dtype).contiguous()
+    return back(dq, q), back(dk, k), back(dv, v)
+
+
+@attn_bwd.register_fake
+def _(do, q, k, v, o, lse, causal, scale):
+    return (q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape))
+
+
+def _attn_setup(ctx, inputs, output):
+    q, k, v, causal, scale = inputs
+    o, lse = output
+    ctx.save_for_backward(q, k, v, o, lse)
+    ctx.causal, ctx.scale = causal, scale
+
+
+def _attn_backward(ctx, do, dlse):
+    q, k, v, o, lse = ctx.saved_tensors
+    dq, dk, dv = attn_bwd(do.contiguous(), q, k, v, o, lse, ctx.causal, ctx.scale)
+    return dq, dk, dv, None, None
+
+
+attn_fwd.register_autograd(_attn_backward, setup_context=_attn_setup)
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = False,
+              scale: Optional[float] = None) -> Tensor:
+    """softmax(q k^T * scale [+ causal mask]) v without materialising the score matrix.
+    Layout [batch, seq, heads, head_dim]; q/k/v may be strided views of a fused projection."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return attn_fwd(q, k, v, causal, float(scale))[0]

@@ -74,6 +74,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                      c_ll(residual.stride(0) if residual is not None else 0), ptr(aux),
                      c_ll(aux.stride(0) if aux is not None else 0), epilogue, int(accumulate),
                      c_f(alpha), ptr(status_word(a.device)), sm_count(a.device), tile_n, stream())
+    if code != 0:
+        check(code, f"pf_gemm(M={M}, N={N}, K={K}, a={tuple(a.shape)}/{a.stride()}/{a.dtype}/"
+                    f"{a.data_ptr() % 256}, b={tuple(b.shape)}/{b.stride()}/{b.data_ptr() % 256}, "
+                    f"a_mn={a_mn}, b_mn={b_mn}, out={out.dtype}/{out.stride()})")
     check(code, "pf_gemm")
     return out
 
@@ -327,3 +331,16 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool = 
                     D, c_ll(x.stride(0)), c_ll(x.stride(1)), c_ll(x.stride(2)), int(inverse),
                     dt(x.dtype), sm_count(x.device), stream()), "pf_rope")
     return out
+
+
+# --------------------------------------------------------------------------- attention
+def attention_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """True when the native flash-attention kernels cover this problem."""
+    L = _lib.lib()
+    return L is not None and hasattr(L, "pf_attn_fwd") and _attn_ok(q, k, v)
+
+
+def _attn_ok(q, k, v) -> bool:
+    D = q.shape[-1]
+    return (q.dtype in (torch.float16, torch.bfloat16) and D % 8 == 0 and D <= 128
+            and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1)

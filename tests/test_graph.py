@@ -1,0 +1,139 @@
+"""Capture, segmentation, profile cache and partitioning on CPU: the composition of the stage
+graphs must equal the original graph for every split, including skip connections, tied weights
+and multi-output models."""
+import itertools
+import os
+
+import pytest
+import torch
+
+from pfeife_b200.graph.capture import classify_inputs, qualified_name
+from pfeife_b200.graph.comp_graph import CompGraph
+from pfeife_b200.graph.partition import check_partition, partition_module
+from pfeife_b200.graph.profiler import gen_comp_graph_cpu, gen_local_comp_graph
+from pfeife_b200.models.toy import DeepMLP, SkipNet, TiedMLP
+from pfeife_b200.models.vit import ViT, vit_config
+from pfeife_b200.option import PipeOption
+
+
+def capture(model, *args, **kwargs):
+    box = {}
+
+    def backend(gm, example_inputs):
+        box["cap"] = classify_inputs(gm, example_inputs)
+        box["args"] = list(example_inputs)
+        return gm.forward
+
+    torch._dynamo.reset()
+    out = torch.compile(model, backend=backend)(*args, **kwargs)
+    return box["cap"], box["args"], out
+
+
+def test_qualified_name():
+    assert qualified_name("L['self']._modules['blocks']._modules['0']._parameters['weight']",
+                          "x") == "blocks.0.weight"
+    assert qualified_name("L['s']._buffers['pos']", "x") == "pos"
+    assert qualified_name(None, "fallback") == "fallback"
+
+
+def test_capture_classifies_params_buffers_inputs():
+    model = ViT(vit_config("vit_tiny", num_layers=2, image_size=32, patch_size=16))
+    cap, args, out = capture(model, torch.randn(2, 3, 32, 32))
+    names = {i.qualname for i in cap.params}
+    assert names == {n for n, _ in model.named_parameters()}
+    assert len(cap.user_inputs) == 1 and cap.user_inputs[0].tensor.shape == (2, 3, 32, 32)
+    # the table holds the model's own Parameter objects
+    by_name = dict(model.named_parameters())
+    assert all(i.tensor is by_name[i.qualname] for i in cap.params)
+
+
+def test_tied_weight_is_one_placeholder():
+    cap, _, _ = capture(TiedMLP(), torch.randn(4, 10))
+    assert len(cap.params) == 2 + 2   # first(=last) weight/bias + middle weight/bias
+    cg = CompGraph(cap)
+    shared = [ph for ph, segs in cg.param_set.users.items() if len(segs) > 1]
+    assert len(shared) == 2
+
+
+@pytest.mark.parametrize("model_fn,inp", [
+    (lambda: DeepMLP(16, 6, 4), (5, 16)),
+    (lambda: SkipNet(16, 3), (5, 16)),
+    (lambda: TiedMLP(10, 2), (5, 10)),
+])
+def test_partition_composition_equals_original(model_fn, inp):
+    torch.manual_seed(0)
+    model = model_fn()
+    x = torch.randn(*inp)
+    cap, args, ref = capture(model, x)
+    cg = CompGraph(cap)
+    n = len(cg.nodes)
+    assert n >= 4
+    for k in (1, 2, 3):
+        for pts in itertools.islice(itertools.combinations(range(1, n), k), 0, 40, 7):
+            part = partition_module(cg, list(pts), device_cnt=2)
+            assert len(part.stages) == k + 1
+            out = check_partition(cg, part, args)
+            got = out[0] if isinstance(out, (tuple, list)) else out
+            assert torch.allclose(got, ref, atol=1e-6), pts
+
+
+def test_partition_vit_with_native_ops_and_shared_detection():
+    torch.manual_seed(0)
+    model = ViT(vit_config("vit_tiny", num_layers=3, image_size=32, patch_size=16))
+    x = torch.randn(2, 3, 32, 32)
+    cap, args, ref = capture(model, x)
+    cg = CompGraph(cap)
+    n = len(cg.nodes)
+    part = partition_module(cg, [n // 3, 2 * n // 3], device_cnt=3)
+    out = check_partition(cg, part, args)
+    assert torch.allclose(out[0], ref, atol=1e-5)
+    assert part.shared_states == {}
+    # every parameter is owned by exactly one rank
+    owned = [i for r in range(3) for i in part.rank_states(r)]
+    assert sorted(set(owned)) == sorted(i.index for i in cap.inputs if i.is_state)
+    # gradients flow through the partitioned graph like through the original
+    ref.sum().backward()
+    g_ref = {n_: p.grad.clone() for n_, p in model.named_parameters()}
+    model.zero_grad()
+    check_partition(cg, part, args)[0].sum().backward()
+    for n_, p in model.named_parameters():
+        assert torch.allclose(p.grad, g_ref[n_], atol=1e-5), n_
+
+
+def test_tied_params_across_ranks_are_reported_shared():
+    cap, args, ref = capture(TiedMLP(10, 2), torch.randn(4, 10))
+    cg = CompGraph(cap)
+    part = partition_module(cg, [len(cg.nodes) // 2], device_cnt=2)
+    assert len(part.shared_states) == 2
+    assert all(r == [0, 1] for r in part.shared_states.values())
+
+
+def test_multi_output_dict_model():
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(8, 8)
+            self.b = torch.nn.Linear(8, 4)
+
+        def forward(self, x):
+            h = torch.relu(self.a(x))
+            return {"hidden": h, "logits": self.b(h), "const": 3}
+
+    cap, args, ref = capture(M(), torch.randn(3, 8))
+    cg = CompGraph(cap)
+    part = partition_module(cg, [2], device_cnt=2)
+    out = check_partition(cg, part, args)
+    assert len(part.sink_outputs()) == 2
+
+
+def test_graph_bench_cache_roundtrip(tmp_path):
+    cap, args, _ = capture(DeepMLP(16, 4, 4), torch.randn(5, 16))
+    path = str(tmp_path / "toy.graph")
+    opt = PipeOption(device_cnt=2, graph_bench=path, no_bench_optimizer=True, cpu_test=True)
+    cg, out = gen_local_comp_graph(cap, args, torch.device("cpu"), opt)
+    assert os.path.exists(path) and all(n.comp_time > 0 for n in cg.nodes)
+    cg2, _ = gen_local_comp_graph(cap, args, torch.device("cpu"), opt)   # loads the cache
+    assert [n.comp_time for n in cg2.nodes] == [n.comp_time for n in cg.nodes]
+    assert cg2.fb_ratio == cg.fb_ratio
+    cgu, _ = gen_comp_graph_cpu(cap, args, opt)
+    assert all(n.comp_time == 1.0 for n in cgu.nodes) and cgu.fb_ratio == 2.0
