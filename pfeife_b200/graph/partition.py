@@ -258,6 +258,11 @@ def partition_module(cg: CompGraph, split_points: Sequence[int], device_cnt: int
             if x.op == "placeholder":
                 return _InRef(ph_info[x.name].index)
             src = produced_in[x.name]
+            if src != n_stage - 1:
+                # model outputs always leave through the last stage (it lives on the main
+                # rank): an earlier stage's value is passed through it as an ordinary edge
+                resolve(n_stage - 1, x)
+                src = n_stage - 1
             j = export_value(src, x)
             if not any(c[0] == OUTSIDE for c in specs[src].outputs[j].consumers):
                 specs[src].outputs[j].consumers.append((OUTSIDE, -1))

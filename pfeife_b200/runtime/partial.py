@@ -1,0 +1,507 @@
+"""Public training front-end: ``partial_compiler`` (a ``torch.compile`` backend),
+``PartialModule`` and ``PartialRunner(option, optimizer).set_exec_fn / step``.
+
+User contract (pfeife/mp/partial/module.py:37-438, README "How to train custom models"):
+
+    initialize_pfeife()
+    option = PipeOption.from_args(args)
+    runner = PartialRunner(option, optimizer)
+    model = torch.compile(model, backend=partial_compiler)
+    runner.set_exec_fn(iter_fn)          # iter_fn(micro_batch...) calls model, loss.backward()
+    losses = runner.step(batch)          # one optimizer step over batch_cnt micro-batches
+
+``exec_fn`` runs in ``batch_cnt`` threads, one per micro-batch.  The compiled model call inside
+it lands in ``PartialModule.forward``, which hands the micro-batch's inputs to the pipeline,
+blocks until the last stage produced that micro-batch's outputs and returns them as detached
+leaves whose gradient hooks feed the pipeline's backward.  The first ``step`` probes (captures
+and profiles the graph with micro-batch 0), plans, partitions and distributes.
+
+Ranks that are not the main rank of their pipeline run ``worker_loop()`` instead of the user
+script (``mp_launch.py`` does this for them).
+"""
+from __future__ import annotations
+
+import atexit
+import copy
+import os
+import pickle
+import queue
+import tempfile
+import threading
+import uuid
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..graph.capture import CapturedGraph, classify_inputs
+from ..graph.comp_graph import CompGraph
+from ..graph.partition import OUTSIDE, PartitionGraph, partition_module
+from ..graph.profiler import gen_comp_graph_cpu, gen_local_comp_graph
+from ..option import PipeOption
+from ..parallel.device_bench import DeviceBench, NCCLDeviceBench
+from ..parallel.planner import Plan, get_pipe_class
+from ..parallel.schedule import get_scheduler_class
+from ..topology import PfeifeState, get_state
+from ..utils import get_logger
+from ..utils.batch import split_args_kwargs
+from .params import StateEntry, snapshot_hyper
+from .transport import DistTransport
+from .worker import LoopFlag, StageWorker
+
+STEP_TOKEN = object()
+_tls = threading.local()
+_current_runner: Optional["PartialRunner"] = None
+
+
+# ------------------------------------------------------------------------------ control plane
+class ControlPlane:
+    """Small host-side messages between the ranks of one pipeline (gloo)."""
+
+    def __init__(self, state: PfeifeState):
+        self.state = state
+        self.group = state.ctrl_pp
+        self.src = state.pp_main_rank
+
+    def bcast(self, obj: Any = None) -> Any:
+        if self.state.pp_size == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        return box[0]
+
+    def gather(self, obj: Any) -> Optional[List[Any]]:
+        if self.state.pp_size == 1:
+            return [obj]
+        out = [None] * self.state.pp_size if self.state.rank == self.src else None
+        dist.gather_object(obj, out, dst=self.src, group=self.group)
+        return out
+
+    def scatter(self, objs: Optional[List[Any]]) -> Any:
+        """Main rank passes one object per pp rank; every rank returns its own."""
+        if self.state.pp_size == 1:
+            return objs[0]
+        out = [None]
+        dist.scatter_object_list(out, objs if self.state.rank == self.src else None,
+                                 src=self.src, group=self.group)
+        return out[0]
+
+    def barrier(self) -> None:
+        if self.state.pp_size > 1:
+            dist.barrier(group=self.group)
+
+
+class _DistReducer:
+    def __init__(self, group):
+        self.group = group
+
+    def all_reduce_sum(self, t: torch.Tensor) -> None:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+
+def _make_worker(state: PfeifeState, option: PipeOption, runner=None) -> StageWorker:
+    transport = None
+    if state.pp_size > 1:
+        transport = DistTransport(state.rank, state.layout.all_pp_groups(), state.device)
+    w = StageWorker(state.pp_rank, state.pp_size, state.device, option, transport, runner,
+                    global_ranks=state.pp_group_ranks)
+
+    def sync_found_inf():
+        if state.world_size > 1:
+            dist.all_reduce(w.params.found_inf, op=dist.ReduceOp.MAX)
+    w.sync_found_inf = sync_found_inf
+    if state.dp_size > 1:
+        from ..parallel.dp import make_dp
+        w.dp = make_dp(state, option)
+    return w
+
+
+def _install_plan(worker: StageWorker, state: PfeifeState, payload: Dict[str, Any]) -> None:
+    worker.batch_cnt = payload["batch_cnt"]
+    worker.set_partition_graph(payload["part"], payload["entries"], payload["optimizer_type"],
+                               payload["hyper"])
+    worker.set_scheduler_steps(payload["steps"], payload["eval_steps"])
+    # groups for parameters shared across pipeline ranks: every rank of the job creates every
+    # group, in the same order
+    sets = sorted({tuple(r) for r in payload["part"].shared_states.values()})
+    made: Dict[Tuple[int, ...], Any] = {}
+    for pp_ranks in sets:
+        for pipeline in state.layout.all_pp_groups():
+            ranks = [pipeline[r] for r in pp_ranks]
+            g = dist.new_group(ranks)
+            if state.rank in ranks:
+                made[pp_ranks] = _DistReducer(g)
+    worker.shared_groups = {k: v for k, v in made.items() if worker.pp_rank in k}
+
+
+def worker_loop(option: Optional[PipeOption] = None) -> None:
+    """Body of a non-main pipeline rank (pfeife/mp/worker.py:168-240 ``wait_for_init`` +
+    ``run_loop``): receive the options and the plan, then execute step programs until told to
+    stop."""
+    state = get_state()
+    ctrl = ControlPlane(state)
+    option = ctrl.bcast(None)
+    option.set_logger()
+    worker = _make_worker(state, option)
+    _run_device_bench(state, option)
+    payload = ctrl.scatter(None)
+    _install_plan(worker, state, payload)
+    ctrl.barrier()
+    while True:
+        msg = ctrl.bcast(None)
+        flag = msg["flag"]
+        if flag == LoopFlag.STOP_LOOP:
+            break
+        if flag in (LoopFlag.CONTINUE_LOOP, LoopFlag.EVAL_LOOP):
+            worker.reset_cache()
+            worker.params.set_hyper(msg.get("hyper"))
+            worker.run(training=(flag == LoopFlag.CONTINUE_LOOP))
+        elif flag == LoopFlag.GATHER_PARAMS:
+            named = {k: v.cpu() for k, v in worker.params.named_tensors().items()}
+            opt = {k: {kk: vv.cpu() for kk, vv in st.items()}
+                   for k, st in worker.params.optimizer_state().items()} if msg.get("opt") else {}
+            ctrl.gather((named, opt))
+        elif flag == LoopFlag.LOAD_PARAMS:
+            worker.params.load_named(msg["named"])
+            if msg.get("opt"):
+                worker.params.load_optimizer_state(msg["opt"])
+        elif flag == LoopFlag.LOG_MEMORY_USAGE:
+            worker.log_memory_usage()
+
+
+def _run_device_bench(state: PfeifeState, option: PipeOption) -> DeviceBench:
+    """Link model shared by the ranks of a pipeline; measured once or loaded from
+    ``option.device_bench`` (pfeife/mp/worker.py:242-263)."""
+    if state.pp_size == 1:
+        return DeviceBench()
+    bench = NCCLDeviceBench(state.rank, state.pp_group_ranks, state.device, state.pp_group, option)
+    if state.cpu and not (option.device_bench and os.path.exists(option.device_bench)):
+        bench.set_uniform(state.pp_size, (0.05, 1.0, 0.0))   # CPU runs: a fixed toy link
+    else:
+        bench.run_bench(option.device_bench, uniform=True)
+    return bench
+
+
+# ------------------------------------------------------------------------------ PartialModule
+class PartialModule(torch.nn.Module):
+    """One captured FX graph.  Pipelined when it is the first eligible graph of the model
+    (enough compute nodes for ``pp_size`` stages); any other graph runs locally as captured
+    (pfeife/mp/partial/module.py:205-216, 392-396)."""
+
+    def __init__(self, gm: torch.fx.GraphModule, example_inputs: Sequence[Any]):
+        super().__init__()
+        self.gm = gm
+        self.runner: Optional[PartialRunner] = _current_runner
+        self.captured: Optional[CapturedGraph] = None
+        self.should_pp = False
+        self.probed = False
+        self.compiled = False
+        self.comp_graph: Optional[CompGraph] = None
+        self.part: Optional[PartitionGraph] = None
+        self.plan: Optional[Plan] = None
+        if self.runner is not None:
+            self.captured = classify_inputs(gm, example_inputs)
+            pp = self.runner.state.pp_size
+            n_nodes = self.captured.compute_node_count()
+            already = any(m.should_pp for m in self.runner.modules)
+            self.should_pp = (not already) and n_nodes >= max(2 * pp, 1) and \
+                len(self.captured.params) > 0
+            self.pipe_idx = len(self.runner.modules)
+            self.runner.modules.append(self)
+
+    # -- first call: profile on the main rank, return a real output so exec_fn can continue
+    def _probe_forward(self, args: Sequence[Any]) -> Any:
+        r = self.runner
+        opt = r.option
+        if r.state.cpu:
+            cg, out = gen_comp_graph_cpu(self.captured, args, opt)
+        else:
+            o = copy.copy(opt)
+            if r.state.dp_size > 1 and not o.graph_bench:
+                o.graph_bench = None
+            cg, out = gen_local_comp_graph(self.captured, args, r.state.device, o)
+        self.comp_graph = cg
+        self.probed = True
+        return out
+
+    def _compile(self, optimizer) -> None:
+        """Plan, partition and distribute (pfeife/mp/partial/module.py:290-371)."""
+        r = self.runner
+        opt, state = r.option, r.state
+        pp = state.pp_size
+        opt_pp = copy.copy(opt)
+        opt_pp.device_cnt = pp
+        if pp == 1:
+            opt_pp.loop_cnt = 1
+        max_mem = None
+        if state.device.type == "cuda":
+            total = torch.cuda.get_device_properties(state.device).total_memory
+            max_mem = [float(total)] * pp
+        gen = get_pipe_class(opt.partitioner)(self.comp_graph, r.device_bench, opt_pp)
+        plan = gen.gen_graph(opt.batch_cnt, max_mem, opt.split_points)
+        self.plan = plan
+        part = partition_module(self.comp_graph, plan.split_points, pp)
+        self.part = part
+        sched_cls = get_scheduler_class(opt.scheduler)
+        sched = sched_cls(plan.sched, plan.dep_graph)
+        steps = sched.steps
+        eval_steps = [sched.get_eval_steps(i) for i in range(pp)]
+
+        # parameter entries per rank, with the user's optimizer group of every parameter
+        group_of: Dict[int, int] = {}
+        if optimizer is not None:
+            for gi, g in enumerate(optimizer.param_groups):
+                for p in g["params"]:
+                    group_of[id(p)] = gi
+        hyper = snapshot_hyper(optimizer) if optimizer is not None else \
+            [dict(opt.optimizer_kwargs)]
+        opt_type = type(optimizer).__name__ if optimizer is not None else opt.optimizer_type
+        payloads = []
+        for rank in range(pp):
+            entries = []
+            for ph in part.rank_states(rank):
+                gi = self.captured.inputs[ph]
+                t = gi.tensor
+                entries.append(StateEntry(ph, gi.qualname, gi.kind,
+                                          t.detach() if rank == state.pp_rank else t.detach().cpu(),
+                                          bool(gi.kind == "param" and t.requires_grad),
+                                          group_of.get(id(t), 0)))
+            payloads.append({"part": part.for_rank(rank), "entries": entries,
+                             "optimizer_type": opt_type, "hyper": hyper, "steps": steps,
+                             "eval_steps": eval_steps, "batch_cnt": opt.batch_cnt})
+        mine = r.ctrl.scatter(payloads)
+        _install_plan(r.worker, state, mine)
+        r.ctrl.barrier()
+        self.compiled = True
+        # the user's module keeps its Parameter objects; they are refreshed by gather_params()
+        for gi in self.captured.params:
+            gi.tensor.grad = None
+
+    def forward(self, *args):
+        r = self.runner
+        if r is None or not self.should_pp:
+            return self.gm(*args)
+        if not self.probed:
+            return self._probe_forward(args)
+        if not self.compiled:      # probe call of a later graph while the first is compiling
+            return self.gm(*args)
+        return self._wait_for_execution(args)
+
+    def _wait_for_execution(self, args: Sequence[Any]) -> Any:
+        r = self.runner
+        mb = getattr(_tls, "mb", None)
+        if mb is None:
+            raise RuntimeError("the compiled model must be called from exec_fn inside "
+                               "PartialRunner.step()")
+        values = {gi.index: args[gi.index] for gi in self.captured.user_inputs}
+        r.worker.submit_inputs(mb, values)
+        r._return_queues[mb].put(STEP_TOKEN)           # "my inputs are in"
+        outs = r._module_queues[mb].get()              # blocks until the last stage ran
+        if isinstance(outs, BaseException):
+            raise outs
+        return self.part.assemble_output(outs, args)
+
+
+def partial_compiler(gm: torch.fx.GraphModule, example_inputs: Sequence[Any]) -> PartialModule:
+    """``torch.compile(model, backend=partial_compiler)``."""
+    return PartialModule(gm, example_inputs)
+
+
+# ------------------------------------------------------------------------------ PartialRunner
+class PartialRunner:
+    def __init__(self, option: PipeOption, optimizer=None):
+        global _current_runner
+        self.option = option
+        self.optimizer = optimizer
+        self.state = get_state()
+        if not self.state.is_main_rank:
+            raise RuntimeError("PartialRunner belongs to the main rank of a pipeline; other "
+                               "ranks call worker_loop() (mp_launch.py does)")
+        self.log = get_logger()
+        self.ctrl = ControlPlane(self.state)
+        self.modules: List[PartialModule] = []
+        self.exec_fn: Optional[Callable] = None
+        self.batch_cnt = option.batch_cnt
+        _current_runner = self
+        self.ctrl.bcast(option)
+        self.worker = _make_worker(self.state, option, runner=self)
+        self.device_bench = _run_device_bench(self.state, option)
+        self._train_queues = [queue.Queue() for _ in range(self.batch_cnt)]
+        self._return_queues = [queue.Queue() for _ in range(self.batch_cnt)]
+        self._module_queues = [queue.Queue() for _ in range(self.batch_cnt)]
+        self._threads = []
+        for bid in range(self.batch_cnt):
+            t = threading.Thread(target=self._exec_loop, args=(bid,), daemon=True)
+            t.start()
+            self._threads.append(t)
+        self._closed = False
+        self._compiled = False
+        atexit.register(self.close)
+
+    # ---- user API
+    def set_exec_fn(self, fn: Callable) -> None:
+        self.exec_fn = fn
+
+    @property
+    def scaler(self):
+        """The job-wide loss scaler: ``runner.scaler.scale(loss).backward()`` under fp16."""
+        return self.worker.scaler
+
+    def step(self, *args, **kwargs) -> List[Any]:
+        if self.exec_fn is None:
+            raise RuntimeError("call set_exec_fn() before step()")
+        a_split, k_split = split_args_kwargs(args, kwargs, self.batch_cnt)
+        if not self._compiled:
+            self._probe_forward(a_split[0], k_split[0])
+            pipelined = [m for m in self.modules if m.should_pp and m.probed]
+            if not pipelined:
+                raise RuntimeError("no captured graph is eligible for pipelining: the model "
+                                   "call must happen inside exec_fn and the graph needs at "
+                                   f"least {2 * self.state.pp_size} compute nodes")
+            for m in pipelined:
+                m._compile(self.optimizer)
+            self._compiled = True
+        return self._run(a_split, k_split, training=True)
+
+    def eval_step(self, *args, **kwargs) -> List[Any]:
+        """Forward-only pass through the pipeline; exec_fn must not call backward."""
+        a_split, k_split = split_args_kwargs(args, kwargs, self.batch_cnt)
+        if not self._compiled:
+            raise RuntimeError("run one training step before eval_step()")
+        return self._run(a_split, k_split, training=False)
+
+    def _run(self, a_split, k_split, training: bool) -> List[Any]:
+        self.reset(training)
+        self._training = training
+        for bid in range(self.batch_cnt):
+            self._train_queues[bid].put((a_split[bid], k_split[bid]))
+        for bid in range(self.batch_cnt):      # every thread reached the model call
+            tok = self._return_queues[bid].get(timeout=self.option.ctrl_timeout)
+            if tok is not STEP_TOKEN:
+                self._abort(tok)
+        try:
+            self.worker.run(training)
+        except BaseException as e:
+            for q in self._module_queues:
+                q.put(e)
+            raise
+        results = []
+        for bid in range(self.batch_cnt):
+            res = self._return_queues[bid].get(timeout=self.option.ctrl_timeout)
+            if isinstance(res, BaseException):
+                raise res
+            results.append(res)
+        return results
+
+    def _abort(self, tok):
+        if isinstance(tok, BaseException):
+            raise tok
+        raise RuntimeError("exec_fn returned without calling the compiled model")
+
+    def reset(self, training: bool = True) -> None:
+        self.worker.reset_cache()
+        msg = {"flag": LoopFlag.CONTINUE_LOOP if training else LoopFlag.EVAL_LOOP}
+        if self.optimizer is not None:
+            msg["hyper"] = snapshot_hyper(self.optimizer)
+            self.worker.params.set_hyper(msg["hyper"])
+        self.ctrl.bcast(msg)
+
+    # ---- outputs and loss gradients (called from the worker / the batch threads)
+    def return_output(self, mb: int, stage: int, sink: List[Tuple[int, torch.Tensor]]) -> None:
+        outs: Dict[Tuple[int, int], Any] = {}
+        training = getattr(self, "_training", True)
+        for j, t in sink:
+            if torch.is_tensor(t):
+                leaf = t.detach()
+                if training and t.requires_grad and leaf.dtype.is_floating_point:
+                    leaf.requires_grad_(True)
+                    leaf.register_hook(self._make_hook(mb, j))
+                outs[(stage, j)] = leaf
+            else:
+                outs[(stage, j)] = t
+        self._module_queues[mb].put(outs)
+
+    def _make_hook(self, mb: int, j: int):
+        def hook(grad):
+            self.worker.recv_loss_grad(mb, j, grad)
+            return grad
+        return hook
+
+    def finalize_output(self, mb: int) -> None:
+        self.worker.loss_backward_done(mb)
+
+    # ---- threads
+    def _exec_loop(self, bid: int) -> None:
+        _tls.mb = bid
+        while True:
+            item = self._train_queues[bid].get()
+            if item is None:
+                return
+            a, k = item
+            try:
+                res = self.exec_fn(*a, **k)
+            except BaseException as e:   # surfaced by step()
+                self._return_queues[bid].put(e)
+                self.finalize_output(bid)
+                continue
+            self.finalize_output(bid)
+            self._return_queues[bid].put(res)
+
+    def _probe_forward(self, a, k) -> Any:
+        _tls.mb = None
+        res = self.exec_fn(*a, **k)
+        return res
+
+    # ---- checkpoint
+    def gather_params(self, with_optimizer: bool = False):
+        """Copies every rank's current parameters back into the user's module (so that
+        ``model.state_dict()`` is a plain checkpoint of the original module,
+        pfeife/mp/partial/module.py:115-117) and, optionally, returns the optimizer state keyed
+        by the original parameter names."""
+        self.ctrl.bcast({"flag": LoopFlag.GATHER_PARAMS, "opt": with_optimizer})
+        named = {k: v for k, v in self.worker.params.named_tensors().items()}
+        opt = self.worker.params.optimizer_state() if with_optimizer else {}
+        gathered = self.ctrl.gather((named, opt)) if self.state.pp_size > 1 else [(named, opt)]
+        all_named: Dict[str, torch.Tensor] = {}
+        all_opt: Dict[str, Dict[str, torch.Tensor]] = {}
+        for item in gathered:
+            if item is None:
+                continue
+            all_named.update(item[0])
+            all_opt.update(item[1])
+        all_named.update(named)
+        all_opt.update(opt)
+        with torch.no_grad():
+            for m in self.modules:
+                if not m.should_pp:
+                    continue
+                for gi in m.captured.inputs:
+                    if gi.is_state and gi.qualname in all_named:
+                        gi.tensor.copy_(all_named[gi.qualname].to(gi.tensor.device))
+        return all_opt if with_optimizer else None
+
+    def load_params(self, named: Dict[str, torch.Tensor],
+                    opt: Optional[Dict[str, Dict[str, torch.Tensor]]] = None) -> None:
+        """Resume: pushes a ``state_dict`` of the original module (and optimizer state) to the
+        ranks that own each parameter."""
+        named = {k: v.detach().cpu() for k, v in named.items()}
+        self.ctrl.bcast({"flag": LoopFlag.LOAD_PARAMS, "named": named, "opt": opt})
+        self.worker.params.load_named(named)
+        if opt:
+            self.worker.params.load_optimizer_state(opt)
+
+    def log_memory_usage(self) -> None:
+        self.ctrl.bcast({"flag": LoopFlag.LOG_MEMORY_USAGE})
+        self.worker.log_memory_usage()
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            self.worker.reset_cache()
+            self.ctrl.bcast({"flag": LoopFlag.STOP_LOOP})
+        except Exception:
+            pass
+        for q in self._train_queues:
+            q.put(None)

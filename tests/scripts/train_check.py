@@ -1,0 +1,122 @@
+"""Training-equality check driven through the public API (run by the tests under
+``mp_launch.py``): trains a model for a few steps through the pipeline and through a plain
+single-process loop with the same optimizer, and writes losses and the largest parameter
+difference to ``--out`` as JSON (only the global main process writes)."""
+import argparse
+import copy
+import json
+import os
+import sys
+
+import torch
+import torch.nn.functional as F
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from pfeife_b200 import PartialRunner, PipeOption, initialize_pfeife, partial_compiler  # noqa
+from pfeife_b200.models.toy import DeepMLP, SkipNet, TiedMLP  # noqa
+from pfeife_b200.models.vit import ViT, vit_config  # noqa
+from pfeife_b200.utils import set_seed  # noqa
+
+
+def build(name):
+    if name == "mlp":
+        return DeepMLP(16, 8, 10), (lambda n: torch.randn(n, 16)), 10
+    if name == "tied":
+        return TiedMLP(10, 3), (lambda n: torch.randn(n, 10)), 10
+    if name == "skip":
+        return SkipNet(16, 3), (lambda n: torch.randn(n, 16)), 16
+    if name == "vit_tiny":
+        cfg = vit_config("vit_tiny")
+        return ViT(cfg), (lambda n: torch.randn(n, 3, 224, 224)), 10
+    if name == "vit_small":
+        cfg = vit_config("vit_tiny", num_layers=4, image_size=32, patch_size=8)
+        return ViT(cfg), (lambda n: torch.randn(n, 3, 32, 32)), 10
+    raise ValueError(name)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="mlp")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--optimizer", default="sgd")
+    ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--check_eval", action="store_true")
+    ap.add_argument("--resume_check", action="store_true")
+    PipeOption.add_arguments(ap)
+    args = ap.parse_args()
+
+    state = initialize_pfeife()
+    option = PipeOption.from_args(args)
+    set_seed(0)
+    model, make_x, n_cls = build(args.model)
+    ref = copy.deepcopy(model)
+    dev = state.device
+    model.to(dev)
+    mk = lambda m: (torch.optim.SGD(m.parameters(), lr=args.lr) if args.optimizer == "sgd" else
+                    torch.optim.AdamW(m.parameters(), lr=args.lr, weight_decay=0.01)
+                    if args.optimizer == "adamw" else torch.optim.Adam(m.parameters(), lr=args.lr))
+    opt, ropt = mk(model), mk(ref)
+    sched = torch.optim.lr_scheduler.StepLR(opt, 1, gamma=0.5)
+    rsched = torch.optim.lr_scheduler.StepLR(ropt, 1, gamma=0.5)
+
+    runner = PartialRunner(option, opt)
+    cm = torch.compile(model, backend=partial_compiler)
+
+    def exec_fn(x, y):
+        loss = F.cross_entropy(cm(x).float(), y)
+        loss.backward()
+        return loss.detach().cpu()
+
+    runner.set_exec_fn(exec_fn)
+    n = option.batch_size * option.batch_cnt
+    g = torch.Generator().manual_seed(100 + state.dp_rank)
+    losses, ref_losses = [], []
+    for step in range(args.steps):
+        x = torch.randn(make_x(n).shape, generator=g)
+        y = torch.randint(0, n_cls, (n,), generator=g)
+        out = runner.step(x.to(dev), y.to(dev))
+        losses.append([float(l) for l in out])
+        sched.step()
+        if state.dp_size == 1:
+            ropt.zero_grad()
+            cur = []
+            for xs, ys in zip(x.chunk(option.batch_cnt), y.chunk(option.batch_cnt)):
+                l = F.cross_entropy(ref(xs), ys)
+                l.backward()
+                cur.append(float(l))
+            ropt.step()
+            rsched.step()
+            ref_losses.append(cur)
+    result = {"losses": losses, "ref_losses": ref_losses}
+    if args.check_eval:
+        x = make_x(n)
+        runner.set_exec_fn(lambda x: cm(x).detach().cpu())
+        got = runner.eval_step(x.to(dev))
+        runner.gather_params()
+        with torch.no_grad():
+            want = model.cpu()(x)
+        result["eval_diff"] = float((torch.cat(got) - want).abs().max())
+        model.to(dev)
+    opt_state = runner.gather_params(with_optimizer=True)
+    diff = 0.0
+    if state.dp_size == 1:
+        for (k, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+            diff = max(diff, float((p.detach().cpu() - q.detach()).abs().max()))
+    result["param_diff"] = diff
+    result["opt_state_keys"] = sorted(opt_state.keys())[:3] if opt_state else []
+    result["state_dict_keys"] = len(model.state_dict())
+    if state.dp_size > 1:
+        # replicas must hold identical parameters after training
+        flat = torch.cat([p.detach().cpu().reshape(-1) for p in model.parameters()])
+        result["param_checksum"] = float(flat.double().sum())
+    if state.is_main_process or state.dp_size > 1:
+        path = args.out if state.is_main_process else f"{args.out}.dp{state.dp_rank}"
+        with open(path, "w") as f:
+            json.dump(result, f)
+    runner.close()
+
+
+if __name__ == "__main__":
+    main()
