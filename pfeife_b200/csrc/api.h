@@ -79,3 +79,14 @@ PF_DECL int pf_embed_bwd(const void* dout, const void* ids, void* dtable_f32, lo
 PF_DECL int pf_rope(const void* x, void* out, const void* cos_t, const void* sin_t, long long B,
                     int S, int H, int D, long long stride_b, long long stride_s,
                     long long stride_h, int inverse, int dtype, int sm_count, void* stream);
+
+// ---- attn_sm100.cu : flash attention on tcgen05 (strides in elements: batch, seq, head)
+PF_DECL int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse, int B,
+                        int H, int Sq, int Sk, int D, const long long* sq, const long long* sk,
+                        const long long* sv, int causal, float scale, int dtype, int* status,
+                        void* stream);
+PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                        const void* out, const void* lse, void* delta, void* dq_accum, void* dq,
+                        void* dk, void* dv, int B, int H, int Sq, int Sk, int D,
+                        const long long* sq, const long long* sk, const long long* sv, int causal,
+                        float scale, int dtype, int* status, int sm_count, void* stream);

@@ -1,0 +1,676 @@
+// Flash attention for sm_100a, forward and backward, on tcgen05 tensor cores.
+//
+// Layout: q [B, Sq, H, D], k/v [B, Sk, H, D] with arbitrary (16-byte aligned) batch / sequence /
+// head strides and a unit inner stride, so the three slices of a fused QKV projection are
+// consumed in place through 4-D TMA tensor maps.  Head dims up to 128, any multiple of 8
+// (88 for ViT-g/14 runs as 96 with zero-filled tails: the tensor map's inner extent is D, so
+// the tail of the last 64-element block is filled with zeros by TMA, never with the next head).
+//
+// Forward, one CTA (128 threads, thread t <-> query row t <-> TMEM lane t) per (q tile of 128,
+// head, batch), looping over 128-row K/V tiles:
+//     S = Q K^T            tcgen05.mma, smem x smem -> TMEM
+//     online softmax       tcgen05.ld S -> registers (base-2 exponent, running max / sum)
+//     P -> smem            16-bit, written in the 128B-swizzled K-major layout the MMA reads
+//     O_tile = P V         tcgen05.mma, V used in place as an MN-major operand -> TMEM
+//     O = alpha O + O_tile in registers
+// The score matrix never exists in global memory.  Two CTAs fit per SM for D <= 96, which is
+// what overlaps one CTA's softmax with the other's MMAs.
+//
+// Backward, one CTA per (k/v tile of 128, head, batch), looping over q tiles, five MMAs per
+// tile pair with S/P and dP/dS in TMEM / smem and dK, dV accumulated in TMEM:
+//     S = Q K^T ; P = exp2(S*c - lse2) ; dP = dO V^T ; dS = P * (dP - delta) * scale
+//     dV += P^T dO ; dK += dS^T Q ; dQ_tile = dS K  -> fp32 atomics into dq_accum
+// delta = rowsum(dO * O) comes from a small pre-pass; dq_accum is converted by a post-pass.
+#include "common.cuh"
+#include "api.h"
+
+namespace pf {
+
+constexpr int ATT_BM = 128;   // query rows per tile
+constexpr int ATT_BN = 128;   // key rows per tile
+constexpr int ATT_BLK = 16384;  // bytes of one [128 rows x 64 x 16-bit] swizzled block
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+struct AttnParams {
+  int B, H, Sq, Sk, D;
+  int causal;
+  float scale;
+  int fmt;  // 0 fp16, 1 bf16
+  void* o;              // fwd: out [B,Sq,H,D] contiguous
+  float* lse;           // [B,H,Sq]
+  // backward
+  const float* delta;   // [B,H,Sq]
+  float* dq_accum;      // [B,Sq,H,D] fp32, zeroed
+  void* dk;             // [B,Sk,H,D] contiguous
+  void* dv;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Writes 32 consecutive 16-bit values of row `r`, columns [c0, c0+32), into a [128 x 128]
+// K-major tile made of two swizzled [128 x 64] blocks.
+template <typename T>
+__device__ __forceinline__ void store_p_chunk(uint8_t* tile, int r, int c0, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = c0 + j * 8;
+    const int blk = c >> 6;
+    const int chunk = (c & 63) >> 3;
+    uint4 q;
+    q.x = pack2<T>(v[j * 8 + 0], v[j * 8 + 1]);
+    q.y = pack2<T>(v[j * 8 + 2], v[j * 8 + 3]);
+    q.z = pack2<T>(v[j * 8 + 4], v[j * 8 + 5]);
+    q.w = pack2<T>(v[j * 8 + 6], v[j * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + blk * ATT_BLK + r * 128 + ((chunk ^ (r & 7)) << 4)) = q;
+  }
+}
+
+// one [128 rows x DP] tile = DP/64 (rounded up) swizzled blocks, loaded with one TMA per block
+template <int NBLK>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
+                                          int h, int s0, int b) {
+  mbar_expect_tx(bar, NBLK * ATT_BLK);
+#pragma unroll
+  for (int i = 0; i < NBLK; ++i) tma_load_4d(dst + i * ATT_BLK, map, bar, i * 64, h, s0, b);
+}
+
+// A[128 x K] (K-major blocks) . B[N x K]^T (K-major blocks), K = KSTEPS * 16
+template <int KSTEPS>
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc,
+                                       bool accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    const uint32_t off = (k >> 2) * ATT_BLK + (k & 3) * 32;
+    tc_mma_f16(d_tmem, make_desc_sw128(sa + off, 16, 1024), make_desc_sw128(sb + off, 16, 1024),
+               idesc, (k > 0) || accumulate_first);
+  }
+}
+// A[128 x 128] K-major . B given as [K=128 rows][N] (N contiguous, MN-major blocks of 64)
+__device__ __forceinline__ void mma_k_mn(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc,
+                                         bool accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t aoff = (k >> 2) * ATT_BLK + (k & 3) * 32;
+    tc_mma_f16(d_tmem, make_desc_sw128(sa + aoff, 16, 1024),
+               make_desc_sw128(sb + k * 2048, ATT_BLK, 1024), idesc, (k > 0) || accumulate_first);
+  }
+}
+// A given as [K=128 rows][M=128] (M contiguous) . B given as [K=128 rows][N] (N contiguous)
+__device__ __forceinline__ void mma_mn_mn(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc,
+                                          bool accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    tc_mma_f16(d_tmem, make_desc_sw128(sa + k * 2048, ATT_BLK, 1024),
+               make_desc_sw128(sb + k * 2048, ATT_BLK, 1024), idesc, (k > 0) || accumulate_first);
+  }
+}
+
+// ================================================================================ forward
+template <typename T, int DP>
+__global__ void __launch_bounds__(128)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const AttnParams p) {
+  constexpr int NBLK = (DP + 63) / 64;
+  constexpr int TILE = NBLK * ATT_BLK;
+  constexpr uint32_t TMEM_COLS = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sP = sV + TILE;                         // 2 blocks
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATT_BLK);
+  uint64_t* bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3,
+          *bar_o = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int q0 = blockIdx.x * ATT_BM, h = blockIdx.y, b = blockIdx.z;
+
+  if (tid == 0) {
+    tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem, t_o = tmem + 128;
+  const uint32_t lane_off = uint32_t(warp * 32) << 16;
+
+  const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
+  const uint32_t idesc_o = make_idesc_f16(128, DP, p.fmt, 0, 1);
+  const float c2 = p.scale * LOG2E;
+
+  int kv_end = p.Sk;
+  const int shift = p.Sk - p.Sq;   // causal: key j visible to query i iff j <= i + shift
+  if (p.causal) kv_end = min(p.Sk, q0 + ATT_BM + shift);
+  const int n_tiles = (kv_end + ATT_BN - 1) / ATT_BN;
+
+  if (tid == 0) load_tile<NBLK>(sQ, &tq, bar_q, h, q0, b);
+
+  float o[DP];
+#pragma unroll
+  for (int i = 0; i < DP; ++i) o[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const int qi = q0 + tid;
+  bool ok = true;
+  uint32_t ph = 0;
+
+  for (int j = 0; j < n_tiles && ok; ++j) {
+    const int k0 = j * ATT_BN;
+    if (tid == 0) {
+      load_tile<NBLK>(sK, &tk, bar_k, h, k0, b);
+      load_tile<NBLK>(sV, &tv, bar_v, h, k0, b);
+      if (j == 0) ok = mbar_wait(bar_q, 0, p.status, PF_ERR_TIMEOUT_FULL);
+      ok = ok && mbar_wait(bar_k, ph, p.status, PF_ERR_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_s, false);
+        tc_commit(bar_s);
+      }
+    }
+    __syncwarp();
+    ok = mbar_wait(bar_s, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+    if (!ok) break;
+    tc_fence_after();
+    // ---- softmax over this tile's 128 scores of row `tid` (two passes over TMEM: the row
+    //      maximum first, then exponentials; only 32 scores are live in registers at a time)
+    float mx = m;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t raw[32];
+      tmem_ld32(t_s + lane_off + c * 32, raw);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int kj = k0 + c * 32 + i;
+        const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
+        if (vis) mx = fmaxf(mx, __uint_as_float(raw[i]) * c2);
+      }
+    }
+    const float m_use = (mx == -INFINITY) ? 0.f : mx;
+    const float alpha = exp2f(m - m_use);     // m = -inf -> 0
+    float rs = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t raw[32];
+      tmem_ld32(t_s + lane_off + c * 32, raw);
+      tmem_ld_wait();
+      float pv[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int kj = k0 + c * 32 + i;
+        const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
+        pv[i] = vis ? exp2f(__uint_as_float(raw[i]) * c2 - m_use) : 0.f;
+        rs += pv[i];
+      }
+      store_p_chunk<T>(sP, tid, c * 32, pv);
+    }
+    l = l * alpha + rs;
+    m = mx;
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      ok = mbar_wait(bar_v, ph, p.status, PF_ERR_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        mma_k_mn(t_o, smem_u32(sP), smem_u32(sV), idesc_o, false);
+        tc_commit(bar_o);
+      }
+    }
+    __syncwarp();
+    ok = mbar_wait(bar_o, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+    if (!ok) break;
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < DP / 32; ++c) {
+      uint32_t raw[32];
+      tmem_ld32(t_o + lane_off + c * 32, raw);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(raw[i]);
+    }
+    ph ^= 1;
+    tc_fence_before();
+    __syncthreads();   // everyone is done with S, O_tile, sK, sV, sP before the next tile
+  }
+
+  if (ok && qi < p.Sq) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* dst = reinterpret_cast<T*>(p.o) + (((long long)b * p.Sq + qi) * p.H + h) * p.D;
+#pragma unroll
+    for (int c = 0; c < DP / 8; ++c) {
+      if (c * 8 < p.D) {
+        uint4 q;
+        q.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
+        q.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        q.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
+        q.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        reinterpret_cast<uint4*>(dst)[c] = q;
+      }
+    }
+    p.lse[((long long)b * p.H + h) * p.Sq + qi] = (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// ================================================================================ backward
+// delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* __restrict__ delta,
+                  int B, int S, int H, int D) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);   // over B*S*H
+  if (row >= (long long)B * S * H) return;
+  const int lane = threadIdx.x & 31;
+  const T* a = dout + row * D;
+  const T* c = out + row * D;
+  float s = 0.f;
+  for (int i = lane; i < D; i += 32) s += to_f32<T>(a[i]) * to_f32<T>(c[i]);
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int h = (int)(row % H);
+    const long long bs = row / H;
+    const int i = (int)(bs % S);
+    const long long b = bs / S;
+    delta[(b * H + h) * S + i] = s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dq[i] = from_f32<T>(acc[i]);
+}
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(128)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                const AttnParams p) {
+  constexpr int NBLK = (DP + 63) / 64;
+  constexpr int TILE = NBLK * ATT_BLK;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;
+  uint8_t* sdO = sQ + TILE;
+  uint8_t* sP = sdO + TILE;                  // [q][kv] 16-bit, 2 blocks
+  uint8_t* sdS = sP + 2 * ATT_BLK;           // [q][kv] 16-bit, 2 blocks
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * ATT_BLK);
+  uint64_t* bar_kv = bars, *bar_q = bars + 1, *bar_mma1 = bars + 2, *bar_mma2 = bars + 3,
+          *bar_dq = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int k0 = blockIdx.x * ATT_BN, h = blockIdx.y, b = blockIdx.z;
+
+  if (tid == 0) {
+    tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&tdo);
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
+  const uint32_t lane_off = uint32_t(warp * 32) << 16;
+
+  const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);     // Q K^T and dO V^T
+  const uint32_t idesc_kd = make_idesc_f16(128, DP, p.fmt, 1, 1);     // P^T dO, dS^T Q
+  const uint32_t idesc_dq = make_idesc_f16(128, DP, p.fmt, 0, 1);     // dS K
+  const float c2 = p.scale * LOG2E;
+  const int shift = p.Sk - p.Sq;
+
+  int q_begin = 0;
+  if (p.causal) q_begin = max(0, k0 - shift) / ATT_BM * ATT_BM;   // first q tile that sees k0
+  const int n_q = (p.Sq + ATT_BM - 1) / ATT_BM;
+
+  if (tid == 0) {
+    mbar_expect_tx(bar_kv, 2 * TILE);
+#pragma unroll
+    for (int i = 0; i < NBLK; ++i) {
+      tma_load_4d(sK + i * ATT_BLK, &tk, bar_kv, i * 64, h, k0, b);
+      tma_load_4d(sV + i * ATT_BLK, &tv, bar_kv, i * 64, h, k0, b);
+    }
+  }
+  bool ok = true;
+  uint32_t ph = 0;
+  bool first = true;
+  for (int qt = q_begin / ATT_BM; qt < n_q && ok; ++qt) {
+    const int q0 = qt * ATT_BM;
+    const int qi = q0 + tid;
+    if (tid == 0) {
+      mbar_expect_tx(bar_q, 2 * TILE);
+#pragma unroll
+      for (int i = 0; i < NBLK; ++i) {
+        tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0, b);
+        tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0, b);
+      }
+      if (first) ok = mbar_wait(bar_kv, 0, p.status, PF_ERR_TIMEOUT_FULL);
+      ok = ok && mbar_wait(bar_q, ph, p.status, PF_ERR_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_s, false);    // S  = Q K^T
+        mma_kk<DP / 16>(t_dp, smem_u32(sdO), smem_u32(sV), idesc_s, false);  // dP = dO V^T
+        tc_commit(bar_mma1);
+      }
+    }
+    __syncwarp();
+    ok = mbar_wait(bar_mma1, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+    if (!ok) break;
+    tc_fence_after();
+    const bool row_ok = qi < p.Sq;
+    const float lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * LOG2E : 0.f;
+    const float dl = row_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rs[32], rp[32];
+      tmem_ld32(t_s + lane_off + c * 32, rs);
+      tmem_ld32(t_dp + lane_off + c * 32, rp);
+      tmem_ld_wait();
+      float pv[32], ds[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int kj = k0 + c * 32 + i;
+        const bool vis = row_ok && kj < p.Sk && !(p.causal && kj > qi + shift);
+        const float pr = vis ? exp2f(__uint_as_float(rs[i]) * c2 - lse2) : 0.f;
+        pv[i] = pr;
+        ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
+      }
+      store_p_chunk<T>(sP, tid, c * 32, pv);
+      store_p_chunk<T>(sdS, tid, c * 32, ds);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      // sP / sdS hold [q rows][kv cols]: as A operands of the two products below they are
+      // MN-major (M = kv contiguous within a row, K = q across rows)
+      mma_mn_mn(t_dv, smem_u32(sP), smem_u32(sdO), idesc_kd, !first);   // dV += P^T dO
+      mma_mn_mn(t_dk, smem_u32(sdS), smem_u32(sQ), idesc_kd, !first);   // dK += dS^T Q
+      tc_commit(bar_mma2);
+      mma_k_mn(t_s, smem_u32(sdS), smem_u32(sK), idesc_dq, false);      // dQ_tile = dS K
+      tc_commit(bar_dq);
+    }
+    __syncwarp();
+    ok = mbar_wait(bar_dq, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+    if (!ok) break;
+    tc_fence_after();
+    {
+      // the TMEM loads are warp-collective: every lane executes them, only valid rows add
+      float* dst = p.dq_accum + (((long long)b * p.Sq + (row_ok ? qi : 0)) * p.H + h) * p.D;
+#pragma unroll
+      for (int c = 0; c < DP / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld32(t_s + lane_off + c * 32, raw);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < p.D) atomicAdd(dst + c * 32 + i, __uint_as_float(raw[i]));
+        }
+      }
+    }
+    ok = mbar_wait(bar_mma2, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+    if (!ok) break;
+    ph ^= 1;
+    first = false;
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  // epilogue: dK, dV rows of this tile
+  if (ok && !first) {
+    tc_fence_after();
+    const int kj = k0 + tid;
+    T* dkp = reinterpret_cast<T*>(p.dk) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+    T* dvp = reinterpret_cast<T*>(p.dv) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+#pragma unroll
+    for (int c = 0; c < DP / 32; ++c) {
+      uint32_t rk[32], rv[32];
+      tmem_ld32(t_dk + lane_off + c * 32, rk);
+      tmem_ld32(t_dv + lane_off + c * 32, rv);
+      tmem_ld_wait();
+      if (kj < p.Sk) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int d0 = c * 32 + g * 8;
+          if (d0 < p.D) {
+            uint4 a, bq;
+            a.x = pack2<T>(__uint_as_float(rk[g * 8 + 0]), __uint_as_float(rk[g * 8 + 1]));
+            a.y = pack2<T>(__uint_as_float(rk[g * 8 + 2]), __uint_as_float(rk[g * 8 + 3]));
+            a.z = pack2<T>(__uint_as_float(rk[g * 8 + 4]), __uint_as_float(rk[g * 8 + 5]));
+            a.w = pack2<T>(__uint_as_float(rk[g * 8 + 6]), __uint_as_float(rk[g * 8 + 7]));
+            bq.x = pack2<T>(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
+            bq.y = pack2<T>(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
+            bq.z = pack2<T>(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
+            bq.w = pack2<T>(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dkp + d0) = a;
+            *reinterpret_cast<uint4*>(dvp + d0) = bq;
+          }
+        }
+      }
+    }
+  } else if (ok && first) {
+    // no query tile sees this key tile (causal with Sk > Sq + ...): gradients are zero
+    const int kj = k0 + tid;
+    if (kj < p.Sk) {
+      T* dkp = reinterpret_cast<T*>(p.dk) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+      T* dvp = reinterpret_cast<T*>(p.dv) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+      for (int d = 0; d < p.D; ++d) { dkp[d] = from_f32<T>(0.f); dvp[d] = from_f32<T>(0.f); }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn attn_get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [B, S, H, D] view with element strides (sb, ss, sh, 1); box = 64 x 1 x 128 x 1
+static int make_tmap_bshd(CUtensorMap* map, const void* base, int fmt, int B, int S, int H, int D,
+                          long long sb, long long ss, long long sh) {
+  EncodeTiledFn enc = attn_get_encode();
+  if (!enc) return -100;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
+}
+
+// `done` must be a distinct array per kernel instantiation (kernels of equal signature share
+// one function-pointer type), so the callers own it.
+template <typename K>
+static int set_smem(K kern, int bytes, bool* done) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) done[dev] = true;
+  }
+  return 0;
+}
+
+template <typename T, int DP>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const AttnParams& p, cudaStream_t st) {
+  constexpr int NBLK = (DP + 63) / 64;
+  constexpr int SMEM = 3 * NBLK * ATT_BLK + 2 * ATT_BLK + 128 + 1024;
+  auto kern = attn_fwd_kernel<T, DP>;
+  static bool done[64] = {};
+  int r = set_smem(kern, SMEM, done);
+  if (r) return r;
+  dim3 grid((p.Sq + ATT_BM - 1) / ATT_BM, p.H, p.B);
+  kern<<<grid, 128, SMEM, st>>>(tq, tk, tv, p);
+  PF_CHECK_LAUNCH();
+  return 0;
+}
+
+template <typename T, int DP>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const CUtensorMap& tdo, const AttnParams& p, cudaStream_t st) {
+  constexpr int NBLK = (DP + 63) / 64;
+  constexpr int SMEM = 4 * NBLK * ATT_BLK + 4 * ATT_BLK + 128 + 1024;
+  auto kern = attn_bwd_kernel<T, DP>;
+  static bool done[64] = {};
+  int r = set_smem(kern, SMEM, done);
+  if (r) return r;
+  dim3 grid((p.Sk + ATT_BN - 1) / ATT_BN, p.H, p.B);
+  kern<<<grid, 128, SMEM, st>>>(tq, tk, tv, tdo, p);
+  PF_CHECK_LAUNCH();
+  return 0;
+}
+
+static bool strides_ok(const void* ptr, long long sb, long long ss, long long sh) {
+  return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && sb % 8 == 0 && ss % 8 == 0 && sh % 8 == 0;
+}
+
+}  // namespace pf
+
+using namespace pf;
+
+#define PF_ATTN_DISPATCH(FN, ...)                                              \
+  do {                                                                         \
+    const int DP = (D + 31) / 32 * 32;                                         \
+    if (dtype == PF_F16) {                                                     \
+      switch (DP) {                                                            \
+        case 32: return FN<__half, 32>(__VA_ARGS__);                            \
+        case 64: return FN<__half, 64>(__VA_ARGS__);                            \
+        case 96: return FN<__half, 96>(__VA_ARGS__);                            \
+        case 128: return FN<__half, 128>(__VA_ARGS__);                          \
+      }                                                                        \
+    } else {                                                                   \
+      switch (DP) {                                                            \
+        case 32: return FN<__nv_bfloat16, 32>(__VA_ARGS__);                     \
+        case 64: return FN<__nv_bfloat16, 64>(__VA_ARGS__);                     \
+        case 96: return FN<__nv_bfloat16, 96>(__VA_ARGS__);                     \
+        case 128: return FN<__nv_bfloat16, 128>(__VA_ARGS__);                   \
+      }                                                                        \
+    }                                                                          \
+    return -3;                                                                 \
+  } while (0)
+
+// strides are in elements, order (batch, seq, head) for each of q, k, v
+PF_API int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse, int B,
+                       int H, int Sq, int Sk, int D, const long long* sq, const long long* sk,
+                       const long long* sv, int causal, float scale, int dtype, int* status,
+                       void* stream) {
+  if (dtype != PF_F16 && dtype != PF_BF16) return -1;
+  if (D % 8 || D > 128) return -3;
+  if (!strides_ok(q, sq[0], sq[1], sq[2]) || !strides_ok(k, sk[0], sk[1], sk[2]) ||
+      !strides_ok(v, sv[0], sv[1], sv[2]))
+    return -2;
+  const int fmt = dtype == PF_BF16;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_tmap_bshd(&tq, q, fmt, B, Sq, H, D, sq[0], sq[1], sq[2]))) return r;
+  if ((r = make_tmap_bshd(&tk, k, fmt, B, Sk, H, D, sk[0], sk[1], sk[2]))) return r;
+  if ((r = make_tmap_bshd(&tv, v, fmt, B, Sk, H, D, sv[0], sv[1], sv[2]))) return r;
+  AttnParams p = {};
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal; p.scale = scale;
+  p.fmt = fmt; p.o = o; p.lse = (float*)lse; p.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  PF_ATTN_DISPATCH(launch_fwd, tq, tk, tv, p, st);
+}
+
+// dout / out: [B, Sq, H, D] contiguous; dq_accum fp32 [B,Sq,H,D] (zeroed here); dq, dk, dv
+// contiguous outputs; delta fp32 [B,H,Sq] scratch.
+PF_API int pf_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                       const void* out, const void* lse, void* delta, void* dq_accum, void* dq,
+                       void* dk, void* dv, int B, int H, int Sq, int Sk, int D,
+                       const long long* sq, const long long* sk, const long long* sv, int causal,
+                       float scale, int dtype, int* status, int sm_count, void* stream) {
+  if (dtype != PF_F16 && dtype != PF_BF16) return -1;
+  if (D % 8 || D > 128) return -3;
+  if (!strides_ok(q, sq[0], sq[1], sq[2]) || !strides_ok(k, sk[0], sk[1], sk[2]) ||
+      !strides_ok(v, sv[0], sv[1], sv[2]) || (reinterpret_cast<uintptr_t>(dout) & 15))
+    return -2;
+  const int fmt = dtype == PF_BF16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long rows = (long long)B * Sq * H;
+  if (dtype == PF_F16)
+    attn_delta_kernel<__half><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(
+        (const __half*)dout, (const __half*)out, (float*)delta, B, Sq, H, D);
+  else
+    attn_delta_kernel<__nv_bfloat16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, (float*)delta, B, Sq, H, D);
+  PF_CHECK_LAUNCH();
+  cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * D, st);
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_tmap_bshd(&tq, q, fmt, B, Sq, H, D, sq[0], sq[1], sq[2]))) return r;
+  if ((r = make_tmap_bshd(&tk, k, fmt, B, Sk, H, D, sk[0], sk[1], sk[2]))) return r;
+  if ((r = make_tmap_bshd(&tv, v, fmt, B, Sk, H, D, sv[0], sv[1], sv[2]))) return r;
+  if ((r = make_tmap_bshd(&tdo, dout, fmt, B, Sq, H, D, (long long)Sq * H * D, (long long)H * D,
+                          D)))
+    return r;
+  AttnParams p = {};
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal; p.scale = scale;
+  p.fmt = fmt; p.lse = (float*)const_cast<void*>(lse); p.delta = (const float*)delta;
+  p.dq_accum = (float*)dq_accum; p.dk = dk; p.dv = dv; p.status = status;
+  {
+    auto run = [&]() -> int { PF_ATTN_DISPATCH(launch_bwd, tq, tk, tv, tdo, p, st); };
+    if ((r = run())) return r;
+  }
+  const long long n = rows * D;
+  long long blocks = (n + 255) / 256;
+  const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 8;
+  if (blocks > cap) blocks = cap;
+  if (dtype == PF_F16)
+    attn_dq_convert_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const float*)dq_accum,
+                                                                     (__half*)dq, n);
+  else
+    attn_dq_convert_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        (const float*)dq_accum, (__nv_bfloat16*)dq, n);
+  PF_CHECK_LAUNCH();
+  return 0;
+}

@@ -344,3 +344,46 @@ def _attn_ok(q, k, v) -> bool:
     D = q.shape[-1]
     return (q.dtype in (torch.float16, torch.bfloat16) and D % 8 == 0 and D <= 128
             and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1)
+
+
+def _strides3(t: torch.Tensor):
+    return (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, scale: float
+             ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,Sq,H,D], k/v [B,Sk,H,D] (strided views allowed) -> (o [B,Sq,H,D], lse [B,H,Sq])."""
+    L = _lib.lib()
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    fix = lambda t: t if (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and
+                          all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
+    q, k, v = fix(q), fix(k), fix(v)
+    o = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    check(L.pf_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), B, H, Sq, Sk, D, _strides3(q),
+                        _strides3(k), _strides3(v), int(causal), c_f(scale), dt(q.dtype),
+                        ptr(status_word(q.device)), stream()), "pf_attn_fwd")
+    return o, lse
+
+
+def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+             o: torch.Tensor, lse: torch.Tensor, causal: bool, scale: float
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    L = _lib.lib()
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    fix = lambda t: t if (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and
+                          all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
+    q, k, v = fix(q), fix(k), fix(v)
+    do, o = do.contiguous(), o.contiguous()
+    dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    acc = torch.empty((B, Sq, H, D), dtype=torch.float32, device=q.device)
+    check(L.pf_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(acc),
+                        ptr(dq), ptr(dk), ptr(dv), B, H, Sq, Sk, D, _strides3(q), _strides3(k),
+                        _strides3(v), int(causal), c_f(scale), dt(q.dtype),
+                        ptr(status_word(q.device)), sm_count(q.device), stream()), "pf_attn_bwd")
+    return dq, dk, dv
