@@ -153,7 +153,7 @@ def run_native(args) -> int:
     option = PipeOption(device_cnt=state.pp_size, batch_size=args.batch_size,
                         batch_cnt=args.batch_cnt, mixed_precision=mp, cpu_test=cpu,
                         no_bench_optimizer=True, optimizer={"type": "adamw", "lr": 1e-4},
-                        fused_dp=not args.nccl_dp, verbosity="info" if args.verbose else "warning")
+                        fused_dp=not args.nccl_dp, cuda_graphs=not args.no_graphs, verbosity="info" if args.verbose else "warning")
     if not state.is_main_rank:
         worker_loop()
         return 0
@@ -258,6 +258,8 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--dp_mesh", type=str, default=None)
     ap.add_argument("--nccl_dp", action="store_true", help="NCCL all-reduce DP baseline")
+    ap.add_argument("--no_graphs", action="store_true",
+                    help="run stages eagerly instead of replaying captured CUDA graphs")
     ap.add_argument("--cpu", action="store_true", help="plumbing check without a GPU")
     ap.add_argument("--verbose", action="store_true")
     # model shape (defaults: ViT-g/14 of the headline configuration)

@@ -137,6 +137,44 @@ class CommPlan:
                 self.channel_recv[a] = msgs
 
 
+class _GraphedStage:
+    """CUDA graphs of one stage's forward and backward for one in-flight slot.
+
+    The forward graph reads ``static_ins`` and produces ``static_outs``; its saved activations
+    live in the graph's private memory pool until the backward graph of the same slot has been
+    replayed.  The backward graph reads ``static_gouts``, accumulates parameter gradients in
+    place (bucket views / wgrad epilogues) and leaves the gradients of the stage inputs in
+    ``static_ins[j].grad``."""
+
+    def __init__(self):
+        self.fwd = None
+        self.bwd = None
+        self.static_ins: List[Any] = []
+        self.static_outs: Tuple[Any, ...] = ()
+        self.grad_outs: List[Tuple[int, torch.Tensor]] = []   # (output index, static grad)
+        self.failed = False
+
+
+def inflight_slots(steps: Sequence[Step]) -> Tuple[Dict[Tuple[int, int], int], int]:
+    """(stage, micro-batch) -> slot such that two micro-batches of a stage share a slot only
+    when the first one's backward precedes the second one's forward."""
+    free: Dict[int, List[int]] = {}
+    nxt: Dict[int, int] = {}
+    slot: Dict[Tuple[int, int], int] = {}
+    for st in steps:
+        if st.work == StepWork.FORWARD:
+            fl = free.setdefault(st.node_id, [])
+            if fl:
+                slot[(st.node_id, st.batch_id)] = fl.pop(0)
+            else:
+                slot[(st.node_id, st.batch_id)] = nxt.get(st.node_id, 0)
+                nxt[st.node_id] = nxt.get(st.node_id, 0) + 1
+        elif st.work == StepWork.BACKWARD:
+            free.setdefault(st.node_id, []).append(slot[(st.node_id, st.batch_id)])
+            free[st.node_id].sort()
+    return slot, max(nxt.values(), default=0)
+
+
 class StageWorker:
     """Executes the step program of one pipeline rank."""
 
@@ -162,6 +200,12 @@ class StageWorker:
         self.dp = None                     # data-parallel reducer (set by the runtime front-end)
         self.shared_groups: Dict[Tuple[int, ...], Any] = {}
         self.idle_mem = 0
+        self.use_graphs = bool(getattr(option, "cuda_graphs", False)) and device.type == "cuda"
+        self.graph_warmup_steps = 1       # eager steps before capture (lazy inits, autotune)
+        self.graphs: Dict[Tuple[int, int], _GraphedStage] = {}
+        self.graph_pool = None
+        self.slot_of: Dict[Tuple[int, int], int] = {}
+        self.train_steps_done = 0
         self._reset_step_state()
 
     # ------------------------------------------------------------------ plan installation
@@ -196,6 +240,7 @@ class StageWorker:
             self.eval_comm = CommPlan(self.part, eval_steps_by_rank, self.batch_cnt,
                                       self.pp_rank, self.main_rank, training=False)
         self.recv_bufs: Dict[MsgKey, torch.Tensor] = {}
+        self.slot_of, _ = inflight_slots(self.steps)
         if self.transport is not None:
             g = self.global_ranks
             self.transport.warm_up([(g[a], g[b]) for a, b in self.comm.channels])
@@ -320,6 +365,18 @@ class StageWorker:
         sp = self.part.stages[stage]
         ins = self._stage_inputs(comm, sp, mb)
         start = self.recorder.record_event(self.device)
+        if self.use_graphs and torch.is_grad_enabled() and \
+                self.train_steps_done >= self.graph_warmup_steps:
+            gs = self._graph_for(sp, stage, mb, ins)
+            if gs is not None:
+                for dst, src in zip(gs.static_ins, ins):
+                    if dst is not src and torch.is_tensor(dst):
+                        dst.copy_(src, non_blocking=True)
+                gs.fwd.replay()
+                self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
+                self.fw_inputs[(stage, mb)] = gs.static_ins
+                self.fw_outputs[(stage, mb)] = gs.static_outs
+                return
         with gen_amp_context(self.device, self.option.mixed_precision):
             outs = self.stage_mods[stage](*ins)
         self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
@@ -327,6 +384,70 @@ class StageWorker:
             outs = (outs,)
         self.fw_inputs[(stage, mb)] = ins
         self.fw_outputs[(stage, mb)] = tuple(outs)
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _graph_for(self, sp: StageSpec, stage: int, mb: int, ins: List[Any]
+                   ) -> Optional[_GraphedStage]:
+        key = (stage, self.slot_of.get((stage, mb), 0))
+        gs = self.graphs.get(key)
+        if gs is not None:
+            return None if gs.failed else gs
+        gs = _GraphedStage()
+        self.graphs[key] = gs
+        try:
+            self._capture(gs, sp, stage, ins)
+        except Exception as e:   # the stage stays on the eager path
+            gs.failed = True
+            self.log.warning("CUDA graph capture of stage %d failed (%s: %s); running it eagerly",
+                             stage, type(e).__name__, e)
+            return None
+        return gs
+
+    def _capture(self, gs: _GraphedStage, sp: StageSpec, stage: int, ins: List[Any]) -> None:
+        if self.graph_pool is None:
+            self.graph_pool = torch.cuda.graph_pool_handle()
+        static_ins: List[Any] = []
+        for inp, v in zip(sp.inputs, ins):
+            if inp.kind == "state" or not torch.is_tensor(v):
+                static_ins.append(v)
+                continue
+            t = torch.empty_like(v).copy_(v)
+            if v.requires_grad:
+                t.requires_grad_(True)
+            static_ins.append(t)
+        torch.cuda.synchronize(self.device)
+        self.params.prepare_backward()
+        mod = self.stage_mods[stage]
+        fwd = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fwd, pool=self.graph_pool, capture_error_mode="thread_local"):
+            with gen_amp_context(self.device, self.option.mixed_precision):
+                outs = mod(*static_ins)
+        if not isinstance(outs, (tuple, list)):
+            outs = (outs,)
+        outs = tuple(outs)
+        grad_outs = [(j, torch.zeros_like(o)) for j, o in enumerate(outs)
+                     if torch.is_tensor(o) and o.requires_grad]
+        bwd = None
+        if grad_outs:
+            for t in static_ins:
+                if torch.is_tensor(t) and t.requires_grad and t.is_leaf and \
+                        not self._is_param_view(t):
+                    t.grad = None
+            bwd = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(bwd, pool=self.graph_pool,
+                                  capture_error_mode="thread_local"):
+                torch.autograd.backward([outs[j] for j, _ in grad_outs],
+                                        [g for _, g in grad_outs])
+        gs.fwd, gs.bwd = fwd, bwd
+        gs.static_ins, gs.static_outs, gs.grad_outs = static_ins, outs, grad_outs
+
+    def _is_param_view(self, t: torch.Tensor) -> bool:
+        ptrs = getattr(self, "_param_ptrs", None)
+        if ptrs is None:
+            ptrs = {s.view.data_ptr() for s in self.params.slots.values()
+                    if torch.is_tensor(s.view)}
+            self._param_ptrs = ptrs
+        return t.data_ptr() in ptrs
 
     def send_act(self, comm: CommPlan, stage: int, mb: int) -> None:
         outs = self.fw_outputs[(stage, mb)]
@@ -367,7 +488,17 @@ class StageWorker:
             tensors.append(o)
             grads.append(g.reshape(o.shape))
         start = self.recorder.record_event(self.device)
-        if tensors:
+        gs = self.graphs.get((stage, self.slot_of.get((stage, mb), 0))) if self.use_graphs else None
+        if gs is not None and not gs.failed and gs.static_outs is outs:
+            if gs.bwd is not None:
+                for j, buf in gs.grad_outs:
+                    g = grads_by_out.get(j)
+                    if g is None:
+                        buf.zero_()
+                    else:
+                        buf.copy_(g.reshape(buf.shape), non_blocking=True)
+                gs.bwd.replay()
+        elif tensors:
             self.params.prepare_backward()
             torch.autograd.backward(tensors, grads)
         self.recorder.append_bw(stage, start, self.recorder.record_event(self.device))
@@ -449,6 +580,7 @@ class StageWorker:
                     self.send_grad(comm, s, b)
                 elif w == StepWork.OPTIMIZER_STEP and training:
                     self.optimizer_step()
+                    self.train_steps_done += 1
                 if nvtx:
                     torch.cuda.nvtx.range_pop()
         if not training:
