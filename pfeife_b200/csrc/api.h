@@ -88,5 +88,6 @@ PF_DECL int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, vo
 PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
                         const void* out, const void* lse, void* delta, void* dq_accum, void* dq,
                         void* dk, void* dv, int B, int H, int Sq, int Sk, int D,
-                        const long long* sq, const long long* sk, const long long* sv, int causal,
-                        float scale, int dtype, int* status, int sm_count, void* stream);
+                        const long long* sq, const long long* sk, const long long* sv,
+                        const long long* sdq, const long long* sdkv, int causal, float scale,
+                        int dtype, int* status, int sm_count, void* stream);

@@ -42,8 +42,9 @@ struct AttnParams {
   // backward
   const float* delta;   // [B,H,Sq]
   float* dq_accum;      // [B,Sq,H,D] fp32, zeroed
-  void* dk;             // [B,Sk,H,D] contiguous
+  void* dk;             // [B,Sk,H,D] with strides sdkv (batch, seq, head)
   void* dv;
+  long long sdkv[3];
   int* status;
 };
 
@@ -98,9 +99,9 @@ __device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t sa, uint32_t sb
 }
 // A[128 x 128] K-major . B given as [K=128 rows][N] (N contiguous, MN-major blocks of 64)
 __device__ __forceinline__ void mma_k_mn(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc,
-                                         bool accumulate_first) {
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
+                                         bool accumulate_first, int ksteps = 8) {
+#pragma unroll 1
+  for (int k = 0; k < ksteps; ++k) {
     const uint32_t aoff = (k >> 2) * ATT_BLK + (k & 3) * 32;
     tc_mma_f16(d_tmem, make_desc_sw128(sa + aoff, 16, 1024),
                make_desc_sw128(sb + k * 2048, ATT_BLK, 1024), idesc, (k > 0) || accumulate_first);
@@ -108,9 +109,9 @@ __device__ __forceinline__ void mma_k_mn(uint32_t d_tmem, uint32_t sa, uint32_t 
 }
 // A given as [K=128 rows][M=128] (M contiguous) . B given as [K=128 rows][N] (N contiguous)
 __device__ __forceinline__ void mma_mn_mn(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc,
-                                          bool accumulate_first) {
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
+                                          bool accumulate_first, int ksteps = 8) {
+#pragma unroll 1
+  for (int k = 0; k < ksteps; ++k) {
     tc_mma_f16(d_tmem, make_desc_sw128(sa + k * 2048, ATT_BLK, 1024),
                make_desc_sw128(sb + k * 2048, ATT_BLK, 1024), idesc, (k > 0) || accumulate_first);
   }
@@ -173,6 +174,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   for (int j = 0; j < n_tiles && ok; ++j) {
     const int k0 = j * ATT_BN;
+    const int rem = min(ATT_BN, p.Sk - k0);
+    const int n_mma = (rem + 15) / 16 * 16;
+    const int n_chunks = (n_mma + 31) / 32;
     if (tid == 0) {
       load_tile<NBLK>(sK, &tk, bar_k, h, k0, b);
       load_tile<NBLK>(sV, &tv, bar_v, h, k0, b);
@@ -180,7 +184,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ok = ok && mbar_wait(bar_k, ph, p.status, PF_ERR_TIMEOUT_FULL);
       if (ok) {
         tc_fence_after();
-        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_s, false);
+        // a ragged last tile only computes the key columns that exist (rounded up to 16)
+        const uint32_t id = (n_mma == ATT_BN) ? idesc_s : make_idesc_f16(128, n_mma, p.fmt, 0, 0);
+        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), id, false);
         tc_commit(bar_s);
       }
     }
@@ -191,8 +197,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     // ---- softmax over this tile's 128 scores of row `tid` (two passes over TMEM: the row
     //      maximum first, then exponentials; only 32 scores are live in registers at a time)
     float mx = m;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll 1
+    for (int c = 0; c < n_chunks; ++c) {
       uint32_t raw[32];
       tmem_ld32(t_s + lane_off + c * 32, raw);
       tmem_ld_wait();
@@ -206,8 +212,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const float m_use = (mx == -INFINITY) ? 0.f : mx;
     const float alpha = exp2f(m - m_use);     // m = -inf -> 0
     float rs = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll 1
+    for (int c = 0; c < n_chunks; ++c) {
       uint32_t raw[32];
       tmem_ld32(t_s + lane_off + c * 32, raw);
       tmem_ld_wait();
@@ -230,7 +236,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ok = mbar_wait(bar_v, ph, p.status, PF_ERR_TIMEOUT_FULL);
       if (ok) {
         tc_fence_after();
-        mma_k_mn(t_o, smem_u32(sP), smem_u32(sV), idesc_o, false);
+        mma_k_mn(t_o, smem_u32(sP), smem_u32(sV), idesc_o, false, n_mma / 16);
         tc_commit(bar_o);
       }
     }
@@ -295,12 +301,28 @@ attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* 
   }
 }
 
+// dq[b, i, h, :] (strided) = convert(acc[b, i, h, :]) ; acc is contiguous [B*Sq*H, D]
 template <typename T>
 __global__ void __launch_bounds__(256)
-attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, long long n) {
+attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, long long rows, int D,
+                       int Sq, int H, long long sb, long long ss, long long sh) {
+  const int dv = D / 8;
+  const long long total = rows * dv;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-    dq[i] = from_f32<T>(acc[i]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long row = i / dv;
+    const int c = (int)(i - row * dv);
+    const int h = (int)(row % H);
+    const long long bs = row / H;
+    const int si = (int)(bs % Sq);
+    const long long b = bs / Sq;
+    const float4 a0 = reinterpret_cast<const float4*>(acc + row * D)[2 * c];
+    const float4 a1 = reinterpret_cast<const float4*>(acc + row * D)[2 * c + 1];
+    uint4 q;
+    q.x = pack2<T>(a0.x, a0.y); q.y = pack2<T>(a0.z, a0.w);
+    q.z = pack2<T>(a1.x, a1.y); q.w = pack2<T>(a1.z, a1.w);
+    reinterpret_cast<uint4*>(dq + b * sb + (long long)si * ss + (long long)h * sh)[c] = q;
+  }
 }
 
 template <typename T, int DP>
@@ -348,6 +370,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const float c2 = p.scale * LOG2E;
   const int shift = p.Sk - p.Sq;
 
+  const int rem_k = min(ATT_BN, p.Sk - k0);
+  const int nk_mma = (rem_k + 15) / 16 * 16;          // key columns that exist, rounded to 16
+  const int nk_chunks = (nk_mma + 31) / 32;
+  const uint32_t idesc_sr = make_idesc_f16(128, nk_mma, p.fmt, 0, 0);
   int q_begin = 0;
   if (p.causal) q_begin = max(0, k0 - shift) / ATT_BM * ATT_BM;   // first q tile that sees k0
   const int n_q = (p.Sq + ATT_BM - 1) / ATT_BM;
@@ -377,8 +403,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ok = ok && mbar_wait(bar_q, ph, p.status, PF_ERR_TIMEOUT_FULL);
       if (ok) {
         tc_fence_after();
-        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_s, false);    // S  = Q K^T
-        mma_kk<DP / 16>(t_dp, smem_u32(sdO), smem_u32(sV), idesc_s, false);  // dP = dO V^T
+        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_sr, false);    // S  = Q K^T
+        mma_kk<DP / 16>(t_dp, smem_u32(sdO), smem_u32(sV), idesc_sr, false);  // dP = dO V^T
         tc_commit(bar_mma1);
       }
     }
@@ -389,8 +415,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const bool row_ok = qi < p.Sq;
     const float lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * LOG2E : 0.f;
     const float dl = row_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll 1
+    for (int c = 0; c < nk_chunks; ++c) {
       uint32_t rs[32], rp[32];
       tmem_ld32(t_s + lane_off + c * 32, rs);
       tmem_ld32(t_dp + lane_off + c * 32, rp);
@@ -414,10 +440,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       // sP / sdS hold [q rows][kv cols]: as A operands of the two products below they are
       // MN-major (M = kv contiguous within a row, K = q across rows)
-      mma_mn_mn(t_dv, smem_u32(sP), smem_u32(sdO), idesc_kd, !first);   // dV += P^T dO
-      mma_mn_mn(t_dk, smem_u32(sdS), smem_u32(sQ), idesc_kd, !first);   // dK += dS^T Q
+      // reductions run only over the query rows / key columns that exist (rounded to 16);
+      // rows of dV / dK beyond the last key are never stored
+      const int q_steps = (min(ATT_BM, p.Sq - q0) + 15) / 16;
+      mma_mn_mn(t_dv, smem_u32(sP), smem_u32(sdO), idesc_kd, !first, q_steps);  // dV += P^T dO
+      mma_mn_mn(t_dk, smem_u32(sdS), smem_u32(sQ), idesc_kd, !first, q_steps);  // dK += dS^T Q
       tc_commit(bar_mma2);
-      mma_k_mn(t_s, smem_u32(sdS), smem_u32(sK), idesc_dq, false);      // dQ_tile = dS K
+      mma_k_mn(t_s, smem_u32(sdS), smem_u32(sK), idesc_dq, false, nk_mma / 16);  // dQ = dS K
       tc_commit(bar_dq);
     }
     __syncwarp();
@@ -451,8 +480,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   if (ok && !first) {
     tc_fence_after();
     const int kj = k0 + tid;
-    T* dkp = reinterpret_cast<T*>(p.dk) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
-    T* dvp = reinterpret_cast<T*>(p.dv) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+    const long long off_kv = (long long)b * p.sdkv[0] + (long long)kj * p.sdkv[1] +
+                             (long long)h * p.sdkv[2];
+    T* dkp = reinterpret_cast<T*>(p.dk) + off_kv;
+    T* dvp = reinterpret_cast<T*>(p.dv) + off_kv;
 #pragma unroll
     for (int c = 0; c < DP / 32; ++c) {
       uint32_t rk[32], rv[32];
@@ -483,8 +514,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     // no query tile sees this key tile (causal with Sk > Sq + ...): gradients are zero
     const int kj = k0 + tid;
     if (kj < p.Sk) {
-      T* dkp = reinterpret_cast<T*>(p.dk) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
-      T* dvp = reinterpret_cast<T*>(p.dv) + (((long long)b * p.Sk + kj) * p.H + h) * p.D;
+      const long long off_kv = (long long)b * p.sdkv[0] + (long long)kj * p.sdkv[1] +
+                               (long long)h * p.sdkv[2];
+      T* dkp = reinterpret_cast<T*>(p.dk) + off_kv;
+      T* dvp = reinterpret_cast<T*>(p.dv) + off_kv;
       for (int d = 0; d < p.D; ++d) { dkp[d] = from_f32<T>(0.f); dvp[d] = from_f32<T>(0.f); }
     }
   }
@@ -627,12 +660,15 @@ PF_API int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, voi
 PF_API int pf_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
                        const void* out, const void* lse, void* delta, void* dq_accum, void* dq,
                        void* dk, void* dv, int B, int H, int Sq, int Sk, int D,
-                       const long long* sq, const long long* sk, const long long* sv, int causal,
+                       const long long* sq, const long long* sk, const long long* sv,
+                       const long long* sdq, const long long* sdkv, int causal,
                        float scale, int dtype, int* status, int sm_count, void* stream) {
   if (dtype != PF_F16 && dtype != PF_BF16) return -1;
   if (D % 8 || D > 128) return -3;
   if (!strides_ok(q, sq[0], sq[1], sq[2]) || !strides_ok(k, sk[0], sk[1], sk[2]) ||
-      !strides_ok(v, sv[0], sv[1], sv[2]) || (reinterpret_cast<uintptr_t>(dout) & 15))
+      !strides_ok(v, sv[0], sv[1], sv[2]) || (reinterpret_cast<uintptr_t>(dout) & 15) ||
+      !strides_ok(dq, sdq[0], sdq[1], sdq[2]) || !strides_ok(dk, sdkv[0], sdkv[1], sdkv[2]) ||
+      !strides_ok(dv, sdkv[0], sdkv[1], sdkv[2]))
     return -2;
   const int fmt = dtype == PF_BF16;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -657,20 +693,21 @@ PF_API int pf_attn_bwd(const void* dout, const void* q, const void* k, const voi
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal; p.scale = scale;
   p.fmt = fmt; p.lse = (float*)const_cast<void*>(lse); p.delta = (const float*)delta;
   p.dq_accum = (float*)dq_accum; p.dk = dk; p.dv = dv; p.status = status;
+  p.sdkv[0] = sdkv[0]; p.sdkv[1] = sdkv[1]; p.sdkv[2] = sdkv[2];
   {
     auto run = [&]() -> int { PF_ATTN_DISPATCH(launch_bwd, tq, tk, tv, tdo, p, st); };
     if ((r = run())) return r;
   }
-  const long long n = rows * D;
+  const long long n = rows * (D / 8);
   long long blocks = (n + 255) / 256;
   const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 8;
   if (blocks > cap) blocks = cap;
   if (dtype == PF_F16)
-    attn_dq_convert_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const float*)dq_accum,
-                                                                     (__half*)dq, n);
+    attn_dq_convert_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
+        (const float*)dq_accum, (__half*)dq, rows, D, Sq, H, sdq[0], sdq[1], sdq[2]);
   else
     attn_dq_convert_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
-        (const float*)dq_accum, (__nv_bfloat16*)dq, n);
+        (const float*)dq_accum, (__nv_bfloat16*)dq, rows, D, Sq, H, sdq[0], sdq[1], sdq[2]);
   PF_CHECK_LAUNCH();
   return 0;
 }

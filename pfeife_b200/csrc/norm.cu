@@ -199,6 +199,110 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* 
   }
 }
 
+// Backward for rows of up to 2048 16-bit elements: one WARP per row (no CTA-wide barrier on the
+// row path), 8 warps per CTA, rows strided over a persistent grid.  Each lane keeps the packed
+// dy / h vectors of its row slice in registers, expands them twice (reduction pass, output
+// pass) and carries dgamma / dbeta partials for its columns across rows.  At the end the 8
+// warps of a CTA fold their partials through shared memory into scratch[blockIdx][2][N].
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h,
+                     const float* __restrict__ gamma, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, const T* __restrict__ dres,
+                     T* __restrict__ dx, float* __restrict__ scratch, long long rows, int N,
+                     int rms) {
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ float sacc[];          // [2][N]
+  const int nvec = N / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 2 * N; i += 256) sacc[i] = 0.f;
+  __syncthreads();
+  float dg[NV][V], db[NV][V];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; }
+  const float inv_n = 1.f / N;
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < rows;
+       row += (long long)gridDim.x * 8) {
+    const float mu = rms ? 0.f : mean[row];
+    const float rs = rstd[row];
+    uint4 qd[NV], qh[NV];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        qd[i] = reinterpret_cast<const uint4*>(dy + row * N)[idx];
+        qh[i] = reinterpret_cast<const uint4*>(h + row * N)[idx];
+        const T* ed = reinterpret_cast<const T*>(&qd[i]);
+        const T* eh = reinterpret_cast<const T*>(&qh[i]);
+        const float4* g4 = reinterpret_cast<const float4*>(gamma + idx * V);
+#pragma unroll
+        for (int j4 = 0; j4 < V / 4; ++j4) {
+          const float4 g = __ldg(g4 + j4);
+          const float gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j4 * 4 + u;
+            const float d = to_f32<T>(ed[j]);
+            const float xhat = (to_f32<T>(eh[j]) - mu) * rs;
+            const float dyg = d * gg[u];
+            s1 += dyg;
+            s2 += dyg * xhat;
+            dg[i][j] += d * xhat;
+            db[i][j] += d;
+          }
+        }
+      }
+    }
+    const float m1 = rms ? 0.f : warp_sum(s1) * inv_n;
+    const float m2 = warp_sum(s2) * inv_n;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        const T* ed = reinterpret_cast<const T*>(&qd[i]);
+        const T* eh = reinterpret_cast<const T*>(&qh[i]);
+        uint4 qr;
+        if (dres) qr = reinterpret_cast<const uint4*>(dres + row * N)[idx];
+        const T* er = reinterpret_cast<const T*>(&qr);
+        uint4 q;
+        T* e = reinterpret_cast<T*>(&q);
+        const float4* g4 = reinterpret_cast<const float4*>(gamma + idx * V);
+#pragma unroll
+        for (int j4 = 0; j4 < V / 4; ++j4) {
+          const float4 g = __ldg(g4 + j4);
+          const float gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j4 * 4 + u;
+            const float xhat = (to_f32<T>(eh[j]) - mu) * rs;
+            float o = rs * (to_f32<T>(ed[j]) * gg[u] - m1 - xhat * m2);
+            if (dres) o += to_f32<T>(er[j]);
+            e[j] = from_f32<T>(o);
+          }
+        }
+        reinterpret_cast<uint4*>(dx + row * N)[idx] = q;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        atomicAdd(&sacc[idx * V + j], dg[i][j]);
+        atomicAdd(&sacc[N + idx * V + j], db[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  float* out = scratch + (long long)blockIdx.x * 2 * N;
+  for (int i = threadIdx.x; i < 2 * N; i += 256) out[i] = sacc[i];
+}
+
 // dgamma[c] (+)= sum_g scratch[g][0][c] ; dbeta likewise
 __global__ void __launch_bounds__(256)
 norm_bwd_finish_kernel(const float* __restrict__ scratch, float* __restrict__ dgamma,
@@ -242,6 +346,19 @@ static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, co
   constexpr int V = 16 / sizeof(T);
   if (N % V) return -2;
   const int nvec = N / V;
+  if (sizeof(T) == 2 && nvec <= 32 * 8) {
+    const size_t smem = 2 * (size_t)N * sizeof(float);
+    if (nvec <= 32 * 3)
+      norm_bwd_warp_kernel<T, 3><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
+          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
+    else if (nvec <= 32 * 6)
+      norm_bwd_warp_kernel<T, 6><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
+          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
+    else
+      norm_bwd_warp_kernel<T, 8><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
+          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
+    return 0;
+  }
   if (nvec <= 128 * NORM_MAX_VEC)
     norm_bwd_kernel<T, 128><<<G, 128, 0, st>>>((const T*)dy, (const T*)h, gamma, mean, rstd,
         (const T*)dres, (T*)dx, scratch, rows, N, rms);
@@ -279,7 +396,7 @@ PF_API int pf_norm_fwd(const void* x, const void* res, const void* gamma, const 
 // Number of CTAs (= rows of the scratch buffer) the backward uses for `rows` rows.
 PF_API int pf_norm_bwd_ctas(long long rows, int sm_count) {
   long long g = (long long)(sm_count > 0 ? sm_count : 148) * 2;
-  if (g > rows) g = rows;
+  if (g > (rows + 7) / 8) g = (rows + 7) / 8;
   if (g < 1) g = 1;
   return (int)g;
 }

@@ -70,7 +70,7 @@ class ViTBlock(nn.Module):
         H = self.num_heads
         y = ops.layer_norm(x, self.ln1.weight, self.ln1.bias, self.eps)
         qkv = ops.linear(y, self.qkv.weight, self.qkv.bias).view(B, S, 3, H, d // H)
-        a = ops.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]).view(B, S, d)
+        a = ops.attention_qkv(qkv).view(B, S, d)
         x = ops.linear(a, self.proj.weight, self.proj.bias, residual=x)
         y = ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.eps)
         return ops.mlp(y, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias,

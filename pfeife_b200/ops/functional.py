@@ -787,3 +787,56 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = False,
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     return attn_fwd(q, k, v, causal, float(scale))[0]
+
+
+# --------------------------------------------------------------------------- packed self-attention
+@torch.library.custom_op("pfeife::attn_qkv_fwd", mutates_args=())
+def attn_qkv_fwd(qkv: Tensor, causal: bool, scale: float) -> Tuple[Tensor, Tensor]:
+    """Self-attention on a fused projection qkv [B, S, 3, H, D] -> (o [B, S, H, D], lse)."""
+    return attn_fwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal, scale)
+
+
+@attn_qkv_fwd.register_fake
+def _(qkv, causal, scale):
+    B, S, _, H, D = qkv.shape
+    return qkv.new_empty((B, S, H, D)), qkv.new_empty((B, H, S), dtype=torch.float32)
+
+
+@torch.library.custom_op("pfeife::attn_qkv_bwd", mutates_args=())
+def attn_qkv_bwd(do: Tensor, qkv: Tensor, o: Tensor, lse: Tensor, causal: bool,
+                 scale: float) -> Tensor:
+    """-> d(qkv) [B, S, 3, H, D], written in place by the backward kernels (no concatenation)."""
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    if _native(qkv) and kx.attention_supported(q, k, v):
+        dq, _, _ = kx.attn_bwd(do, q, k, v, o, lse, causal, scale, packed=True)
+        return dq._base if dq._base is not None else torch.stack(
+            kx.attn_bwd(do, q, k, v, o, lse, causal, scale), dim=2)
+    dq, dk, dv = attn_bwd(do, q, k, v, o, lse, causal, scale)
+    return torch.stack([dq, dk, dv], dim=2)
+
+
+@attn_qkv_bwd.register_fake
+def _(do, qkv, o, lse, causal, scale):
+    return torch.empty_like(qkv)
+
+
+def _attn_qkv_setup(ctx, inputs, output):
+    qkv, causal, scale = inputs
+    o, lse = output
+    ctx.save_for_backward(qkv, o, lse)
+    ctx.causal, ctx.scale = causal, scale
+
+
+def _attn_qkv_backward(ctx, do, dlse):
+    qkv, o, lse = ctx.saved_tensors
+    return attn_qkv_bwd(do.contiguous(), qkv, o, lse, ctx.causal, ctx.scale), None, None
+
+
+attn_qkv_fwd.register_autograd(_attn_qkv_backward, setup_context=_attn_qkv_setup)
+
+
+def attention_qkv(qkv: Tensor, causal: bool = False, scale: Optional[float] = None) -> Tensor:
+    """Self-attention directly on a fused QKV projection laid out [B, S, 3, H, D]."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(qkv.shape[-1])
+    return attn_qkv_fwd(qkv, causal, float(scale))[0]

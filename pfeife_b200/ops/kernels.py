@@ -368,8 +368,11 @@ def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, sc
 
 
 def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-             o: torch.Tensor, lse: torch.Tensor, causal: bool, scale: float
-             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+             o: torch.Tensor, lse: torch.Tensor, causal: bool, scale: float,
+             packed: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (dq, dk, dv).  With ``packed`` (self-attention on slices of one fused projection) the
+    three gradients are slices of a single [B, S, 3, H, D] buffer, i.e. the gradient of the
+    fused projection needs no concatenation."""
     L = _lib.lib()
     B, Sq, H, D = q.shape
     Sk = k.shape[1]
@@ -377,13 +380,18 @@ def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                           all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
     q, k, v = fix(q), fix(k), fix(v)
     do, o = do.contiguous(), o.contiguous()
-    dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
+    if packed and Sq == Sk:
+        dqkv = torch.empty((B, Sq, 3, H, D), dtype=q.dtype, device=q.device)
+        dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    else:
+        dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, Sk, H, D), dtype=q.dtype, device=q.device)
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
     acc = torch.empty((B, Sq, H, D), dtype=torch.float32, device=q.device)
     check(L.pf_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(acc),
                         ptr(dq), ptr(dk), ptr(dv), B, H, Sq, Sk, D, _strides3(q), _strides3(k),
-                        _strides3(v), int(causal), c_f(scale), dt(q.dtype),
-                        ptr(status_word(q.device)), sm_count(q.device), stream()), "pf_attn_bwd")
+                        _strides3(v), _strides3(dq), _strides3(dk), int(causal), c_f(scale),
+                        dt(q.dtype), ptr(status_word(q.device)), sm_count(q.device), stream()),
+          "pf_attn_bwd")
     return dq, dk, dv

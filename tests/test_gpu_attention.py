@@ -65,3 +65,16 @@ def test_attention_on_fused_qkv_views():
     o_ref.sum().backward()
     assert (out.float() - o_ref).abs().max() <= 1e-2
     assert (qkv.grad.float() - ref_in.grad).abs().max() <= 5e-2
+
+
+def test_packed_qkv_attention_writes_fused_gradient():
+    from pfeife_b200 import ops
+    B, S, H, D = 2, 300, 2, 64
+    qkv = (torch.randn(B, S, 3, H, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    out = ops.attention_qkv(qkv, causal=True)
+    out.float().sum().backward()
+    ref_in = qkv.detach().float().requires_grad_()
+    o_ref, _ = ref_attn(ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2], True, 1 / math.sqrt(D))
+    o_ref.sum().backward()
+    assert (out.float() - o_ref).abs().max() <= 2e-2
+    assert (qkv.grad.float() - ref_in.grad).abs().max() <= 1e-1
