@@ -91,3 +91,16 @@ PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const vo
                         const long long* sq, const long long* sk, const long long* sv,
                         const long long* sdq, const long long* sdkv, int causal, float scale,
                         int dtype, int* status, int sm_count, void* stream);
+
+// ---- dp_fused.cu : reduce-scatter + AdamW + all-gather over NVLink peer memory, IPC plumbing
+PF_DECL int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
+                             void* const* lp, void* const* flags, void* m, void* v,
+                             void* local_sync, long long shard_lo, long long shard_hi, float lr,
+                             float beta1, float beta2, float eps, float weight_decay, int step,
+                             float grad_scale, int adamw, int lp_dtype, int check_inf,
+                             const void* loss_scale, void* found_inf, int epoch, int calls_before,
+                             int* status, int sm_count, void* stream);
+PF_DECL int pf_ipc_get_handle(void* ptr, void* handle_out_64);
+PF_DECL int pf_ipc_open(const void* handle_64, void** ptr_out);
+PF_DECL int pf_ipc_close(void* ptr);
+PF_DECL int pf_get_base(void* ptr, void** base_out, long long* size_out);

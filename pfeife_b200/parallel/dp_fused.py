@@ -1,0 +1,147 @@
+"""Fused data-parallel path: the gradient reduce-scatter, unscale, non-finite agreement,
+partitioned AdamW and the all-gather of the updated weights run as one hand-written kernel per
+rank that reads and writes the other ranks' buffers directly over NVLink (csrc/dp_fused.cu).
+
+Host side: the flat gradient / master / shadow buffers of ``RankParams`` are ordinary device
+allocations whose CUDA IPC handles are exchanged once over the control group; every rank maps
+its peers' buffers and keeps a table of peer pointers.  Optimizer moments exist only for the
+rank's own shard (ZeRO-1).  The kernel's cross-GPU barriers are epoch counters in a small
+peer-visible flag buffer.
+
+Optimizers other than Adam / AdamW fall back to the NCCL path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import kernels as kx
+from ..ops._lib import c_f, c_ll, check, dt, ptr, sm_count, stream
+from .dp import NcclDP
+
+DP_MAX = 8
+ALIGN = 128
+
+
+class PeerMemory:
+    """Maps the peers' copies of local device tensors.  All ranks call ``share`` with tensors
+    in the same order."""
+
+    def __init__(self, ctrl_group, size: int, rank: int):
+        self.ctrl_group, self.size, self.rank = ctrl_group, size, rank
+        self._opened: Dict[Tuple[int, bytes], int] = {}
+
+    def share(self, t: torch.Tensor) -> List[int]:
+        """-> per-rank device pointers of `t` (own pointer at index ``rank``)."""
+        L = _lib.lib()
+        _lib.bind_thread()
+        handle = ctypes.create_string_buffer(64)
+        code = L.pf_ipc_get_handle(ctypes.c_void_p(t.data_ptr()), handle)
+        if code:
+            raise _lib.KernelError(f"cudaIpcGetMemHandle failed: {code}")
+        base = ctypes.c_void_p()
+        size = ctypes.c_longlong()
+        code = L.pf_get_base(ctypes.c_void_p(t.data_ptr()), ctypes.byref(base), ctypes.byref(size))
+        if code:
+            raise _lib.KernelError(f"cuMemGetAddressRange failed: {code}")
+        mine = (handle.raw, t.data_ptr() - (base.value or 0))
+        everyone: List[Optional[Tuple[bytes, int]]] = [None] * self.size
+        dist.all_gather_object(everyone, mine, group=self.ctrl_group)
+        ptrs: List[int] = []
+        for r, (h, off) in enumerate(everyone):
+            if r == self.rank:
+                ptrs.append(t.data_ptr())
+                continue
+            key = (r, h)
+            if key not in self._opened:
+                out = ctypes.c_void_p()
+                code = L.pf_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(out))
+                if code:
+                    raise _lib.KernelError(f"cudaIpcOpenMemHandle(rank {r}) failed: {code}")
+                self._opened[key] = out.value
+            ptrs.append(self._opened[key] + off)
+        return ptrs
+
+
+def _table(ptrs: List[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class FusedDP(NcclDP):
+    fused = True
+
+    def __init__(self, state, option):
+        super().__init__(state, option)
+        if self.size > DP_MAX:
+            raise ValueError(f"fused data parallelism supports up to {DP_MAX} ranks")
+        self.rank = state.dp_rank
+        self.device = state.device
+        self.peers = PeerMemory(state.ctrl_dp, self.size, self.rank)
+        self.calls = 0
+        self.params = None
+
+    def attach(self, params) -> None:
+        super().attach(params)          # replicas start from dp rank 0's values
+        self.params = params
+        if params.optimizer_type not in ("adam", "adamw") or not params.numel:
+            self.fused = False
+            return
+        n = params.numel
+        per = (n + self.size - 1) // self.size
+        per = (per + ALIGN - 1) // ALIGN * ALIGN
+        self.shard = (min(n, self.rank * per), min(n, (self.rank + 1) * per))
+        ln = max(self.shard[1] - self.shard[0], 4)
+        self.m = torch.zeros(ln, dtype=torch.float32, device=self.device)
+        self.v = torch.zeros(ln, dtype=torch.float32, device=self.device)
+        self.flags = torch.zeros(2 * DP_MAX, dtype=torch.int32, device=self.device)
+        self.local_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        self.t_grad = _table(self.peers.share(params.grad))
+        self.t_master = _table(self.peers.share(params.master))
+        self.t_lp = _table(self.peers.share(params.lp)) if params.lp is not None else None
+        self.t_flags = _table(self.peers.share(self.flags))
+        dist.barrier(group=self.state.ctrl_dp)
+
+    def reduce_and_step(self, params, scaler, fp16: bool) -> None:
+        L = _lib.lib()
+        params.step_count += 1
+        lo_s, hi_s = self.shard
+        for g, lo, hi in params.group_ranges:
+            h = params.hyper[min(g, len(params.hyper) - 1)]
+            a, b = max(lo, lo_s), min(hi, hi_s)
+            if b < a:
+                a = b = lo_s
+            b1, b2 = h.get("betas", (0.9, 0.999))
+            adamw = params.optimizer_type == "adamw"
+            off = a - lo_s
+            m = self.m[off:] if off < self.m.numel() else self.m
+            v = self.v[off:] if off < self.v.numel() else self.v
+            code = L.pf_dp_fused_step(
+                self.rank, self.size, self.t_grad, self.t_master, self.t_lp, self.t_flags,
+                ptr(m), ptr(v), ptr(self.local_sync), c_ll(a), c_ll(b), c_f(h.get("lr", 1e-3)),
+                c_f(b1), c_f(b2), c_f(h.get("eps", 1e-8)),
+                c_f(h.get("weight_decay", 0.01 if adamw else 0.0)), int(params.step_count),
+                c_f(1.0 / self.size), int(adamw),
+                dt(params.lp.dtype) if params.lp is not None else 0, int(fp16),
+                ptr(scaler.scale_tensor), ptr(params.found_inf), 3 * self.calls + 1, self.calls,
+                ptr(kx.status_word(self.device)), sm_count(self.device), stream())
+            check(code, "pf_dp_fused_step")
+            self.calls += 1
+        if fp16:
+            scaler.update(params.found_inf)
+
+    def gather_optimizer_state(self) -> Dict[str, torch.Tensor]:
+        """Full-length moments assembled from every rank's shard (for checkpoints)."""
+        n = self.params.numel
+        out = {}
+        for name, local in (("exp_avg", self.m), ("exp_avg_sq", self.v)):
+            full = torch.zeros(n, dtype=torch.float32, device=self.device)
+            lo, hi = self.shard
+            full[lo:hi] = local[:hi - lo]
+            dist.all_reduce(full, group=self.group)
+            out[name] = full
+        return out
