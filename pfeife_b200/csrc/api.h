@@ -104,3 +104,21 @@ PF_DECL int pf_ipc_get_handle(void* ptr, void* handle_out_64);
 PF_DECL int pf_ipc_open(const void* handle_64, void** ptr_out);
 PF_DECL int pf_ipc_close(void* ptr);
 PF_DECL int pf_get_base(void* ptr, void** base_out, long long* size_out);
+PF_DECL int pf_peek_u32(const void* dev_ptr, unsigned int* out);
+
+// ---- conv_gn.cu : NHWC im2col / col2im, GroupNorm(+SiLU), nearest 2x upsample
+PF_DECL int pf_im2col(const void* x, void* cols, int B, int H, int W, int C, int KH, int KW,
+                      int Ho, int Wo, int stride, int pad, long long ldc, int dtype, int sm_count,
+                      void* stream);
+PF_DECL int pf_col2im(const void* dcols, void* dx, int B, int H, int W, int C, int KH, int KW,
+                      int Ho, int Wo, int stride, int pad, long long ldc, int dtype, int sm_count,
+                      void* stream);
+PF_DECL int pf_groupnorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
+                             void* mean, void* rstd, int B, int HW, int C, int G, float eps,
+                             int act_silu, int dtype, int sm_count, void* stream);
+PF_DECL int pf_groupnorm_bwd(const void* dy, const void* x, const void* mean, const void* rstd,
+                             const void* gamma, const void* beta, void* dx, void* dgamma,
+                             void* dbeta, void* sums, int B, int HW, int C, int G, int act_silu,
+                             int dtype, int sm_count, void* stream);
+PF_DECL int pf_upsample2x(const void* x, void* y, int B, int H, int W, int C, int backward,
+                          int dtype, int sm_count, void* stream);

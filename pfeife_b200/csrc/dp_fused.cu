@@ -256,3 +256,9 @@ PF_API int pf_get_base(void* ptr, void** base_out, long long* size_out) {
   *size_out = (long long)size;
   return 0;
 }
+
+// Reads 4 bytes at a (possibly peer-mapped) device address through the copy engine.  An
+// unmapped address makes the copy return an error code; it does not fault the context.
+PF_API int pf_peek_u32(const void* dev_ptr, unsigned int* out) {
+  return (int)cudaMemcpy(out, dev_ptr, 4, cudaMemcpyDeviceToHost);
+}

@@ -840,3 +840,225 @@ def attention_qkv(qkv: Tensor, causal: bool = False, scale: Optional[float] = No
     if scale is None:
         scale = 1.0 / math.sqrt(qkv.shape[-1])
     return attn_qkv_fwd(qkv, causal, float(scale))[0]
+
+
+# =========================================================================== UNet ops (NHWC)
+def _pad_to8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+@torch.library.custom_op("pfeife::conv2d_fwd", mutates_args=())
+def conv2d_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], stride: int, pad: int) -> Tensor:
+    """Channels-last convolution: x [B, H, W, Cin], w [Cout, Cin, KH, KW] -> [B, Ho, Wo, Cout].
+    On the native path the convolution is a tcgen05 GEMM over im2col rows (1x1: no im2col)."""
+    Cout, Cin, KH, KW = w.shape
+    cd = compute_dtype(x)
+    if x.is_cuda and cd in (torch.float16, torch.bfloat16):
+        xc = x if x.dtype == cd else kx.cast(x, cd)
+        B, H, W, _ = xc.shape
+        cin8, cout8 = _pad_to8(Cin), _pad_to8(Cout)
+        if cin8 != Cin:
+            xc = F.pad(xc, (0, cin8 - Cin))
+        w2 = _weight_as(w, cd).permute(0, 2, 3, 1)                      # [Cout, KH, KW, Cin]
+        if cin8 != Cin or cout8 != Cout:
+            w2 = F.pad(w2, (0, cin8 - Cin, 0, 0, 0, 0, 0, cout8 - Cout))
+        w2 = w2.reshape(cout8, KH * KW * cin8).contiguous()
+        Ho = (H + 2 * pad - KH) // stride + 1
+        Wo = (W + 2 * pad - KW) // stride + 1
+        if KH == 1 and KW == 1 and stride == 1 and pad == 0:
+            cols = xc.reshape(B * H * W, cin8)
+        else:
+            cols = kx.im2col(xc, KH, KW, stride, pad)
+        b2 = None
+        if bias is not None:
+            b2 = bias.float() if cout8 == Cout else F.pad(bias.float(), (0, cout8 - Cout))
+        y = kx.gemm(cols, w2, bias=b2)
+        y = y.view(B, Ho, Wo, cout8)
+        return y[..., :Cout].contiguous() if cout8 != Cout else y
+    y = F.conv2d(x.to(cd).permute(0, 3, 1, 2), w.to(cd), None if bias is None else bias.to(cd),
+                 stride=stride, padding=pad)
+    return y.permute(0, 2, 3, 1).contiguous()
+
+
+@conv2d_fwd.register_fake
+def _(x, w, bias, stride, pad):
+    B, H, W, _ = x.shape
+    Cout, _, KH, KW = w.shape
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    return x.new_empty((B, Ho, Wo, Cout), dtype=compute_dtype(x))
+
+
+@torch.library.custom_op("pfeife::conv2d_bwd", mutates_args=())
+def conv2d_bwd(dy: Tensor, x: Tensor, w: Tensor, stride: int, pad: int, need_dx: bool,
+               need_db: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """-> (dx [B,H,W,Cin], dw fp32 [Cout,Cin,KH,KW], db fp32 [Cout])."""
+    Cout, Cin, KH, KW = w.shape
+    cd = dy.dtype
+    if dy.is_cuda and cd in (torch.float16, torch.bfloat16):
+        xc = x if x.dtype == cd else kx.cast(x, cd)
+        B, H, W, _ = xc.shape
+        cin8, cout8 = _pad_to8(Cin), _pad_to8(Cout)
+        if cin8 != Cin:
+            xc = F.pad(xc, (0, cin8 - Cin))
+        dy2 = dy.reshape(-1, Cout)
+        if cout8 != Cout:
+            dy2 = F.pad(dy2, (0, cout8 - Cout))
+        dy2 = dy2.contiguous()
+        one = KH == 1 and KW == 1 and stride == 1 and pad == 0
+        cols = xc.reshape(B * H * W, cin8) if one else kx.im2col(xc, KH, KW, stride, pad)
+        dw2 = kx.gemm(dy2, cols, a_mn=True, b_mn=True, out_dtype=torch.float32)   # [cout8, K]
+        dw = dw2.view(cout8, KH, KW, cin8)[:Cout, :, :, :Cin].permute(0, 3, 1, 2).contiguous()
+        dx = dy.new_empty(0)
+        if need_dx:
+            w2 = _weight_as(w, cd).permute(0, 2, 3, 1)
+            if cin8 != Cin or cout8 != Cout:
+                w2 = F.pad(w2, (0, cin8 - Cin, 0, 0, 0, 0, 0, cout8 - Cout))
+            w2 = w2.reshape(cout8, KH * KW * cin8).contiguous()
+            dcols = kx.gemm(dy2, w2, b_mn=True)                                  # [M, K]
+            dxp = dcols.view(B, H, W, cin8) if one else \
+                kx.col2im(dcols, (B, H, W, cin8), KH, KW, stride, pad)
+            dx = dxp[..., :Cin].contiguous() if cin8 != Cin else dxp
+        db = kx.colsum(dy2)[:Cout].contiguous() if need_db else dy.new_empty(0, dtype=torch.float32)
+        return dx, dw, db
+    xn = x.to(cd).permute(0, 3, 1, 2)
+    dyn = dy.permute(0, 3, 1, 2)
+    dx = torch.nn.grad.conv2d_input(xn.shape, w.to(cd), dyn, stride=stride, padding=pad) \
+        .permute(0, 2, 3, 1).contiguous() if need_dx else dy.new_empty(0)
+    dw = torch.nn.grad.conv2d_weight(xn.float(), w.shape, dyn.float(), stride=stride, padding=pad)
+    db = dyn.float().sum((0, 2, 3)) if need_db else dy.new_empty(0, dtype=torch.float32)
+    return dx, dw.float(), db
+
+
+@conv2d_bwd.register_fake
+def _(dy, x, w, stride, pad, need_dx, need_db):
+    return (torch.empty_like(x, dtype=dy.dtype) if need_dx else dy.new_empty(0),
+            w.new_empty(w.shape, dtype=torch.float32),
+            dy.new_empty(w.shape[0] if need_db else 0, dtype=torch.float32))
+
+
+def _conv_setup(ctx, inputs, output):
+    x, w, bias, stride, pad = inputs
+    ctx.save_for_backward(x, w)
+    ctx.stride, ctx.pad = stride, pad
+    ctx.meta = (x.dtype, w.dtype, None if bias is None else bias.dtype)
+
+
+def _conv_backward(ctx, dy):
+    x, w = ctx.saved_tensors
+    xd, wd, bd = ctx.meta
+    need = ctx.needs_input_grad
+    dx, dw, db = conv2d_bwd(dy.contiguous(), x, w, ctx.stride, ctx.pad, need[0], bd is not None)
+    return (dx.to(xd) if need[0] else None, dw.to(wd) if need[1] else None,
+            db.to(bd) if bd is not None else None, None, None)
+
+
+conv2d_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
+
+
+def conv2d(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, stride: int = 1,
+           padding: int = 0) -> Tensor:
+    """NHWC convolution with a standard [Cout, Cin, KH, KW] weight."""
+    return conv2d_fwd(x, weight, bias, stride, padding)
+
+
+@torch.library.custom_op("pfeife::group_norm_fwd", mutates_args=())
+def group_norm_fwd(x: Tensor, gamma: Tensor, beta: Tensor, groups: int, eps: float,
+                   silu_act: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """NHWC GroupNorm with optional fused SiLU -> (y, mean[B*G], rstd[B*G])."""
+    if _native(x):
+        return kx.groupnorm_fwd(x, gamma, beta, groups, eps, silu_act)
+    B, H, W, C = x.shape
+    xf = x.float().reshape(B, H * W, groups, C // groups)
+    mean = xf.mean((1, 3))
+    var = xf.var((1, 3), unbiased=False)
+    rstd = torch.rsqrt(var + eps)
+    xh = (xf - mean[:, None, :, None]) * rstd[:, None, :, None]
+    y = xh.reshape(B, H, W, C) * gamma.float() + beta.float()
+    if silu_act:
+        y = F.silu(y)
+    return y.to(x.dtype), mean.reshape(-1), rstd.reshape(-1)
+
+
+@group_norm_fwd.register_fake
+def _(x, gamma, beta, groups, eps, silu_act):
+    s = x.new_empty(x.shape[0] * groups, dtype=torch.float32)
+    return torch.empty_like(x), s, torch.empty_like(s)
+
+
+@torch.library.custom_op("pfeife::group_norm_bwd", mutates_args=())
+def group_norm_bwd(dy: Tensor, x: Tensor, mean: Tensor, rstd: Tensor, gamma: Tensor, beta: Tensor,
+                   groups: int, silu_act: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    if _native(x):
+        return kx.groupnorm_bwd(dy, x, mean, rstd, gamma, beta, groups, silu_act)
+    B, H, W, C = x.shape
+    cpg = C // groups
+    xf = x.float().reshape(B, H * W, groups, cpg)
+    xh = (xf - mean.view(B, 1, groups, 1)) * rstd.view(B, 1, groups, 1)
+    g = gamma.float().view(1, 1, groups, cpg)
+    dz = dy.float().reshape(B, H * W, groups, cpg)
+    if silu_act:
+        z = xh * g + beta.float().view(1, 1, groups, cpg)
+        dz = dz * _dact_ref(z, ACT_SILU)
+    dgamma = (dz * xh).sum((0, 1)).reshape(C)
+    dbeta = dz.sum((0, 1)).reshape(C)
+    dzg = dz * g
+    n = H * W * cpg
+    a = dzg.sum((1, 3), keepdim=True) / n
+    b = (dzg * xh).sum((1, 3), keepdim=True) / n
+    dx = rstd.view(B, 1, groups, 1) * (dzg - a - xh * b)
+    return dx.reshape(B, H, W, C).to(x.dtype), dgamma, dbeta
+
+
+@group_norm_bwd.register_fake
+def _(dy, x, mean, rstd, gamma, beta, groups, silu_act):
+    C = x.shape[-1]
+    return (torch.empty_like(x), x.new_empty(C, dtype=torch.float32),
+            x.new_empty(C, dtype=torch.float32))
+
+
+def _gn_setup(ctx, inputs, output):
+    x, gamma, beta, groups, eps, silu_act = inputs
+    ctx.save_for_backward(x, output[1], output[2], gamma, beta)
+    ctx.groups, ctx.silu_act = groups, silu_act
+
+
+def _gn_backward(ctx, dy, dmean, drstd):
+    x, mean, rstd, gamma, beta = ctx.saved_tensors
+    dx, dg, db = group_norm_bwd(dy.contiguous(), x, mean, rstd, gamma, beta, ctx.groups,
+                                ctx.silu_act)
+    return dx, dg.to(gamma.dtype), db.to(beta.dtype), None, None, None
+
+
+group_norm_fwd.register_autograd(_gn_backward, setup_context=_gn_setup)
+
+
+def group_norm(x: Tensor, weight: Tensor, bias: Tensor, groups: int = 32, eps: float = 1e-5,
+               silu: bool = False) -> Tensor:
+    """GroupNorm over an NHWC tensor, optionally followed by SiLU in the same kernel."""
+    return group_norm_fwd(x, weight, bias, groups, eps, silu)[0]
+
+
+@torch.library.custom_op("pfeife::upsample2x_op", mutates_args=())
+def upsample2x_op(x: Tensor, backward: bool) -> Tensor:
+    if _native(x) and x.shape[-1] % 8 == 0:
+        return kx.upsample2x(x, backward)
+    if not backward:
+        return x.repeat_interleave(2, 1).repeat_interleave(2, 2)
+    B, H2, W2, C = x.shape
+    return x.float().reshape(B, H2 // 2, 2, W2 // 2, 2, C).sum((2, 4)).to(x.dtype)
+
+
+@upsample2x_op.register_fake
+def _(x, backward):
+    B, H, W, C = x.shape
+    return x.new_empty((B, H // 2, W // 2, C) if backward else (B, 2 * H, 2 * W, C))
+
+
+upsample2x_op.register_autograd(
+    lambda ctx, dy: (upsample2x_op(dy.contiguous(), not ctx.backward), None),
+    setup_context=lambda ctx, inputs, output: setattr(ctx, "backward", inputs[1]))
+
+
+def upsample_nearest2x(x: Tensor) -> Tensor:
+    return upsample2x_op(x, False)

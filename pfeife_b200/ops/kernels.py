@@ -395,3 +395,71 @@ def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                         dt(q.dtype), ptr(status_word(q.device)), sm_count(q.device), stream()),
           "pf_attn_bwd")
     return dq, dk, dv
+
+
+# --------------------------------------------------------------------------- UNet kernels (NHWC)
+def im2col(x: torch.Tensor, KH: int, KW: int, stride: int, pad: int) -> torch.Tensor:
+    L = _lib.lib()
+    B, H, W, C = x.shape
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    cols = torch.empty((B * Ho * Wo, KH * KW * C), dtype=x.dtype, device=x.device)
+    check(L.pf_im2col(ptr(x.contiguous()), ptr(cols), B, H, W, C, KH, KW, Ho, Wo, stride, pad,
+                      c_ll(cols.stride(0)), dt(x.dtype), sm_count(x.device), stream()), "pf_im2col")
+    return cols
+
+
+def col2im(dcols: torch.Tensor, shape, KH: int, KW: int, stride: int, pad: int) -> torch.Tensor:
+    L = _lib.lib()
+    B, H, W, C = shape
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    dx = torch.empty(shape, dtype=dcols.dtype, device=dcols.device)
+    check(L.pf_col2im(ptr(dcols), ptr(dx), B, H, W, C, KH, KW, Ho, Wo, stride, pad,
+                      c_ll(dcols.stride(0)), dt(dcols.dtype), sm_count(dcols.device), stream()),
+          "pf_col2im")
+    return dx
+
+
+def groupnorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, groups: int,
+                  eps: float, silu: bool):
+    """x NHWC [B, H, W, C] -> (y, mean[B*G], rstd[B*G])."""
+    L = _lib.lib()
+    x = x.contiguous()
+    B, H, W, C = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(B * groups, dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    check(L.pf_groupnorm_fwd(ptr(x), ptr(gamma.float()), ptr(beta.float()), ptr(y), ptr(mean),
+                             ptr(rstd), B, H * W, C, groups, c_f(eps), int(silu), dt(x.dtype),
+                             sm_count(x.device), stream()), "pf_groupnorm_fwd")
+    return y, mean, rstd
+
+
+def groupnorm_bwd(dy, x, mean, rstd, gamma, beta, groups: int, silu: bool):
+    L = _lib.lib()
+    x, dy = x.contiguous(), dy.contiguous()
+    B, H, W, C = x.shape
+    dx = torch.empty_like(x)
+    dgamma = torch.zeros(C, dtype=torch.float32, device=x.device)
+    dbeta = torch.zeros(C, dtype=torch.float32, device=x.device)
+    sums = torch.empty(2 * B * groups, dtype=torch.float32, device=x.device)
+    check(L.pf_groupnorm_bwd(ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma.float()),
+                             ptr(beta.float()), ptr(dx), ptr(dgamma), ptr(dbeta), ptr(sums), B,
+                             H * W, C, groups, int(silu), dt(x.dtype), sm_count(x.device),
+                             stream()), "pf_groupnorm_bwd")
+    return dx, dgamma, dbeta
+
+
+def upsample2x(x: torch.Tensor, backward: bool = False) -> torch.Tensor:
+    L = _lib.lib()
+    x = x.contiguous()
+    B, H, W, C = x.shape
+    if backward:
+        H, W = H // 2, W // 2
+        y = torch.empty((B, H, W, C), dtype=x.dtype, device=x.device)
+    else:
+        y = torch.empty((B, 2 * H, 2 * W, C), dtype=x.dtype, device=x.device)
+    check(L.pf_upsample2x(ptr(x), ptr(y), B, H, W, C, int(backward), dt(x.dtype),
+                          sm_count(x.device), stream()), "pf_upsample2x")
+    return y

@@ -64,7 +64,53 @@ class PeerMemory:
                     raise _lib.KernelError(f"cudaIpcOpenMemHandle(rank {r}) failed: {code}")
                 self._opened[key] = out.value
             ptrs.append(self._opened[key] + off)
+        self._verify(t, ptrs)
         return ptrs
+
+    def _verify(self, t: torch.Tensor, ptrs: List[int]) -> None:
+        """Checks every peer mapping end to end before any kernel trusts it: each rank
+        publishes the first and last 32-bit word of its buffer, and every rank reads the same
+        two words through its mapping of that peer (a copy-engine read, which reports an
+        unmapped address as an error code)."""
+        L = _lib.lib()
+        nbytes = t.numel() * t.element_size()
+        if nbytes < 8:
+            return
+        torch.cuda.synchronize(t.device)
+
+        def peek(addr: int) -> int:
+            out = ctypes.c_uint(0)
+            code = L.pf_peek_u32(ctypes.c_void_p(addr), ctypes.byref(out))
+            if code:
+                raise _lib.KernelError(f"peer mapping unreadable at {addr:#x}: CUDA error {code}")
+            return int(out.value)
+
+        last = (nbytes - 4) // 4 * 4
+        # stamp a rank-specific signature on both ends for the duration of the check (the
+        # buffers may be all zeros, which would match any readable memory)
+        raw = t.view(-1).view(torch.uint8)
+        saved = (raw[:4].clone(), raw[last:last + 4].clone())
+        sig = torch.tensor([0xA5, 0x5A, self.rank + 1, 0xC3], dtype=torch.uint8, device=t.device)
+        raw[:4].copy_(sig)
+        raw[last:last + 4].copy_(sig.flip(0))
+        torch.cuda.synchronize(t.device)
+        mine = (peek(t.data_ptr()), peek(t.data_ptr() + last), nbytes)
+        everyone: List[Optional[Tuple[int, int, int]]] = [None] * self.size
+        dist.all_gather_object(everyone, mine, group=self.ctrl_group)
+        for r, (first_w, last_w, nb) in enumerate(everyone):
+            if r == self.rank:
+                continue
+            if nb != nbytes:
+                raise _lib.KernelError(f"rank {r} shares {nb} bytes, this rank {nbytes}")
+            got = (peek(ptrs[r]), peek(ptrs[r] + last))
+            if got != (first_w, last_w):
+                raise _lib.KernelError(
+                    f"peer mapping of rank {r} does not show that rank's data "
+                    f"(read {got}, expected {(first_w, last_w)})")
+        dist.barrier(group=self.ctrl_group)      # everyone has read before anyone restores
+        raw[:4].copy_(saved[0])
+        raw[last:last + 4].copy_(saved[1])
+        torch.cuda.synchronize(t.device)
 
 
 def _table(ptrs: List[int]):

@@ -19,19 +19,45 @@ from pfeife_b200.models.vit import ViT, vit_config  # noqa
 from pfeife_b200.utils import set_seed  # noqa
 
 
+def _clf(model, make_x, n_cls):
+    def batch(n, g):
+        return (torch.randn(make_x(n).shape, generator=g), torch.randint(0, n_cls, (n,), generator=g))
+
+    def loss(call, x, y):
+        return F.cross_entropy(call(x).float(), y)
+    return model, batch, loss
+
+
 def build(name):
+    """-> (model, make_batch(n, generator) -> tensors, loss(callable_model, *tensors))."""
     if name == "mlp":
-        return DeepMLP(16, 8, 10), (lambda n: torch.randn(n, 16)), 10
+        return _clf(DeepMLP(16, 8, 10), (lambda n: torch.randn(n, 16)), 10)
     if name == "tied":
-        return TiedMLP(10, 3), (lambda n: torch.randn(n, 10)), 10
+        return _clf(TiedMLP(10, 3), (lambda n: torch.randn(n, 10)), 10)
     if name == "skip":
-        return SkipNet(16, 3), (lambda n: torch.randn(n, 16)), 16
+        return _clf(SkipNet(16, 3), (lambda n: torch.randn(n, 16)), 16)
     if name == "vit_tiny":
-        cfg = vit_config("vit_tiny")
-        return ViT(cfg), (lambda n: torch.randn(n, 3, 224, 224)), 10
+        return _clf(ViT(vit_config("vit_tiny")), (lambda n: torch.randn(n, 3, 224, 224)), 10)
     if name == "vit_small":
         cfg = vit_config("vit_tiny", num_layers=4, image_size=32, patch_size=8)
-        return ViT(cfg), (lambda n: torch.randn(n, 3, 32, 32)), 10
+        return _clf(ViT(cfg), (lambda n: torch.randn(n, 3, 32, 32)), 10)
+    if name == "llama_tiny":
+        from pfeife_b200.models.llama import Llama, causal_lm_loss, llama_config
+        model = Llama(llama_config("llama_tiny", tie_embeddings=True))
+        return (model, lambda n, g: (torch.randint(0, 256, (n, 16), generator=g),),
+                lambda call, ids: causal_lm_loss(call(ids).float(), ids))
+    if name == "unet_tiny":
+        from pfeife_b200.models.unet import UNet, unet_config
+        model = UNet(unet_config("unet_tiny"))
+
+        def batch(n, g):
+            r = lambda *s: torch.randn(*s, generator=g)
+            return (r(n, 4, 16, 16), torch.randint(0, 1000, (n,), generator=g), r(n, 7, 32),
+                    r(n, 16), r(n, 6), r(n, 4, 16, 16))
+
+        def loss(call, lat, t, txt, pooled, ids, noise):
+            return F.mse_loss(call(lat, t, txt, pooled, ids).float(), noise)
+        return model, batch, loss
     raise ValueError(name)
 
 
@@ -50,7 +76,7 @@ def main():
     state = initialize_pfeife()
     option = PipeOption.from_args(args)
     set_seed(0)
-    model, make_x, n_cls = build(args.model)
+    model, make_batch, loss_fn = build(args.model)
     ref = copy.deepcopy(model)
     dev = state.device
     model.to(dev)
@@ -64,8 +90,8 @@ def main():
     runner = PartialRunner(option, opt)
     cm = torch.compile(model, backend=partial_compiler)
 
-    def exec_fn(x, y):
-        loss = F.cross_entropy(cm(x).float(), y)
+    def exec_fn(*batch):
+        loss = loss_fn(cm, *batch)
         loss.backward()
         return loss.detach().cpu()
 
@@ -74,24 +100,23 @@ def main():
     g = torch.Generator().manual_seed(100 + state.dp_rank)
     losses, ref_losses = [], []
     for step in range(args.steps):
-        x = torch.randn(make_x(n).shape, generator=g)
-        y = torch.randint(0, n_cls, (n,), generator=g)
-        out = runner.step(x.to(dev), y.to(dev))
+        batch = make_batch(n, g)
+        out = runner.step(*[t.to(dev) for t in batch])
         losses.append([float(l) for l in out])
         sched.step()
         if state.dp_size == 1:
             ropt.zero_grad()
             cur = []
-            for xs, ys in zip(x.chunk(option.batch_cnt), y.chunk(option.batch_cnt)):
-                l = F.cross_entropy(ref(xs), ys)
+            for mb in zip(*[t.chunk(option.batch_cnt) for t in batch]):
+                l = loss_fn(ref, *mb)
                 l.backward()
-                cur.append(float(l))
+                cur.append(float(l.detach()))
             ropt.step()
             rsched.step()
             ref_losses.append(cur)
     result = {"losses": losses, "ref_losses": ref_losses}
     if args.check_eval:
-        x = make_x(n)
+        x = make_batch(n, g)[0]
         runner.set_exec_fn(lambda x: cm(x).detach().cpu())
         got = runner.eval_step(x.to(dev))
         runner.gather_params()

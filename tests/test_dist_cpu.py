@@ -73,3 +73,15 @@ def test_dp2_x_pp2_replicas_stay_identical(tmp_path):
         other = json.load(f)
     assert res["param_checksum"] == pytest.approx(other["param_checksum"], rel=1e-9)
     assert res["losses"] != other["losses"]      # replicas saw different data
+
+
+def test_llama_tied_embeddings_looped(tmp_path):
+    res, _ = launch(tmp_path, 2, ["--model", "llama_tiny", "--device_cnt", "2", "--batch_size", "2",
+                                  "--batch_cnt", "4", "--steps", "2"])
+    assert_equal_training(res, tol=1e-5)
+
+
+def test_unet_long_skip_edges_and_many_inputs(tmp_path):
+    res, _ = launch(tmp_path, 2, ["--model", "unet_tiny", "--device_cnt", "2", "--batch_size", "2",
+                                  "--batch_cnt", "4", "--steps", "2"])
+    assert_equal_training(res, tol=1e-5)
