@@ -270,7 +270,7 @@ class PartialModule(torch.nn.Module):
                              "optimizer_type": opt_type, "hyper": hyper, "steps": steps,
                              "eval_steps": eval_steps, "batch_cnt": opt.batch_cnt})
         mine = r.ctrl.scatter(payloads)
-        _install_plan(r.worker, state, mine)
+        r.install_plan(mine)
         r.ctrl.barrier()
         self.compiled = True
         # the user's module keeps its Parameter objects; they are refreshed by gather_params()
@@ -313,19 +313,31 @@ class PartialRunner:
         global _current_runner
         self.option = option
         self.optimizer = optimizer
-        self.state = get_state()
-        if not self.state.is_main_rank:
-            raise RuntimeError("PartialRunner belongs to the main rank of a pipeline; other "
-                               "ranks call worker_loop() (mp_launch.py does)")
         self.log = get_logger()
-        self.ctrl = ControlPlane(self.state)
         self.modules: List[PartialModule] = []
         self.exec_fn: Optional[Callable] = None
         self.batch_cnt = option.batch_cnt
         _current_runner = self
+        self._setup_runtime()
+        self._start_threads()
+
+    def _setup_runtime(self) -> None:
+        """Process-per-GPU runtime: topology from ``initialize_pfeife``, control plane over
+        gloo, one StageWorker for this rank."""
+        option = self.option
+        self.state = get_state()
+        if not self.state.is_main_rank:
+            raise RuntimeError("PartialRunner belongs to the main rank of a pipeline; other "
+                               "ranks call worker_loop() (mp_launch.py does)")
+        self.ctrl = ControlPlane(self.state)
         self.ctrl.bcast(option)
         self.worker = _make_worker(self.state, option, runner=self)
         self.device_bench = _run_device_bench(self.state, option)
+
+    def install_plan(self, payload: Dict[str, Any]) -> None:
+        _install_plan(self.worker, self.state, payload)
+
+    def _start_threads(self) -> None:
         self._train_queues = [queue.Queue() for _ in range(self.batch_cnt)]
         self._return_queues = [queue.Queue() for _ in range(self.batch_cnt)]
         self._module_queues = [queue.Queue() for _ in range(self.batch_cnt)]
