@@ -178,7 +178,48 @@ class PipeGraph:
         return Simulation(max(ends) if ends else 0.0, busy, ends, order, starts)
 
     def get_value(self, sched: PipeSchedParams) -> float:
-        return self.simulate(sched).makespan
+        """Makespan in ms.  Uses the C++ evaluator when the host library is built, otherwise
+        the Python simulation above (the oracle)."""
+        v = self._native_value(sched)
+        return self.simulate(sched).makespan if v is None else v
+
+    def _native_value(self, sched: PipeSchedParams) -> Optional[float]:
+        import ctypes
+        from ..ops import _lib
+        host = _lib.host_lib()
+        if host is None:
+            return None
+        fn = host.pf_sim_schedule
+        fn.restype = ctypes.c_double
+        cache = getattr(sched, "_flat", None)
+        if cache is None:
+            off, st, mb, fw = [0], [], [], []
+            for works in sched.rank_works:
+                for s, b, f in works:
+                    st.append(s)
+                    mb.append(b)
+                    fw.append(1 if f else 0)
+                off.append(len(st))
+            cache = ((ctypes.c_int * len(off))(*off), (ctypes.c_int * len(st))(*st),
+                     (ctypes.c_int * len(mb))(*mb), (ctypes.c_uint8 * len(fw))(*fw))
+            sched._flat = cache
+        n, D, E = len(self.nodes), self.device_cnt, len(self.edges)
+        dbl = lambda xs: (ctypes.c_double * max(1, len(xs)))(*xs)
+        ints = lambda xs: (ctypes.c_int * max(1, len(xs)))(*xs)
+        optim = [0.0] * D
+        for nd in self.nodes:
+            optim[nd.rank] += nd.optim_time
+        v = fn(D, n, sched.batch_cnt, dbl([x.comp_time for x in self.nodes]),
+               dbl([x.back_time for x in self.nodes]), dbl(optim),
+               ints([x.rank for x in self.nodes]), E, ints([e.start for e in self.edges]),
+               ints([e.end for e in self.edges]),
+               dbl([0.0 if self.nodes[e.start].rank == self.nodes[e.end].rank else e.send_time
+                    for e in self.edges]),
+               cache[0], cache[1], cache[2], cache[3], None)
+        if v < 0:
+            raise RuntimeError("schedule deadlocks: a work item waits on an input that is "
+                               "never produced")
+        return float(v)
 
     # ------------------------------------------------------------------ printing
     def describe(self) -> str:
