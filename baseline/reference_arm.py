@@ -138,4 +138,9 @@ def run(args) -> int:
     emit_result(args, impl="reference", n_gpus=world, ms=ms, ms_e2e=ms_e2e, samples=n,
                 clocks=clocks, launches=None, parallelism=f"pp{world}",
                 h2d=host_x.numel() * 4 + host_y.numel() * 8, d2h=4)
-    os._exit(0)   # the reference's atexit teardown can block on its own workers
+    sys.stdout.flush()
+    try:
+        runner.worker.destroy_workers()   # the reference's own shutdown broadcast (its atexit hook)
+    except Exception:
+        pass
+    os._exit(0)

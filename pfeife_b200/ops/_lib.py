@@ -25,6 +25,7 @@ _tried = False
 _launches = 0  # kernels launched through this module (reported by bench.py)
 
 PF_F32, PF_F16, PF_BF16 = 0, 1, 2
+_tls = threading.local()
 _DT = {torch.float32: PF_F32, torch.float16: PF_F16, torch.bfloat16: PF_BF16}
 
 
@@ -77,10 +78,14 @@ def use_kernels(t: torch.Tensor) -> bool:
 
 
 def ptr(t: Optional[torch.Tensor]):
-    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
-
-
-_tls = threading.local()
+    """Device pointer of `t` (NULL for None).  Also remembers, per thread, the device of the
+    last tensor seen, which is the device ``stream()`` launches on: a thread's *current* torch
+    device is not reliable (new Python threads start on device 0)."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    if t.is_cuda:
+        _tls.op_device = t.device.index
+    return ctypes.c_void_p(t.data_ptr())
 
 
 def bind_thread(device_index: Optional[int] = None) -> None:
@@ -94,10 +99,16 @@ def bind_thread(device_index: Optional[int] = None) -> None:
         _tls.dev = idx
 
 
-def stream() -> ctypes.c_void_p:
-    """Current torch stream handle; also binds the calling thread to the current device."""
-    bind_thread()
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+def stream(device: Optional[int] = None) -> ctypes.c_void_p:
+    """Handle of the torch stream that is current for the device of the operands (the device
+    of the last tensor passed through ``ptr`` in this thread); binds the calling thread of the
+    library's own CUDA runtime to that device."""
+    if device is None:
+        device = getattr(_tls, "op_device", None)
+    if device is None:
+        device = torch.cuda.current_device()
+    bind_thread(device)
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
 _sm_count_cache = {}

@@ -445,6 +445,8 @@ class PartialRunner:
     # ---- threads
     def _exec_loop(self, bid: int) -> None:
         _tls.mb = bid
+        if self.state.device.type == "cuda":
+            torch.cuda.set_device(self.state.device)   # new threads start on device 0
         while True:
             item = self._train_queues[bid].get()
             if item is None:

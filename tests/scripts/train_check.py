@@ -13,7 +13,7 @@ import torch.nn.functional as F
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
-from pfeife_b200 import PartialRunner, PipeOption, initialize_pfeife, partial_compiler  # noqa
+from pfeife_b200 import PartialRunner, PipeOption, initialize_pfeife, ops, partial_compiler  # noqa
 from pfeife_b200.models.toy import DeepMLP, SkipNet, TiedMLP  # noqa
 from pfeife_b200.models.vit import ViT, vit_config  # noqa
 from pfeife_b200.utils import set_seed  # noqa
@@ -24,7 +24,8 @@ def _clf(model, make_x, n_cls):
         return (torch.randn(make_x(n).shape, generator=g), torch.randint(0, n_cls, (n,), generator=g))
 
     def loss(call, x, y):
-        return F.cross_entropy(call(x).float(), y)
+        # the fused loss kernel runs in the front-end threads on GPU ranks
+        return ops.cross_entropy(call(x).float(), y)
     return model, batch, loss
 
 
