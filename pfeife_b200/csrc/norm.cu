@@ -422,3 +422,41 @@ PF_API int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const v
   PF_CHECK_LAUNCH();
   return 0;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+#include "no_alloc.h"
+
+// Partial dgamma / dbeta sums of pf_norm_bwd_static.  One copy per device that loads the
+// library; shared by every call on that device.
+static __device__ __align__(256) float g_norm_static_scratch[PF_NORM_STATIC_SCRATCH_FLOATS];
+
+// In host code `g_norm_static_scratch` is only a handle for the runtime's symbol table, not
+// a device address; the address is queried once per device, with that device current.
+static float* norm_static_scratch_ptr(int* err) {
+  static float* ptrs[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) { *err = e != cudaSuccess ? (int)e : -3; return nullptr; }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_norm_static_scratch);
+    if (e != cudaSuccess) { *err = (int)e; return nullptr; }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  *err = 0;
+  return ptrs[dev];
+}
+
+PF_API int pf_norm_bwd_static(const void* dy, const void* h, const void* gamma, const void* mean,
+                              const void* rstd, const void* dres, void* dx, void* dgamma,
+                              void* dbeta, long long rows, int N, int rms, int accumulate,
+                              int dtype, int sm_count, void* stream) {
+  if (rows <= 0) return 0;
+  const long long need = (long long)pf_norm_bwd_ctas(rows, sm_count) * 2 * N;
+  if (need > PF_NORM_STATIC_SCRATCH_FLOATS) return -3;   // beyond the built-in scratch
+  int err = 0;
+  float* scratch = norm_static_scratch_ptr(&err);
+  if (!scratch) return err;
+  return pf_norm_bwd(dy, h, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, rows, N, rms,
+                     accumulate, dtype, sm_count, stream);
+}
