@@ -191,6 +191,38 @@ colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, 
   }
 }
 
+// Same reduction for 16-bit inputs whose pitch allows 16-byte loads: a CTA owns 256 columns
+// (lane = 8 consecutive columns) and a slab of rows split over its 8 warps.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+                  long long ld, int rows_per_cta) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_cta;
+  const long long r1 = min(rows, r0 + rows_per_cta);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c0 < cols) {
+    for (long long r = r0 + warp; r < r1; r += 8) {
+      const uint4 q = *reinterpret_cast<const uint4*>(x + r * ld + c0);
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    atomicAdd(out + c, t);
+  }
+}
+
 // 16-bit tiled transpose: dst[c, r] = src[r, c]
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -305,6 +337,22 @@ PF_API int pf_colsum(const void* x, void* out_f32, long long rows, int cols, lon
                      int dtype, int sm_count, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype != PF_F32 && cols % 8 == 0 && ld % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int gxv = (cols + 255) / 256;
+    int gyv = ((sm_count > 0 ? sm_count : 148) * 4 + gxv - 1) / gxv;
+    int per = (int)((rows + gyv - 1) / gyv);
+    if (per < 32) per = 32;
+    gyv = (int)((rows + per - 1) / per);
+    if (dtype == PF_F16)
+      colsum_vec_kernel<__half><<<dim3(gxv, gyv), 256, 0, st>>>((const __half*)x, (float*)out_f32,
+                                                                rows, cols, ld, per);
+    else
+      colsum_vec_kernel<__nv_bfloat16><<<dim3(gxv, gyv), 256, 0, st>>>(
+          (const __nv_bfloat16*)x, (float*)out_f32, rows, cols, ld, per);
+    PF_CHECK_LAUNCH();
+    return 0;
+  }
   const int gx = (cols + 31) / 32;
   int gy = ((sm_count > 0 ? sm_count : 148) * 4 + gx - 1) / gx;
   if (gy < 1) gy = 1;

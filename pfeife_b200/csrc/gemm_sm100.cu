@@ -12,8 +12,9 @@
 // pre-activation to `aux`), multiply by gelu'(aux) (dGELU), + residual[m,n], accumulate into C
 // (fp32 gradient buckets), cast to the output dtype.
 //
-// Role layout of the 192-thread CTA: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and
-// MMA issuer (one lane), warps 2..5 = epilogue (one accumulator row per thread).
+// Role layout of the 320-thread CTA: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and
+// MMA issuer (one lane), warps 2..9 = epilogue (one accumulator row per thread; two warps share a
+// TMEM lane quadrant and split the tile's columns, which halves the epilogue latency per tile).
 #include "common.cuh"
 #include "api.h"
 
@@ -22,7 +23,8 @@ namespace pf {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;       // 64 x 16-bit = one 128 B swizzle row
 constexpr int GEMM_UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 8;     // two warps per TMEM lane quadrant, half the columns each
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
 enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_GELU_TANH = 3, EPI_DGELU_TANH = 4,
                  EPI_SILU = 5 };
@@ -132,7 +134,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 128);
+      mbar_init(&tmem_empty[i], 32 * GEMM_EPI_WARPS);
     }
     mbar_fence_init();
   }
@@ -224,6 +226,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int col_half = (warp - 2) >> 2;          // which half of the tile's columns
+    const int c_begin = col_half * (BN / 2), c_end = c_begin + BN / 2;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -241,9 +245,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         const int col = n0 + c;
-        if (col >= p.N) break;  // uniform across the CTA
+        if (col >= p.N) break;  // uniform across the warp
         uint32_t raw[32];
         tmem_ld32(t_row + c, raw);
         tmem_ld_wait();

@@ -125,8 +125,8 @@ embed_bwd_kernel(const T* __restrict__ dout, const long long* __restrict__ ids,
     atomicAdd(dtable + id * D + i, to_f32<T>(dout[t * D + i]));
 }
 
-// Rotary embedding on x[B, S, H, D] (half-split convention: pairs (i, i + D/2)), in place or
-// out of place.  inverse != 0 applies the transpose rotation (the backward).
+// Rotary embedding on a (possibly strided) x[B, S, H, D] (half-split convention: pairs
+// (i, i + D/2)) into a contiguous output.  inverse != 0 applies the transpose rotation (the backward).
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cos_t,
@@ -147,8 +147,10 @@ rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restric
     if (inverse) sn = -sn;
     const float x1 = to_f32<T>(x[off + d]);
     const float x2 = to_f32<T>(x[off + d + half]);
-    out[off + d] = from_f32<T>(x1 * c - x2 * sn);
-    out[off + d + half] = from_f32<T>(x2 * c + x1 * sn);
+    // the output is always contiguous [B, S, H, D]
+    const long long oo = ((b * S + s) * H + h) * (long long)D;
+    out[oo + d] = from_f32<T>(x1 * c - x2 * sn);
+    out[oo + d + half] = from_f32<T>(x2 * c + x1 * sn);
   }
 }
 

@@ -199,6 +199,196 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* 
   }
 }
 
+// Forward for rows of up to 2048 16-bit elements: one warp per row, the row in registers,
+// shuffle reductions only (no CTA barrier), 8 rows per CTA.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                     const float* __restrict__ gamma, const float* __restrict__ beta,
+                     T* __restrict__ y, T* __restrict__ h_out, float* __restrict__ mean_out,
+                     float* __restrict__ rstd_out, long long rows, int N, float eps, int rms) {
+  constexpr int V = 8;
+  const int nvec = N / V;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float v[NV][V];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      uint4 q = reinterpret_cast<const uint4*>(x + row * N)[idx];
+      const T* e = reinterpret_cast<const T*>(&q);
+      if (res) {
+        uint4 qr = reinterpret_cast<const uint4*>(res + row * N)[idx];
+        const T* er = reinterpret_cast<const T*>(&qr);
+        uint4 qh;
+        T* eh = reinterpret_cast<T*>(&qh);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          eh[j] = from_f32<T>(to_f32<T>(e[j]) + to_f32<T>(er[j]));
+          v[i][j] = to_f32<T>(eh[j]);
+        }
+        if (h_out) reinterpret_cast<uint4*>(h_out + row * N)[idx] = qh;
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = to_f32<T>(e[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += v[i][j];
+    }
+  }
+  const float mean = rms ? 0.f : warp_sum(s) / N;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + i * 32 < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) { const float d = v[i][j] - mean; sq += d * d; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / N + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V));
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V) + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (beta) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + idx * V));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + idx * V) + 1);
+        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
+        b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      }
+      uint4 q;
+      T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+      for (int j = 0; j < V; ++j) e[j] = from_f32<T>((v[i][j] - mean) * rstd * g[j] + b[j]);
+      reinterpret_cast<uint4*>(y + row * N)[idx] = q;
+    }
+  }
+}
+
+// Backward, input gradient only: one warp per row, packed dy / h kept in registers, two
+// shuffle reductions.  The parameter gradients come from norm_bwd_param_kernel.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ h,
+                   const float* __restrict__ gamma, const float* __restrict__ mean,
+                   const float* __restrict__ rstd, const T* __restrict__ dres,
+                   T* __restrict__ dx, long long rows, int N, int rms) {
+  constexpr int V = 8;
+  const int nvec = N / V;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float mu = rms ? 0.f : mean[row];
+  const float rs = rstd[row];
+  uint4 qd[NV], qh[NV];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      qd[i] = reinterpret_cast<const uint4*>(dy + row * N)[idx];
+      qh[i] = reinterpret_cast<const uint4*>(h + row * N)[idx];
+      const T* ed = reinterpret_cast<const T*>(&qd[i]);
+      const T* eh = reinterpret_cast<const T*>(&qh[i]);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V));
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V) + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float dyg = to_f32<T>(ed[j]) * g[j];
+        s1 += dyg;
+        s2 += dyg * (to_f32<T>(eh[j]) - mu) * rs;
+      }
+    }
+  }
+  const float m1 = rms ? 0.f : warp_sum(s1) / N;
+  const float m2 = warp_sum(s2) / N;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      const T* ed = reinterpret_cast<const T*>(&qd[i]);
+      const T* eh = reinterpret_cast<const T*>(&qh[i]);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V));
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + idx * V) + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      uint4 qr;
+      if (dres) qr = reinterpret_cast<const uint4*>(dres + row * N)[idx];
+      const T* er = reinterpret_cast<const T*>(&qr);
+      uint4 q;
+      T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float xhat = (to_f32<T>(eh[j]) - mu) * rs;
+        float o = rs * (to_f32<T>(ed[j]) * g[j] - m1 - xhat * m2);
+        if (dres) o += to_f32<T>(er[j]);
+        e[j] = from_f32<T>(o);
+      }
+      reinterpret_cast<uint4*>(dx + row * N)[idx] = q;
+    }
+  }
+}
+
+// dgamma[c] += sum_r dy[r,c] * xhat[r,c] ; dbeta[c] += sum_r dy[r,c].  Each CTA owns 256
+// columns (lane = 8 consecutive columns, 16-byte loads) and a slab of rows split over its 8
+// warps; warps are combined through shared memory and the CTA writes its partial sums to the
+// scratch buffer, which norm_bwd_finish_kernel folds (deterministic, nothing to zero).
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_bwd_param_kernel(const T* __restrict__ dy, const T* __restrict__ h,
+                      const float* __restrict__ mean, const float* __restrict__ rstd,
+                      float* __restrict__ scratch, long long rows, int N, int rows_per_cta,
+                      int rms) {
+  __shared__ float red[2][8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_cta;
+  const long long r1 = min(rows, r0 + rows_per_cta);
+  float ag[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c0 < N) {
+    for (long long r = r0 + warp; r < r1; r += 8) {
+      const float mu = rms ? 0.f : mean[r];
+      const float rs = rstd[r];
+      const uint4 qd = *reinterpret_cast<const uint4*>(dy + r * N + c0);
+      const uint4 qh = *reinterpret_cast<const uint4*>(h + r * N + c0);
+      const T* ed = reinterpret_cast<const T*>(&qd);
+      const T* eh = reinterpret_cast<const T*>(&qh);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = to_f32<T>(ed[j]);
+        ag[j] += d * (to_f32<T>(eh[j]) - mu) * rs;
+        ab[j] += d;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    red[0][warp][lane * 8 + j] = ag[j];
+    red[1][warp][lane * 8 + j] = ab[j];
+  }
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float g = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { g += red[0][w][threadIdx.x]; b += red[1][w][threadIdx.x]; }
+    // partial sums of this row slab: scratch[slab][0][c] (dgamma), scratch[slab][1][c] (dbeta)
+    scratch[((long long)blockIdx.y * 2) * N + c] = g;
+    scratch[((long long)blockIdx.y * 2 + 1) * N + c] = b;
+  }
+}
+
 // Backward for rows of up to 2048 16-bit elements: one WARP per row (no CTA-wide barrier on the
 // row path), 8 warps per CTA, rows strided over a persistent grid.  Each lane keeps the packed
 // dy / h vectors of its row slice in registers, expands them twice (reduction pass, output
@@ -325,6 +515,18 @@ static int norm_fwd_launch(const void* x, const void* res, const float* gamma, c
   constexpr int V = 16 / sizeof(T);
   if (N % V) return -2;
   const int nvec = N / V;
+  if (sizeof(T) == 2 && nvec <= 32 * 8) {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+#define PF_NORM_FWD_WARP(NV)                                                                  \
+    norm_fwd_warp_kernel<T, NV><<<grid, 256, 0, st>>>((const T*)x, (const T*)res, gamma, beta, \
+        (T*)y, (T*)h_out, mean, rstd, rows, N, eps, rms)
+    if (nvec <= 32 * 2) PF_NORM_FWD_WARP(2);
+    else if (nvec <= 32 * 4) PF_NORM_FWD_WARP(4);
+    else if (nvec <= 32 * 6) PF_NORM_FWD_WARP(6);
+    else PF_NORM_FWD_WARP(8);
+#undef PF_NORM_FWD_WARP
+    return 0;
+  }
   if (nvec <= 128 * NORM_MAX_VEC)
     norm_fwd_kernel<T, 128><<<(unsigned)rows, 128, 0, st>>>((const T*)x, (const T*)res, gamma,
         beta, (T*)y, (T*)h_out, mean, rstd, N, eps, rms);
@@ -341,22 +543,29 @@ static int norm_fwd_launch(const void* x, const void* res, const float* gamma, c
 
 template <typename T>
 static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, const float* mean,
-                           const float* rstd, const void* dres, void* dx, float* scratch, int G,
+                           const float* rstd, const void* dres, void* dx, float* scratch, int& G,
                            long long rows, int N, int rms, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   if (N % V) return -2;
   const int nvec = N / V;
   if (sizeof(T) == 2 && nvec <= 32 * 8) {
-    const size_t smem = 2 * (size_t)N * sizeof(float);
-    if (nvec <= 32 * 3)
-      norm_bwd_warp_kernel<T, 3><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
-          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
-    else if (nvec <= 32 * 6)
-      norm_bwd_warp_kernel<T, 6><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
-          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
-    else
-      norm_bwd_warp_kernel<T, 8><<<G, 256, smem, st>>>((const T*)dy, (const T*)h, gamma, mean,
-          rstd, (const T*)dres, (T*)dx, scratch, rows, N, rms);
+    // input gradient: warp per row; parameter gradients: column reduction over row slabs
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+#define PF_NORM_BWD_DX(NV)                                                                   \
+    norm_bwd_dx_kernel<T, NV><<<grid, 256, 0, st>>>((const T*)dy, (const T*)h, gamma, mean,  \
+        rstd, (const T*)dres, (T*)dx, rows, N, rms)
+    if (nvec <= 32 * 2) PF_NORM_BWD_DX(2);
+    else if (nvec <= 32 * 4) PF_NORM_BWD_DX(4);
+    else if (nvec <= 32 * 6) PF_NORM_BWD_DX(6);
+    else PF_NORM_BWD_DX(8);
+#undef PF_NORM_BWD_DX
+    int slabs = (int)((rows + 31) / 32);
+    if (slabs > G) slabs = G;
+    const int rows_per = (int)((rows + slabs - 1) / slabs);
+    slabs = (int)((rows + rows_per - 1) / rows_per);
+    norm_bwd_param_kernel<T><<<dim3((N + 255) / 256, slabs), 256, 0, st>>>(
+        (const T*)dy, (const T*)h, mean, rstd, scratch, rows, N, rows_per, rms);
+    G = slabs;
     return 0;
   }
   if (nvec <= 128 * NORM_MAX_VEC)
@@ -408,7 +617,7 @@ PF_API int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const v
                        int sm_count, void* stream) {
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int G = pf_norm_bwd_ctas(rows, sm_count);
+  int G = pf_norm_bwd_ctas(rows, sm_count);   // rows of scratch; the launch may use fewer
   int r = -1;
   switch (dtype) {
     case PF_F32: r = norm_bwd_launch<float>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;

@@ -139,6 +139,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """Accounts for kernels launched by replaying a captured CUDA graph."""
+    global _launches
+    _launches += n
+
+
 def c_ll(v) -> ctypes.c_longlong:
     return ctypes.c_longlong(int(v))
 

@@ -323,10 +323,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool = 
     L = _lib.lib()
     assert x.dim() == 4 and x.stride(3) == 1
     B, S, H, D = x.shape
-    out = torch.empty_like(x)
-    assert out.stride() == x.stride() or x.is_contiguous()
-    if out.stride() != x.stride():
-        x = x.contiguous()
+    out = torch.empty((B, S, H, D), dtype=x.dtype, device=x.device)
     check(L.pf_rope(ptr(x), ptr(out), ptr(cos.contiguous()), ptr(sin.contiguous()), c_ll(B), S, H,
                     D, c_ll(x.stride(0)), c_ll(x.stride(1)), c_ll(x.stride(2)), int(inverse),
                     dt(x.dtype), sm_count(x.device), stream()), "pf_rope")

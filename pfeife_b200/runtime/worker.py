@@ -137,6 +137,11 @@ class CommPlan:
                 self.channel_recv[a] = msgs
 
 
+def _lib_add(n: int) -> None:
+    from ..ops import _lib
+    _lib.add_launches(n)
+
+
 class _GraphedStage:
     """CUDA graphs of one stage's forward and backward for one in-flight slot.
 
@@ -153,6 +158,8 @@ class _GraphedStage:
         self.static_outs: Tuple[Any, ...] = ()
         self.grad_outs: List[Tuple[int, torch.Tensor]] = []   # (output index, static grad)
         self.failed = False
+        self.fwd_kernels = 0     # native kernels recorded in each graph (for launch accounting)
+        self.bwd_kernels = 0
 
 
 def inflight_slots(steps: Sequence[Step]) -> Tuple[Dict[Tuple[int, int], int], int]:
@@ -373,6 +380,7 @@ class StageWorker:
                     if dst is not src and torch.is_tensor(dst):
                         dst.copy_(src, non_blocking=True)
                 gs.fwd.replay()
+                _lib_add(gs.fwd_kernels)
                 self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
                 self.fw_inputs[(stage, mb)] = gs.static_ins
                 self.fw_outputs[(stage, mb)] = gs.static_outs
@@ -418,6 +426,8 @@ class StageWorker:
         torch.cuda.synchronize(self.device)
         self.params.prepare_backward()
         mod = self.stage_mods[stage]
+        from ..ops import _lib
+        n0 = _lib.launch_count()
         fwd = torch.cuda.CUDAGraph()
         with torch.cuda.graph(fwd, pool=self.graph_pool, capture_error_mode="thread_local"):
             with gen_amp_context(self.device, self.option.mixed_precision):
@@ -427,6 +437,7 @@ class StageWorker:
         outs = tuple(outs)
         grad_outs = [(j, torch.zeros_like(o)) for j, o in enumerate(outs)
                      if torch.is_tensor(o) and o.requires_grad]
+        n1 = _lib.launch_count()
         bwd = None
         if grad_outs:
             for t in static_ins:
@@ -439,6 +450,8 @@ class StageWorker:
                 torch.autograd.backward([outs[j] for j, _ in grad_outs],
                                         [g for _, g in grad_outs])
         gs.fwd, gs.bwd = fwd, bwd
+        gs.fwd_kernels, gs.bwd_kernels = n1 - n0, _lib.launch_count() - n1
+        _lib.add_launches(-(gs.fwd_kernels + gs.bwd_kernels))   # recorded, not executed
         gs.static_ins, gs.static_outs, gs.grad_outs = static_ins, outs, grad_outs
 
     def _is_param_view(self, t: torch.Tensor) -> bool:
@@ -498,6 +511,7 @@ class StageWorker:
                     else:
                         buf.copy_(g.reshape(buf.shape), non_blocking=True)
                 gs.bwd.replay()
+                _lib_add(gs.bwd_kernels)
         elif tensors:
             self.params.prepare_backward()
             torch.autograd.backward(tensors, grads)
