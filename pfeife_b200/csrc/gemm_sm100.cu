@@ -15,6 +15,7 @@
 // Role layout of the 320-thread CTA: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and
 // MMA issuer (one lane), warps 2..9 = epilogue (one accumulator row per thread; two warps share a
 // TMEM lane quadrant and split the tile's columns, which halves the epilogue latency per tile).
+#include <cstring>
 #include "common.cuh"
 #include "api.h"
 
@@ -42,6 +43,7 @@ struct GemmParams {
   int epilogue;
   int accumulate;
   int vec_ok;     // C / residual / aux rows are 16-byte aligned at every 32-column chunk
+  int tma_store;  // outputs leave through smem staging + TMA stores (needs vec_ok)
   float alpha;
   int a_mn, b_mn;
   int fmt;        // 0 = fp16 inputs, 1 = bf16 inputs
@@ -54,7 +56,11 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+  // epilogue staging for TMA stores: per epilogue warp one [32 rows x 32 cols] box for C and one
+  // for aux (16-bit outputs) or one 4 KB box for C (fp32 outputs)
+  static constexpr int STAGING_OFFSET = BAR_OFFSET + 1024;
+  static constexpr int STAGING_PER_WARP = 4096;
+  static constexpr int TOTAL = STAGING_OFFSET + GEMM_EPI_WARPS * STAGING_PER_WARP + 1024;
 };
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
@@ -101,10 +107,30 @@ __device__ __forceinline__ void store_row32(OutT* p, bool vec, int nvalid, const
   }
 }
 
+// Writes row `r` (32 values) of a [32 x 32] staging box in the swizzled layout the TMA store
+// expects: 64-byte rows with SWIZZLE_64B for 16-bit outputs, 128-byte rows with SWIZZLE_128B
+// for fp32 outputs.  Conflict-free across the 32 lanes of a warp.
+template <typename OutT>
+__device__ __forceinline__ void stage_row32(uint8_t* box, int r, const float (&v)[32]) {
+  constexpr int PER = 16 / sizeof(OutT);
+  constexpr int NCH = 32 / PER;            // 4 (16-bit) or 8 (fp32) 16-byte chunks per row
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    uint4 q;
+    OutT* e = reinterpret_cast<OutT*>(&q);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) e[j] = from_f32<OutT>(v[c * PER + j]);
+    const int sw = (NCH == 4) ? (c ^ ((r >> 1) & 3)) : (c ^ (r & 7));
+    *reinterpret_cast<uint4*>(box + r * (NCH * 16) + sw * 16) = q;
+  }
+}
+
 template <typename OutT, int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c,
+                    const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle atoms need 1024 B alignment
@@ -235,6 +261,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     OutT* C = reinterpret_cast<OutT*>(p.C);
     const OutT* R = reinterpret_cast<const OutT*>(p.residual);
     OutT* AUX = reinterpret_cast<OutT*>(p.aux);
+    uint8_t* stage_c = smem + S::STAGING_OFFSET + (warp - 2) * S::STAGING_PER_WARP;
+    uint8_t* stage_aux = stage_c + 2048;           // only used by 16-bit outputs
+    const bool aux_out = AUX && (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH ||
+                                 p.epilogue == EPI_SILU);
+    bool stores_pending = false;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % num_m) * GEMM_BM;
       const int n0 = (tile / num_m) * BN;
@@ -251,46 +282,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t raw[32];
         tmem_ld32(t_row + c, raw);
         tmem_ld_wait();
-        if (row_ok) {
-          const int nvalid = min(32, p.N - col);
-          const bool vec = p.vec_ok != 0;
-          float v[32];
+        const int nvalid = min(32, p.N - col);
+        const bool vec = p.vec_ok != 0;
+        const bool tma_out = p.tma_store != 0;
+        float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
-          if (p.bias) {
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
+        if (p.bias) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < nvalid) v[i] += load_bias(p.bias, p.bias_dtype, col + i);
+          for (int i = 0; i < 32; ++i)
+            if (i < nvalid) v[i] += load_bias(p.bias, p.bias_dtype, col + i);
+        }
+        if (tma_out && stores_pending) {
+          // the previous chunk's TMA stores must have read the staging boxes before reuse
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          stores_pending = false;
+        }
+        if (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH || p.epilogue == EPI_SILU) {
+          if (aux_out) {
+            if (tma_out) stage_row32<OutT>(stage_aux, lane, v);
+            else if (row_ok)
+              store_row32<OutT>(AUX + (long long)row * p.ldaux + col, vec, nvalid, v);
           }
-          if (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH || p.epilogue == EPI_SILU) {
-            if (AUX) store_row32<OutT>(AUX + (long long)row * p.ldaux + col, vec, nvalid, v);
-            if (p.epilogue == EPI_GELU) {
+          if (p.epilogue == EPI_GELU) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-            } else if (p.epilogue == EPI_GELU_TANH) {
+            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+          } else if (p.epilogue == EPI_GELU_TANH) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-            } else {
+            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+          } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
-            }
-          } else if (p.epilogue == EPI_DGELU || p.epilogue == EPI_DGELU_TANH) {
-            float z[32];
-            load_row32<OutT>(AUX + (long long)row * p.ldaux + col, vec, nvalid, z);
-            if (p.epilogue == EPI_DGELU) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf(z[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= dgelu_tanh(z[i]);
-            }
+            for (int i = 0; i < 32; ++i) v[i] = silu(v[i]);
           }
-          if (R) {
-            float r[32];
-            load_row32<OutT>(R + (long long)row * p.ldr + col, vec, nvalid, r);
+        } else if ((p.epilogue == EPI_DGELU || p.epilogue == EPI_DGELU_TANH) && row_ok) {
+          float z[32];
+          load_row32<OutT>(AUX + (long long)row * p.ldaux + col, vec, nvalid, z);
+          if (p.epilogue == EPI_DGELU) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += r[i];
+            for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf(z[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= dgelu_tanh(z[i]);
           }
+        }
+        if (R && row_ok) {
+          float r[32];
+          load_row32<OutT>(R + (long long)row * p.ldr + col, vec, nvalid, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += r[i];
+        }
+        if (tma_out) {
+          // rows / columns beyond M / N are clipped by the TMA store itself
+          stage_row32<OutT>(stage_c, lane, v);
+          fence_async_smem();
+          __syncwarp();
+          const int row0 = m0 + quad * 32;
+          if (lane == 0 && row0 < p.M) {
+            if (p.accumulate) tma_reduce_add_2d(&tmap_c, stage_c, col, row0);
+            else tma_store_2d(&tmap_c, stage_c, col, row0);
+            if (aux_out) tma_store_2d(&tmap_aux, stage_aux, col, row0);
+            tma_store_commit();
+          }
+          stores_pending = true;
+        } else if (row_ok) {
           OutT* dst = C + (long long)row * p.ldc + col;
           if (p.accumulate) {
             float o[32];
@@ -309,6 +364,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   // teardown: every role reaches this point (all waits are bounded)
+  if (warp >= 2 && lane == 0 && p.tma_store) tma_store_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -352,9 +408,31 @@ int make_tmap_2d_16bit(CUtensorMap* map, const void* base, int fmt, long long in
   return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
 }
 
+// [rows, cols] output map with a 32 x 32 box; 16-bit: 64 B rows (SWIZZLE_64B), fp32: 128 B rows
+// (SWIZZLE_128B)
+static int make_tmap_out(CUtensorMap* map, const void* base, int out_dtype, long long cols,
+                         long long rows, long long ld) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -100;
+  const int es = out_dtype == PF_F32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = out_dtype == PF_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : out_dtype == PF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   out_dtype == PF_F32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
+}
+
 template <typename OutT, int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                       int sm_count, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                       const CUtensorMap& taux, const GemmParams& p, int sm_count,
+                       cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
   auto kern = gemm_tcgen05_kernel<OutT, BN, STAGES>;
   static bool configured[64] = {};  // the attribute is per device
@@ -368,7 +446,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   }
   const int num_tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, tc, taux, p);
   PF_CHECK_LAUNCH();
   return 0;
 }
@@ -388,7 +466,8 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;  // TMA needs 16-byte aligned bases and pitches
   const int fmt = in_dtype == PF_BF16 ? 1 : 0;
-  const int BN = (tile_n == 128 || tile_n == 256) ? tile_n : (N <= 128 ? 128 : 256);
+  const int tn = tile_n & 1023;     // bit 10 of tile_n forces the direct-store epilogue (tests)
+  const int BN = (tn == 128 || tn == 256) ? tn : (N <= 128 ? 128 : 256);
 
   CUtensorMap ta, tb;
   int r;
@@ -412,12 +491,25 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0);
   };
   p.vec_ok = aligned(C, ldc) && aligned(residual, ldr) && aligned(aux, ldaux);
+  // TMA-store epilogue: needs aligned outputs; fp32 accumulation uses the reduce-add store,
+  // 16-bit accumulation (unused by the framework) stays on the direct path
+  p.tma_store = p.vec_ok && !(accumulate && out_dtype != PF_F32) && !(tile_n & 1024) &&
+                !(aux && out_dtype == PF_F32);
+  CUtensorMap tc, taux;
+  memset(&tc, 0, sizeof(tc));
+  memset(&taux, 0, sizeof(taux));
+  if (p.tma_store) {
+    if ((r = make_tmap_out(&tc, C, out_dtype, N, M, ldc))) return r;
+    const bool aux_is_out = aux && (epilogue == EPI_GELU || epilogue == EPI_GELU_TANH ||
+                                    epilogue == EPI_SILU);
+    if (aux_is_out && (r = make_tmap_out(&taux, aux, out_dtype, N, M, ldaux))) return r;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (sm_count <= 0) sm_count = 148;
 
 #define PF_GEMM_DISPATCH(T)                                                          \
-  (BN == 256 ? launch_gemm<T, 256, 4>(ta, tb, p, sm_count, st)                       \
-             : launch_gemm<T, 128, 6>(ta, tb, p, sm_count, st))
+  (BN == 256 ? launch_gemm<T, 256, 4>(ta, tb, tc, taux, p, sm_count, st)             \
+             : launch_gemm<T, 128, 6>(ta, tb, tc, taux, p, sm_count, st))
   switch (out_dtype) {
     case PF_F32: return PF_GEMM_DISPATCH(float);
     case PF_F16: return PF_GEMM_DISPATCH(__half);

@@ -559,8 +559,13 @@ static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, co
     else if (nvec <= 32 * 6) PF_NORM_BWD_DX(6);
     else PF_NORM_BWD_DX(8);
 #undef PF_NORM_BWD_DX
-    int slabs = (int)((rows + 31) / 32);
+    // enough row slabs to fill the GPU once with (column blocks x slabs) CTAs, few enough
+    // that folding them (norm_bwd_finish_kernel) stays negligible
+    const int col_blocks = (N + 255) / 256;
+    int slabs = (2 * 148 + col_blocks - 1) / col_blocks;
+    if (slabs > (int)((rows + 31) / 32)) slabs = (int)((rows + 31) / 32);
     if (slabs > G) slabs = G;
+    if (slabs < 1) slabs = 1;
     const int rows_per = (int)((rows + slabs - 1) / slabs);
     slabs = (int)((rows + rows_per - 1) / rows_per);
     norm_bwd_param_kernel<T><<<dim3((N + 255) / 256, slabs), 256, 0, st>>>(

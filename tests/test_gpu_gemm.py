@@ -40,7 +40,7 @@ def test_gemm_layouts(a_mn, b_mn, dtype, M, N, K):
     _close(out, _ref(a, b, a_mn, b_mn), K, dtype)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 1024 + 256])   # bit 10: direct-store epilogue
 def test_gemm_tile_variants_and_fp32_out(tile_n):
     from pfeife_b200.ops import kernels as kx
     a, b = _mk(520, 776, 320, False, False, torch.bfloat16)
@@ -49,9 +49,11 @@ def test_gemm_tile_variants_and_fp32_out(tile_n):
     _close(out, _ref(a, b, False, False), 320, torch.float32)
 
 
-def test_gemm_epilogues():
+@pytest.mark.parametrize("tile_n", [0, 1024])
+@pytest.mark.parametrize("M,N,K", [(400, 384, 192), (6168, 1408, 320)])
+def test_gemm_epilogues(tile_n, M, N, K):
+    """Every fused epilogue through the TMA-store path (tile_n 0) and the direct-store path."""
     from pfeife_b200.ops import kernels as kx
-    M, N, K = 400, 384, 192
     dtype = torch.bfloat16
     a, b = _mk(M, N, K, False, False, dtype)
     a = a * 0.1
@@ -59,24 +61,24 @@ def test_gemm_epilogues():
     res = torch.randn(M, N, device="cuda").to(dtype)
     ref = _ref(a, b, False, False) + bias
     # bias + residual
-    out = kx.gemm(a, b, bias=bias, residual=res)
+    out = kx.gemm(a, b, bias=bias, residual=res, tile_n=tile_n)
     _close(out, ref + res.float(), K, dtype)
     # bias + GELU with saved pre-activation
     aux = torch.empty(M, N, device="cuda", dtype=dtype)
-    out = kx.gemm(a, b, bias=bias, aux=aux, epilogue=kx.EPI_GELU)
+    out = kx.gemm(a, b, bias=bias, aux=aux, epilogue=kx.EPI_GELU, tile_n=tile_n)
     _close(aux, ref, K, dtype)
     _close(out, torch.nn.functional.gelu(ref), K, dtype)
     # dGELU: out = acc * gelu'(aux)
     z = torch.randn(M, N, device="cuda").to(dtype)
-    out = kx.gemm(a, b, aux=z, epilogue=kx.EPI_DGELU)
+    out = kx.gemm(a, b, aux=z, epilogue=kx.EPI_DGELU, tile_n=tile_n)
     zf = z.float().requires_grad_()
     torch.nn.functional.gelu(zf).sum().backward()
     _close(out, _ref(a, b, False, False) * zf.grad, K, dtype)
     # fp32 accumulate (gradient bucket), both operands MN-major as in wgrad
     at, bt = a.t().contiguous(), b.t().contiguous()
     bucket = torch.ones(M, N, device="cuda")
-    kx.gemm(at, bt, a_mn=True, b_mn=True, out=bucket, accumulate=True)
-    kx.gemm(at, bt, a_mn=True, b_mn=True, out=bucket, accumulate=True)
+    kx.gemm(at, bt, a_mn=True, b_mn=True, out=bucket, accumulate=True, tile_n=tile_n)
+    kx.gemm(at, bt, a_mn=True, b_mn=True, out=bucket, accumulate=True, tile_n=tile_n)
     torch.cuda.synchronize()
     kx.check_status()
     _close(bucket, 1.0 + 2.0 * _ref(a, b, False, False), K, torch.float32)
