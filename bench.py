@@ -235,6 +235,10 @@ def run_native(args) -> int:
     if not cpu:
         from pfeife_b200.ops import kernels as kx
         kx.check_status()
+    bubble = 0.0
+    for m in runner.modules:
+        if m.plan is not None and m.plan.sim is not None:
+            bubble = m.plan.sim.bubble_fraction
     if state.is_main_process:
         samples = n * state.dp_size
         emit_result(args, impl="pfeife_b200", n_gpus=world, ms=ms, ms_e2e=ms_e2e, samples=samples,
@@ -242,7 +246,9 @@ def run_native(args) -> int:
                     parallelism=f"pp{state.pp_size}xdp{state.dp_size}",
                     h2d=host_x16.numel() * host_x16.element_size() + host_y.numel() * 8, d2h=4,
                     extra={"dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
-                           if state.dp_size > 1 else None})
+                           if state.dp_size > 1 else None,
+                           "optimizer_and_dp_exposed_ms": runner.worker.last_optimizer_ms(),
+                           "pipeline_bubble_pct": 100.0 * bubble})
     runner.close()
     if world > 1:
         dist.barrier()

@@ -122,3 +122,11 @@ PF_DECL int pf_groupnorm_bwd(const void* dy, const void* x, const void* mean, co
                              int dtype, int sm_count, void* stream);
 PF_DECL int pf_upsample2x(const void* x, void* y, int B, int H, int W, int C, int backward,
                           int dtype, int sm_count, void* stream);
+
+// ---- gemm_sm100.cu : GEMM with the all-gather of a row-sharded weight fused in
+PF_DECL int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, int world,
+                              int rank, int rows_per_rank, void* ready, void* C, int M, int N,
+                              int K, long long lda, long long ldb, long long ldc, int in_dtype,
+                              int out_dtype, const void* bias, int bias_dtype,
+                              const void* residual, long long ldr, void* aux, long long ldaux,
+                              int epilogue, float alpha, int* status, int sm_count, void* stream);

@@ -48,6 +48,14 @@ struct GemmParams {
   int a_mn, b_mn;
   int fmt;        // 0 = fp16 inputs, 1 = bf16 inputs
   int* status;
+  // ---- fused all-gather of the B operand (weights sharded by rows over `gather_world` ranks)
+  int gather_world;            // 0: B is an ordinary local operand
+  int gather_rank;
+  int gather_rows;             // rows of B owned by each rank
+  const void* gather_src[8];   // peer pointers to every rank's shard [gather_rows, K] (pitch ldb)
+  void* gather_dst;            // local full-size B [N, K] (pitch ldb); own rows already in place
+  int* gather_ready;           // local counters, one per BN-row tile of B, zeroed before launch
+  long long gather_ld;
 };
 
 template <int BN, int STAGES>
@@ -150,6 +158,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  // with a fused all-gather the tiles whose rows of B this rank owns are computed first, while
+  // the remote rows are still arriving
+  const int n_rot = p.gather_world > 1 ? (p.gather_rank * p.gather_rows) / BN : 0;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -181,7 +192,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % num_m) * GEMM_BM;
-        const int n0 = (tile / num_m) * BN;
+        const int nt = (tile / num_m + n_rot) % num_n;
+        const int n0 = nt * BN;
+        if (p.gather_world > 1) {
+          // rows of this B tile that other ranks own must have landed in the local buffer
+          int expect = 0;
+          for (int r = n0; r < min(p.N, n0 + BN); ++r)
+            expect += (r / p.gather_rows) != p.gather_rank;
+          long long t0 = clock64();
+          while (*reinterpret_cast<volatile int*>(p.gather_ready + nt) < expect) {
+            if (clock64() - t0 > PF_WAIT_CYCLES) { report(p.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+          }
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic writes -> TMA reads
+          if (!ok) break;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY);
           if (!ok) break;
@@ -266,9 +291,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool aux_out = AUX && (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH ||
                                  p.epilogue == EPI_SILU);
     bool stores_pending = false;
+    if (p.gather_world > 1) {
+      // All-gather of the remote shards of B: every epilogue warp of every CTA copies whole
+      // rows from the owners' memory (plain peer loads, 16 bytes per lane) into the local
+      // buffer and bumps the counter of the row's tile.  The TMA producer of a tile waits for
+      // its counter, so the transfer overlaps the tiles computed before it.
+      const int ew = (blockIdx.x * GEMM_EPI_WARPS) + (warp - 2);
+      const int n_ew = gridDim.x * GEMM_EPI_WARPS;
+      const int kvec = p.K / 8;
+      for (int r = ew; r < p.N; r += n_ew) {
+        const int owner = r / p.gather_rows;
+        if (owner == p.gather_rank) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const uint16_t*>(p.gather_src[owner]) +
+            (long long)(r - owner * p.gather_rows) * p.gather_ld);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.gather_dst) +
+                                              (long long)r * p.gather_ld);
+        for (int c = lane; c < kvec; c += 32) dst[c] = src[c];
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.gather_ready + r / BN, 1);
+      }
+    }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % num_m) * GEMM_BM;
-      const int n0 = (tile / num_m) * BN;
+      const int n0 = ((tile / num_m + n_rot) % num_n) * BN;
       ok = mbar_wait(&tmem_full[acc], acc_phase, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
@@ -455,6 +503,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 
 using namespace pf;
 
+// all-gather arguments of the call in flight on this thread (set by pf_gemm_allgather)
+struct GatherArgs { int world = 0, rank = 0, rows = 0; int* ready = nullptr; const void* src[8] = {}; };
+static thread_local GatherArgs g_gather;
+
 PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                    long long ldb, long long ldc, int a_mn, int b_mn, int in_dtype, int out_dtype,
                    const void* bias, int bias_dtype, const void* residual, long long ldr,
@@ -486,6 +538,10 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
   p.aux = aux; p.ldaux = ldaux;
   p.epilogue = epilogue; p.accumulate = accumulate;
   p.alpha = alpha; p.a_mn = a_mn; p.b_mn = b_mn; p.fmt = fmt; p.status = status;
+  p.gather_world = g_gather.world; p.gather_rank = g_gather.rank;
+  p.gather_rows = g_gather.rows; p.gather_dst = const_cast<void*>(B);
+  p.gather_ready = g_gather.ready; p.gather_ld = ldb;
+  for (int i = 0; i < 8; ++i) p.gather_src[i] = g_gather.src[i];
   const size_t es = out_dtype == PF_F32 ? 4 : 2;
   auto aligned = [&](const void* ptr, long long ld) {
     return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0);
@@ -523,4 +579,30 @@ PF_API int pf_tmap_probe(const void* base, long long inner, long long outer, lon
                          int box_inner, int box_outer) {
   CUtensorMap m;
   return make_tmap_2d_16bit(&m, base, 1, inner, outer, ld, box_inner, box_outer);
+}
+
+// C[M,N] = epi(A[M,K] . W[N,K]^T) where W is sharded by rows over `world` ranks: rank r owns rows
+// [r*rows_per_rank, (r+1)*rows_per_rank) and `shards[r]` is a pointer (peer-mapped for r != rank)
+// to its [rows_per_rank, K] shard with pitch ldb.  `w_full` is a local [N, K] buffer (pitch ldb)
+// that already holds this rank's rows; the kernel fills in the others while it computes.
+// `ready` is an int array with one entry per 256-row tile of W (zeroed here).
+PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, int world, int rank,
+                             int rows_per_rank, void* ready, void* C, int M, int N, int K,
+                             long long lda, long long ldb, long long ldc, int in_dtype,
+                             int out_dtype, const void* bias, int bias_dtype,
+                             const void* residual, long long ldr, void* aux, long long ldaux,
+                             int epilogue, float alpha, int* status, int sm_count, void* stream) {
+  if (world < 1 || world > 8 || K % 8) return -3;
+  const int tiles = (N + 255) / 256;
+  cudaError_t e = cudaMemsetAsync(ready, 0, sizeof(int) * tiles,
+                                  reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return (int)e;
+  g_gather.world = world; g_gather.rank = rank; g_gather.rows = rows_per_rank;
+  g_gather.ready = (int*)ready;
+  for (int i = 0; i < 8; ++i) g_gather.src[i] = i < world ? shards[i] : nullptr;
+  const int r = pf_gemm(A, w_full, C, M, N, K, lda, ldb, ldc, 0, 0, in_dtype, out_dtype, bias,
+                        bias_dtype, residual, ldr, aux, ldaux, epilogue, 0, alpha, status,
+                        sm_count, 256, stream);
+  g_gather = GatherArgs();
+  return r;
 }

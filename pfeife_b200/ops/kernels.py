@@ -460,3 +460,28 @@ def upsample2x(x: torch.Tensor, backward: bool = False) -> torch.Tensor:
     check(L.pf_upsample2x(ptr(x), ptr(y), B, H, W, C, int(backward), dt(x.dtype),
                           sm_count(x.device), stream()), "pf_upsample2x")
     return y
+
+
+def gemm_allgather(a: torch.Tensor, w_full: torch.Tensor, shard_table, world: int, rank: int,
+                   rows_per_rank: int, ready: torch.Tensor, *, bias=None, residual=None, aux=None,
+                   epilogue: int = EPI_NONE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = epi(a @ W^T) with W sharded by rows over `world` ranks; the kernel pulls the other
+    ranks' rows into ``w_full`` over NVLink while it computes the tiles it already has.
+
+    ``shard_table`` is a ctypes array of per-rank shard pointers (see
+    ``parallel.dp_fused.PeerMemory.share``); ``ready`` an int32 tensor with one entry per
+    256-row tile of W."""
+    L = _lib.lib()
+    M, K = a.shape
+    N = w_full.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    check(L.pf_gemm_allgather(ptr(a), ptr(w_full), shard_table, world, rank, rows_per_rank,
+                              ptr(ready), ptr(out), M, N, K, c_ll(a.stride(0)),
+                              c_ll(w_full.stride(0)), c_ll(out.stride(0)), dt(a.dtype),
+                              dt(out.dtype), ptr(bias), dt(bias.dtype) if bias is not None else 0,
+                              ptr(residual), c_ll(residual.stride(0) if residual is not None else 0),
+                              ptr(aux), c_ll(aux.stride(0) if aux is not None else 0), epilogue,
+                              c_f(1.0), ptr(status_word(a.device)), sm_count(a.device), stream()),
+          "pf_gemm_allgather")
+    return out

@@ -546,6 +546,21 @@ class StageWorker:
             g.all_reduce_sum(slot.grad)
 
     def optimizer_step(self) -> None:
+        ev0 = self.recorder.record_event(self.device)
+        self._optimizer_step()
+        self.opt_events = (ev0, self.recorder.record_event(self.device))
+
+    def last_optimizer_ms(self) -> float:
+        """Device time of the last optimizer step (data-parallel reduce + update + gather); it
+        runs after the last backward, so all of it is exposed."""
+        ev = getattr(self, "opt_events", None)
+        if ev is None:
+            return 0.0
+        if self.device.type == "cuda":
+            ev[1].synchronize()
+        return float(ev[0].elapsed_time(ev[1]))
+
+    def _optimizer_step(self) -> None:
         self.all_reduce_shared_grads()
         grad_scale = 1.0
         fp16 = self.scaler.enabled

@@ -49,3 +49,19 @@ def test_fused_dp_equals_nccl_dp(tmp_path):
     assert fused["param_checksum"] == pytest.approx(nccl["param_checksum"], rel=1e-4, abs=1e-3)
     for a, b in zip(fused["losses"], nccl["losses"]):
         assert a == pytest.approx(b, rel=2e-2, abs=2e-2)
+
+
+def test_allgather_fused_into_gemm(tmp_path):
+    out = str(tmp_path / "ag.json")
+    _port[0] += 1
+    cmd = [sys.executable, os.path.join(ROOT, "mp_launch.py"), "--world_size", "2", "--all_main",
+           "--master_port", str(_port[0]),
+           os.path.join(ROOT, "tests", "scripts", "allgather_gemm_check.py"), "--out", out,
+           "--M", "1000", "--N", "1024", "--K", "320", "--iters", "3"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=300, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-3000:]
+    with open(out) as f:
+        res = json.load(f)
+    assert res["gathered_ok"] and res["err"] < 0.15
