@@ -128,11 +128,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
+  // P (two blocks) is written over the K tile once S = Q K^T has completed; with a one-block
+  // K tile (D <= 64) it gets room of its own
+  constexpr int PK = (NBLK >= 2) ? 0 : 2 * ATT_BLK;
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE;
   uint8_t* sV = sK + TILE;
-  uint8_t* sP = sV + TILE;                         // 2 blocks
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATT_BLK);
+  uint8_t* sP = (NBLK >= 2) ? sK : sV + TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + TILE + PK);
   uint64_t* bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3,
           *bar_o = bars + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
@@ -325,8 +328,14 @@ attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, long l
   }
 }
 
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
 template <typename T, int DP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                 const AttnParams p) {
@@ -347,7 +356,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           *bar_dq = bars + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row_t = (warp & 3) * 32 + lane;     // TMEM lane / tile row of this thread
+  const int half = warp >> 2;                   // which half of the columns this warp handles
   const int k0 = blockIdx.x * ATT_BN, h = blockIdx.y, b = blockIdx.z;
 
   if (tid == 0) {
@@ -362,7 +373,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
-  const uint32_t lane_off = uint32_t(warp * 32) << 16;
+  const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
 
   const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);     // Q K^T and dO V^T
   const uint32_t idesc_kd = make_idesc_f16(128, DP, p.fmt, 1, 1);     // P^T dO, dS^T Q
@@ -391,7 +402,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   bool first = true;
   for (int qt = q_begin / ATT_BM; qt < n_q && ok; ++qt) {
     const int q0 = qt * ATT_BM;
-    const int qi = q0 + tid;
+    const int qi = q0 + row_t;
     if (tid == 0) {
       mbar_expect_tx(bar_q, 2 * TILE);
 #pragma unroll
@@ -416,7 +427,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const float lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * LOG2E : 0.f;
     const float dl = row_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
 #pragma unroll 1
-    for (int c = 0; c < nk_chunks; ++c) {
+    for (int c = half; c < nk_chunks; c += 2) {
       uint32_t rs[32], rp[32];
       tmem_ld32(t_s + lane_off + c * 32, rs);
       tmem_ld32(t_dp + lane_off + c * 32, rp);
@@ -430,8 +441,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         pv[i] = pr;
         ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
       }
-      store_p_chunk<T>(sP, tid, c * 32, pv);
-      store_p_chunk<T>(sdS, tid, c * 32, ds);
+      store_p_chunk<T>(sP, row_t, c * 32, pv);
+      store_p_chunk<T>(sdS, row_t, c * 32, ds);
     }
     fence_async_smem();
     tc_fence_before();
@@ -458,13 +469,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       float* dst = p.dq_accum + (((long long)b * p.Sq + (row_ok ? qi : 0)) * p.H + h) * p.D;
 #pragma unroll
       for (int c = 0; c < DP / 32; ++c) {
+        if ((c & 1) != half) continue;            // warp-uniform
         uint32_t raw[32];
         tmem_ld32(t_s + lane_off + c * 32, raw);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < p.D) atomicAdd(dst + c * 32 + i, __uint_as_float(raw[i]));
+          for (int i = 0; i < 32; i += 4)
+            if (c * 32 + i < p.D)                 // D is a multiple of 8
+              red_add_v4(dst + c * 32 + i, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]),
+                         __uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3]));
         }
       }
     }
@@ -479,13 +493,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   // epilogue: dK, dV rows of this tile
   if (ok && !first) {
     tc_fence_after();
-    const int kj = k0 + tid;
+    const int kj = k0 + row_t;
     const long long off_kv = (long long)b * p.sdkv[0] + (long long)kj * p.sdkv[1] +
                              (long long)h * p.sdkv[2];
     T* dkp = reinterpret_cast<T*>(p.dk) + off_kv;
     T* dvp = reinterpret_cast<T*>(p.dv) + off_kv;
 #pragma unroll
     for (int c = 0; c < DP / 32; ++c) {
+      if ((c & 1) != half) continue;              // warp-uniform
       uint32_t rk[32], rv[32];
       tmem_ld32(t_dk + lane_off + c * 32, rk);
       tmem_ld32(t_dv + lane_off + c * 32, rv);
@@ -512,8 +527,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
   } else if (ok && first) {
     // no query tile sees this key tile (causal with Sk > Sq + ...): gradients are zero
-    const int kj = k0 + tid;
-    if (kj < p.Sk) {
+    const int kj = k0 + row_t;
+    if (kj < p.Sk && half == 0) {
       const long long off_kv = (long long)b * p.sdkv[0] + (long long)kj * p.sdkv[1] +
                                (long long)h * p.sdkv[2];
       T* dkp = reinterpret_cast<T*>(p.dk) + off_kv;
@@ -577,7 +592,7 @@ template <typename T, int DP>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const AttnParams& p, cudaStream_t st) {
   constexpr int NBLK = (DP + 63) / 64;
-  constexpr int SMEM = 3 * NBLK * ATT_BLK + 2 * ATT_BLK + 128 + 1024;
+  constexpr int SMEM = 3 * NBLK * ATT_BLK + (NBLK >= 2 ? 0 : 2 * ATT_BLK) + 128 + 1024;
   auto kern = attn_fwd_kernel<T, DP>;
   static bool done[64] = {};
   int r = set_smem(kern, SMEM, done);
@@ -598,7 +613,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   int r = set_smem(kern, SMEM, done);
   if (r) return r;
   dim3 grid((p.Sk + ATT_BN - 1) / ATT_BN, p.H, p.B);
-  kern<<<grid, 128, SMEM, st>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, 256, SMEM, st>>>(tq, tk, tv, tdo, p);
   PF_CHECK_LAUNCH();
   return 0;
 }

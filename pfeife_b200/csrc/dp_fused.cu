@@ -28,7 +28,7 @@ constexpr int DP_MAX = 8;
 // them (first-step compilation, graph capture), so that wait is allowed ~20 s; the later
 // barriers only cover the kernel's own phases.
 constexpr long long DP_ENTRY_WAIT = 20 * PF_WAIT_CYCLES;
-constexpr int DP_THREADS = 256;
+constexpr int DP_THREADS = 512;
 
 struct DpArgs {
   int rank, world;
@@ -98,7 +98,7 @@ __device__ void job_barrier(const DpArgs& a, int k) {
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(DP_THREADS, 1)
+__global__ void __launch_bounds__(DP_THREADS, 2)
 dp_fused_kernel(const DpArgs a) {
   const long long lo = a.shard_lo, hi = a.shard_hi;
   const long long nvec = (hi - lo) / 4;        // shards are multiples of 4 elements
@@ -107,19 +107,40 @@ dp_fused_kernel(const DpArgs a) {
 
   job_barrier(a, 0);                            // every rank's gradients are complete
 
-  // ---- reduce-scatter into the local bucket, zero the peers' copies
+  // ---- reduce-scatter into the local bucket, zero the peers' copies.  Four 16-byte vectors
+  //      per thread and peer are requested before any is consumed, so enough bytes are in
+  //      flight to cover the NVLink latency.
   bool bad = false;
-  for (long long i = tid; i < nvec; i += stride) {
-    const long long e = lo + i * 4;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  constexpr int U = 4;
+  for (long long i0 = tid; i0 < nvec; i0 += stride * U) {
+    float4 s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < a.world; ++p) {
-      const float4 g = *reinterpret_cast<const float4*>(a.grad[p] + e);
-      s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-      if (p != a.rank)
-        *reinterpret_cast<float4*>(a.grad[p] + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 g[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        g[u] = i < nvec ? *reinterpret_cast<const float4*>(a.grad[p] + lo + i * 4)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        s[u].x += g[u].x; s[u].y += g[u].y; s[u].z += g[u].z; s[u].w += g[u].w;
+        if (p != a.rank && i < nvec)
+          *reinterpret_cast<float4*>(a.grad[p] + lo + i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
-    *reinterpret_cast<float4*>(a.grad[a.rank] + e) = s;
-    if (a.check_inf) bad |= !(isfinite(s.x) && isfinite(s.y) && isfinite(s.z) && isfinite(s.w));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+        *reinterpret_cast<float4*>(a.grad[a.rank] + lo + i * 4) = s[u];
+        if (a.check_inf)
+          bad |= !(isfinite(s[u].x) && isfinite(s[u].y) && isfinite(s[u].z) && isfinite(s[u].w));
+      }
+    }
   }
   if (a.check_inf) {
     if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0)
@@ -213,7 +234,8 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   a.grad_scale = grad_scale; a.adamw = adamw; a.lp_dtype = lp_dtype; a.check_inf = check_inf;
   a.loss_scale = (const float*)loss_scale; a.found_inf = (float*)found_inf;
   a.epoch = epoch; a.status = status;
-  const int grid = sm_count > 0 ? sm_count : 148;   // one CTA per SM: all CTAs are co-resident
+  // two 512-thread CTAs per SM: all CTAs are co-resident (the barriers rely on it)
+  const int grid = 2 * (sm_count > 0 ? sm_count : 148);
   a.sync_base = calls_before * 3 * grid;
   dp_fused_kernel<<<grid, DP_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   PF_CHECK_LAUNCH();

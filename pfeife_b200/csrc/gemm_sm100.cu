@@ -25,7 +25,8 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;       // 64 x 16-bit = one 128 B swizzle row
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_EPI_WARPS = 8;     // two warps per TMEM lane quadrant, half the columns each
-constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
+constexpr int GEMM_GATHER_WARPS = 2;  // copy remote rows of a sharded B operand (fused all-gather)
+constexpr int GEMM_THREADS = 64 + 32 * (GEMM_EPI_WARPS + GEMM_GATHER_WARPS);
 
 enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_GELU_TANH = 3, EPI_DGELU_TANH = 4,
                  EPI_SILU = 5 };
@@ -274,8 +275,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
+  } else if (warp >= 2 + GEMM_EPI_WARPS) {
+    // ------------------------------------------------------------------ gather warps
+    if (p.gather_world > 1) {
+      // All-gather of the remote shards of B: the gather warps of every CTA copy whole
+      // rows from the owners' memory (plain peer loads, 16 bytes per lane) into the local
+      // buffer and bumps the counter of the row's tile.  The TMA producer of a tile waits for
+      // its counter, so the transfer overlaps the tiles computed before it.
+      const int ew = blockIdx.x * GEMM_GATHER_WARPS + (warp - 2 - GEMM_EPI_WARPS);
+      const int n_ew = gridDim.x * GEMM_GATHER_WARPS;
+      const int kvec = p.K / 8;
+      for (int r = ew; r < p.N; r += n_ew) {
+        const int owner = r / p.gather_rows;
+        if (owner == p.gather_rank) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const uint16_t*>(p.gather_src[owner]) +
+            (long long)(r - owner * p.gather_rows) * p.gather_ld);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.gather_dst) +
+                                              (long long)r * p.gather_ld);
+        // up to 8 vectors per lane are requested before any is stored (latency hiding)
+        for (int c0 = lane; c0 < kvec; c0 += 256) {
+          uint4 buf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (c0 + u * 32 < kvec) buf[u] = src[c0 + u * 32];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (c0 + u * 32 < kvec) dst[c0 + u * 32] = buf[u];
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.gather_ready + r / BN, 1);
+      }
+    }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
+    // ------------------------------------------------------------------ epilogue (8 warps)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int col_half = (warp - 2) >> 2;          // which half of the tile's columns
     const int c_begin = col_half * (BN / 2), c_end = c_begin + BN / 2;
@@ -291,29 +326,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool aux_out = AUX && (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH ||
                                  p.epilogue == EPI_SILU);
     bool stores_pending = false;
-    if (p.gather_world > 1) {
-      // All-gather of the remote shards of B: every epilogue warp of every CTA copies whole
-      // rows from the owners' memory (plain peer loads, 16 bytes per lane) into the local
-      // buffer and bumps the counter of the row's tile.  The TMA producer of a tile waits for
-      // its counter, so the transfer overlaps the tiles computed before it.
-      const int ew = (blockIdx.x * GEMM_EPI_WARPS) + (warp - 2);
-      const int n_ew = gridDim.x * GEMM_EPI_WARPS;
-      const int kvec = p.K / 8;
-      for (int r = ew; r < p.N; r += n_ew) {
-        const int owner = r / p.gather_rows;
-        if (owner == p.gather_rank) continue;
-        const uint4* src = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const uint16_t*>(p.gather_src[owner]) +
-            (long long)(r - owner * p.gather_rows) * p.gather_ld);
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.gather_dst) +
-                                              (long long)r * p.gather_ld);
-        for (int c = lane; c < kvec; c += 32) dst[c] = src[c];
-        asm volatile("fence.proxy.async;" ::: "memory");
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) atomicAdd(p.gather_ready + r / BN, 1);
-      }
-    }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % num_m) * GEMM_BM;
       const int n0 = ((tile / num_m + n_rot) % num_n) * BN;
