@@ -57,6 +57,8 @@ def bench_gemm(timer, out):
         ("vitg_qkv_fwd", 6168, 4224, 1408, False, False),
         ("vitg_fc1_fwd", 6168, 6144, 1408, False, False),
         ("vitg_fc2_fwd", 6168, 1408, 6144, False, False),
+        ("vitg_proj_fwd", 6168, 1408, 1408, False, False),
+        ("vitg_fc2_dgrad", 6168, 6144, 1408, False, True),
         ("vitg_fc1_dgrad", 6168, 1408, 6144, False, True),
         ("vitg_fc1_wgrad", 6144, 1408, 6168, True, True),
         ("llama_ffn_fwd", 2048, 11008, 4096, False, False),
@@ -68,12 +70,16 @@ def bench_gemm(timer, out):
             b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(dtype)
             c = torch.empty(M, N, device="cuda", dtype=dtype)
             ms = timer(lambda: kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c))
+            # the two tile forms on their own (bit 12: single-CTA tiles, bit 11: CTA pairs)
+            ms_single = timer(lambda: kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c, tile_n=4096))
+            ms_pair = timer(lambda: kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c, tile_n=2048))
             A = a.t() if a_mn else a
             Bt = b if b_mn else b.t()
             ms_ref = timer(lambda: torch.matmul(A, Bt, out=c))
             tfl = 2.0 * M * N * K / ms / 1e9
             out({"kernel": "gemm_tcgen05", "case": name, "M": M, "N": N, "K": K, "ms": ms,
                  "tflops": tfl, "frac_peak": tfl / tf, "peak_ref": tag,
+                 "ms_single_cta": ms_single, "ms_cta_pair": ms_pair,
                  "torch_matmul_ms": ms_ref, "vs_torch": ms_ref / ms})
 
 

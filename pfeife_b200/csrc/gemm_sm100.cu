@@ -14,7 +14,8 @@
 //
 // Role layout of the 320-thread CTA: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and
 // MMA issuer (one lane), warps 2..9 = epilogue (one accumulator row per thread; two warps share a
-// TMEM lane quadrant and split the tile's columns, which halves the epilogue latency per tile).
+// TMEM lane quadrant and split the tile's columns, which halves the epilogue latency per tile);
+// the instantiation that fuses an all-gather of B adds two warps that copy the remote rows.
 #include <cstring>
 #include "common.cuh"
 #include "api.h"
@@ -26,7 +27,11 @@ constexpr int GEMM_BK = 64;       // 64 x 16-bit = one 128 B swizzle row
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_EPI_WARPS = 8;     // two warps per TMEM lane quadrant, half the columns each
 constexpr int GEMM_GATHER_WARPS = 2;  // copy remote rows of a sharded B operand (fused all-gather)
-constexpr int GEMM_THREADS = 64 + 32 * (GEMM_EPI_WARPS + GEMM_GATHER_WARPS);
+// the gather warps exist only in the instantiation that fuses the all-gather; without them the
+// other roles may use more registers per thread
+constexpr int gemm_threads(bool gather) {
+  return 64 + 32 * (GEMM_EPI_WARPS + (gather ? GEMM_GATHER_WARPS : 0));
+}
 
 enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_GELU_TANH = 3, EPI_DGELU_TANH = 4,
                  EPI_SILU = 5 };
@@ -59,16 +64,17 @@ struct GemmParams {
   long long gather_ld;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int SPW>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  // epilogue staging for TMA stores: per epilogue warp one [32 rows x 32 cols] box for C and one
-  // for aux (16-bit outputs) or one 4 KB box for C (fp32 outputs)
+  // epilogue staging for TMA stores: SPW bytes per epilogue warp, holding [32 rows x 32 cols]
+  // boxes (2 KB for 16-bit outputs, 4 KB for fp32): C and, when saved, aux; twice over when
+  // SPW has room for it
   static constexpr int STAGING_OFFSET = BAR_OFFSET + 1024;
-  static constexpr int STAGING_PER_WARP = 4096;
+  static constexpr int STAGING_PER_WARP = SPW;
   static constexpr int TOTAL = STAGING_OFFSET + GEMM_EPI_WARPS * STAGING_PER_WARP + 1024;
 };
 
@@ -134,13 +140,18 @@ __device__ __forceinline__ void stage_row32(uint8_t* box, int r, const float (&v
   }
 }
 
-template <typename OutT, int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// PAIR = false: one CTA per 128 x BN tile.  PAIR = true: the kernel runs as clusters of two CTAs
+// that share one 256 x 2BN tile through tcgen05.mma.cta_group::2: each CTA loads 128 rows of A
+// and BN rows of B per k-block (half the shared-memory traffic per FLOP of the single-CTA form),
+// the even CTA issues the MMAs, and each CTA's TMEM receives -- and its epilogue warps drain --
+// the 128 accumulator rows that match its rows of A.
+template <typename OutT, int BN, int STAGES, int SPW, bool PAIR, bool GATHER>
+__global__ void __launch_bounds__(gemm_threads(GATHER), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c,
                     const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p) {
-  using S = GemmSmem<BN, STAGES>;
+  using S = GemmSmem<BN, STAGES, SPW>;
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle atoms need 1024 B alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -153,15 +164,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two
+  constexpr int BNT = PAIR ? 2 * BN : BN;          // columns of the output tile
+  constexpr int BMT = PAIR ? 2 * GEMM_BM : GEMM_BM; // rows of the output tile (both CTAs of a pair)
+  constexpr uint32_t TMEM_COLS = 2 * BNT;  // 256 or 512: a power of two
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
-  const int num_m = (p.M + GEMM_BM - 1) / GEMM_BM;
-  const int num_n = (p.N + BN - 1) / BN;
+  const int num_m = (p.M + BMT - 1) / BMT;
+  const int num_n = (p.N + BNT - 1) / BNT;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   // with a fused all-gather the tiles whose rows of B this rank owns are computed first, while
   // the remote rows are still arriving
-  const int n_rot = p.gather_world > 1 ? (p.gather_rank * p.gather_rows) / BN : 0;
+  const int n_rot = (GATHER && p.gather_world > 1) ? (p.gather_rank * p.gather_rows) / BNT : 0;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -172,16 +188,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 32 * GEMM_EPI_WARPS);
+      // single CTA: every epilogue thread arrives; pair: lane 0 of every epilogue warp of both
+      // CTAs arrives on the leader's barrier
+      mbar_init(&tmem_empty[i], PAIR ? 2 * GEMM_EPI_WARPS : 32 * GEMM_EPI_WARPS);
     }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();   // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -191,43 +215,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * GEMM_BM;
+      bool all_gathered = false;
+      // pair: both CTAs' loads of a stage are counted on the leader's barrier
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
         const int nt = (tile / num_m + n_rot) % num_n;
-        const int n0 = nt * BN;
-        if (p.gather_world > 1) {
+        const int n0 = nt * BNT;
+        const int nb0 = n0 + int(cta_rank) * BN;     // first row of B this CTA loads
+        if (GATHER && p.gather_world > 1 && !all_gathered) {
           // rows of this B tile that other ranks own must have landed in the local buffer
-          int expect = 0;
-          for (int r = n0; r < min(p.N, n0 + BN); ++r)
-            expect += (r / p.gather_rows) != p.gather_rank;
-          long long t0 = clock64();
-          while (*reinterpret_cast<volatile int*>(p.gather_ready + nt) < expect) {
-            if (clock64() - t0 > PF_WAIT_CYCLES) { report(p.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+          const int n1 = min(p.N, n0 + BNT);
+          const int own0 = p.gather_rank * p.gather_rows, own1 = own0 + p.gather_rows;
+          const int expect = (n1 - n0) - max(0, min(n1, own1) - max(n0, own0));
+          if (expect > 0) {
+            long long t0 = clock64();
+            while (*reinterpret_cast<volatile int*>(p.gather_ready + nt) < expect) {
+              if (clock64() - t0 > PF_WAIT_CYCLES) { report(p.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+            }
+            // once every remote row is in place no later tile needs to look again
+            const int remote_rows = p.N - max(0, min(p.N, own1) - own0);
+            all_gathered = *reinterpret_cast<volatile int*>(p.gather_ready + num_n) >= remote_rows;
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");   // generic writes -> TMA reads
+            if (!ok) break;
           }
-          __threadfence();
-          asm volatile("fence.proxy.async;" ::: "memory");   // generic writes -> TMA reads
-          if (!ok) break;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           const int k0 = kb * GEMM_BK;
-          if (!p.a_mn) {
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
-          } else {
+          if (PAIR) {
+            if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+            const uint32_t bar = mapa_u32(&full_bar[stage], 0);
+            if (!p.a_mn) {
+              tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < GEMM_BM / 64; ++j)
-              tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
-          }
-          if (!p.b_mn) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
-          } else {
+              for (int j = 0; j < GEMM_BM / 64; ++j)
+                tma_load_2d_pair(sa + j * 8192, &tmap_a, bar, m0 + j * 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d_pair(sb, &tmap_b, bar, k0, nb0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d_pair(sb + j * 8192, &tmap_b, bar, nb0 + j * 64, k0);
+            }
+          } else {
+            mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+            if (!p.a_mn) {
+              tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < GEMM_BM / 64; ++j)
+                tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -236,8 +287,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(GEMM_BM, BN, p.fmt, p.a_mn, p.b_mn);
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc_f16(BMT, BNT, p.fmt, p.a_mn, p.b_mn);
       // per-UMMA_K advance of the descriptor start address and its LBO/SBO
       const uint32_t a_adv = p.a_mn ? 2048u : 32u;
       const uint32_t b_adv = p.b_mn ? 2048u : 32u;
@@ -248,11 +299,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, PF_ERR_TIMEOUT_TMEM_EMPTY);
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        ok = PAIR ? mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, p.status,
+                                      PF_ERR_TIMEOUT_TMEM_EMPTY)
+                  : mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status,
+                              PF_ERR_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * BNT;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, p.status, PF_ERR_TIMEOUT_FULL);
           if (!ok) break;
@@ -263,13 +317,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             const uint64_t da = make_desc_sw128(sa + k * a_adv, a_lbo, 1024);
             const uint64_t db = make_desc_sw128(sb + k * b_adv, b_lbo, 1024);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+            if (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            else tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
           }
-          tc_commit(&empty_bar[stage]);  // smem slot reusable once these MMAs retire
+          // smem slot reusable (in both CTAs of a pair) once these MMAs retire
+          if (PAIR) tc_commit_pair(&empty_bar[stage], 3);
+          else tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tmem_full[acc]);
+        if (PAIR) tc_commit_pair(&tmem_full[acc], 3);
+        else tc_commit(&tmem_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -277,7 +335,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
   } else if (warp >= 2 + GEMM_EPI_WARPS) {
     // ------------------------------------------------------------------ gather warps
-    if (p.gather_world > 1) {
+    if (GATHER && p.gather_world > 1) {
       // All-gather of the remote shards of B: the gather warps of every CTA copy whole
       // rows from the owners' memory (plain peer loads, 16 bytes per lane) into the local
       // buffer and bumps the counter of the row's tile.  The TMA producer of a tile waits for
@@ -306,14 +364,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         asm volatile("fence.proxy.async;" ::: "memory");
         __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(p.gather_ready + r / BN, 1);
+        if (lane == 0) {
+          atomicAdd(p.gather_ready + r / BNT, 1);
+          atomicAdd(p.gather_ready + num_n, 1);   // running total of gathered rows
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (8 warps)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int col_half = (warp - 2) >> 2;          // which half of the tile's columns
-    const int c_begin = col_half * (BN / 2), c_end = c_begin + BN / 2;
+    const int c_begin = col_half * (BNT / 2), c_end = c_begin + BNT / 2;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -321,43 +382,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     OutT* C = reinterpret_cast<OutT*>(p.C);
     const OutT* R = reinterpret_cast<const OutT*>(p.residual);
     OutT* AUX = reinterpret_cast<OutT*>(p.aux);
-    uint8_t* stage_c = smem + S::STAGING_OFFSET + (warp - 2) * S::STAGING_PER_WARP;
-    uint8_t* stage_aux = stage_c + 2048;           // only used by 16-bit outputs
     const bool aux_out = AUX && (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH ||
                                  p.epilogue == EPI_SILU);
-    bool stores_pending = false;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % num_m) * GEMM_BM;
-      const int n0 = ((tile / num_m + n_rot) % num_n) * BN;
+    // Staging for TMA stores: a set is the C box (2 KB for 16-bit outputs, 4 KB for fp32) plus,
+    // when the pre-activation is saved, the aux box.  With room for two sets the warp fills one
+    // while the stores of the other are still reading it.
+    uint8_t* stage_base = smem + S::STAGING_OFFSET + (warp - 2) * S::STAGING_PER_WARP;
+    const int set_bytes = (sizeof(OutT) == 4 || aux_out) ? 4096 : 2048;
+    const bool two_sets = S::STAGING_PER_WARP >= 2 * set_bytes;
+    int set = 0;
+    int staged = 0;        // chunks handed to the TMA so far (saturates at 2)
+    const bool vec = p.vec_ok != 0;
+    const bool tma_out = p.tma_store != 0;
+    const bool bias_vec = p.bias && p.bias_dtype == PF_F32 &&
+                          (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
+      const int n0 = ((tile / num_m + n_rot) % num_n) * BNT;
       ok = mbar_wait(&tmem_full[acc], acc_phase, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
-      const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BNT;
+      uint32_t raw[32];
+      if (n0 + c_begin < p.N) tmem_ld32(t_row + c_begin, raw);   // uniform across the warp
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 32) {
         const int col = n0 + c;
         if (col >= p.N) break;  // uniform across the warp
-        uint32_t raw[32];
-        tmem_ld32(t_row + c, raw);
-        tmem_ld_wait();
+        tmem_ld_wait_for(raw);
         const int nvalid = min(32, p.N - col);
-        const bool vec = p.vec_ok != 0;
-        const bool tma_out = p.tma_store != 0;
         float v[32];
+        if (p.alpha != 1.0f) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
-        if (p.bias) {
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i < nvalid) v[i] += load_bias(p.bias, p.bias_dtype, col + i);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
         }
-        if (tma_out && stores_pending) {
-          // the previous chunk's TMA stores must have read the staging boxes before reuse
-          if (lane == 0) tma_store_wait_read();
+        // the next chunk's accumulators travel from TMEM while this one is processed
+        if (c + 32 < c_end && col + 32 < p.N) tmem_ld32(t_row + c + 32, raw);
+        if (p.bias) {
+          if (bias_vec && nvalid == 32) {
+            const float4* bp = reinterpret_cast<const float4*>(
+                reinterpret_cast<const float*>(p.bias) + col);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 b4 = __ldg(bp + j);
+              v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nvalid) v[i] += load_bias(p.bias, p.bias_dtype, col + i);
+          }
+        }
+        uint8_t* stage_c = stage_base + set * set_bytes;
+        uint8_t* stage_aux = stage_c + 2048;           // only used by 16-bit outputs
+        if (tma_out && staged >= (two_sets ? 2 : 1)) {
+          // the stores that last used this set must have read it before it is refilled
+          if (lane == 0) {
+            if (two_sets) tma_store_wait_read_but_one();
+            else tma_store_wait_read();
+          }
           __syncwarp();
-          stores_pending = false;
         }
         if (p.epilogue == EPI_GELU || p.epilogue == EPI_GELU_TANH || p.epilogue == EPI_SILU) {
           if (aux_out) {
@@ -367,7 +456,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (p.epilogue == EPI_GELU) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+            for (int i = 0; i < 32; ++i) v[i] = gelu_erf_fast(v[i]);
           } else if (p.epilogue == EPI_GELU_TANH) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
@@ -380,7 +469,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           load_row32<OutT>(AUX + (long long)row * p.ldaux + col, vec, nvalid, z);
           if (p.epilogue == EPI_DGELU) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf(z[i]);
+            for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf_fast(z[i]);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] *= dgelu_tanh(z[i]);
@@ -402,9 +491,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (p.accumulate) tma_reduce_add_2d(&tmap_c, stage_c, col, row0);
             else tma_store_2d(&tmap_c, stage_c, col, row0);
             if (aux_out) tma_store_2d(&tmap_aux, stage_aux, col, row0);
-            tma_store_commit();
           }
-          stores_pending = true;
+          // an (empty) group is committed even for a clipped chunk so that the group count
+          // matches the set rotation
+          if (lane == 0) tma_store_commit();
+          if (staged < 2) ++staged;
+          if (two_sets) set ^= 1;
         } else if (row_ok) {
           OutT* dst = C + (long long)row * p.ldc + col;
           if (p.accumulate) {
@@ -417,7 +509,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+      if (PAIR) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(&tmem_empty[acc], 0));
+      } else {
+        mbar_arrive(&tmem_empty[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -427,9 +524,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp >= 2 && lane == 0 && p.tma_store) tma_store_wait_all();
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();   // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -489,12 +588,13 @@ static int make_tmap_out(CUtensorMap* map, const void* base, int out_dtype, long
   return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
 }
 
-template <typename OutT, int BN, int STAGES>
+template <typename OutT, int BN, int STAGES, int SPW, bool PAIR, bool GATHER>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                        const CUtensorMap& taux, const GemmParams& p, int sm_count,
                        cudaStream_t stream) {
-  using S = GemmSmem<BN, STAGES>;
-  auto kern = gemm_tcgen05_kernel<OutT, BN, STAGES>;
+  using S = GemmSmem<BN, STAGES, SPW>;
+  constexpr int THREADS = gemm_threads(GATHER);
+  auto kern = gemm_tcgen05_kernel<OutT, BN, STAGES, SPW, PAIR, GATHER>;
   static bool configured[64] = {};  // the attribute is per device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -504,9 +604,41 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     if (e != cudaSuccess) return (int)e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
+  if (PAIR) {
+    const int num_tiles = ((p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((p.N + 2 * BN - 1) / (2 * BN));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count / 2));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // pairs that can be resident at once (the two CTAs of a pair sit on neighbouring SMs)
+    static int resident_pairs[64] = {};
+    int max_pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : 0;
+    if (max_pairs == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        n = sm_count / 2;
+      }
+      max_pairs = n < sm_count / 2 ? n : sm_count / 2;
+      if (dev >= 0 && dev < 64) resident_pairs[dev] = max_pairs;
+    }
+    const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, taux, p);
+    if (e != cudaSuccess) return (int)e;
+    return 0;
+  }
   const int num_tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, tc, taux, p);
+  kern<<<grid, THREADS, S::TOTAL, stream>>>(ta, tb, tc, taux, p);
   PF_CHECK_LAUNCH();
   return 0;
 }
@@ -530,8 +662,25 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;  // TMA needs 16-byte aligned bases and pitches
   const int fmt = in_dtype == PF_BF16 ? 1 : 0;
-  const int tn = tile_n & 1023;     // bit 10 of tile_n forces the direct-store epilogue (tests)
-  const int BN = (tn == 128 || tn == 256) ? tn : (N <= 128 ? 128 : 256);
+  // tile_n: low bits 0 / 128 / 256 = tile width of the single-CTA form; bit 10 forces the
+  // direct-store epilogue, bit 11 forces the CTA-pair form, bit 12 forbids it (tests, benches)
+  const int tn = tile_n & 1023;
+  if (sm_count <= 0) sm_count = 148;
+  bool pair = false;
+  if (g_gather.world <= 1 && !(tile_n & 4096) && sm_count >= 2) {
+    if (tile_n & 2048) {
+      pair = true;
+    } else if (tn == 0 && M > 128 && N > 128) {
+      // waves of 256 x 256 pair tiles over sm_count / 2 pairs against waves of 128 x 256 tiles
+      // over sm_count CTAs; a pair tile costs each SM about 0.8 of a single tile
+      const long long t2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+      const long long t1 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+      const long long w2 = (t2 + sm_count / 2 - 1) / (sm_count / 2);
+      const long long w1 = (t1 + sm_count - 1) / sm_count;
+      pair = 4 * w2 <= 5 * w1;
+    }
+  }
+  const int BN = pair ? 128 : (tn == 128 || tn == 256) ? tn : (N <= 128 ? 128 : 256);
 
   CUtensorMap ta, tb;
   int r;
@@ -573,11 +722,13 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     if (aux_is_out && (r = make_tmap_out(&taux, aux, out_dtype, N, M, ldaux))) return r;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (sm_count <= 0) sm_count = 148;
 
-#define PF_GEMM_DISPATCH(T)                                                          \
-  (BN == 256 ? launch_gemm<T, 256, 4>(ta, tb, tc, taux, p, sm_count, st)             \
-             : launch_gemm<T, 128, 6>(ta, tb, tc, taux, p, sm_count, st))
+  const bool gather = g_gather.world > 1;
+#define PF_GEMM_DISPATCH(T)                                                                    \
+  (pair     ? launch_gemm<T, 128, 5, 8192, true, false>(ta, tb, tc, taux, p, sm_count, st)     \
+   : gather ? launch_gemm<T, 256, 4, 4096, false, true>(ta, tb, tc, taux, p, sm_count, st)     \
+   : BN == 256 ? launch_gemm<T, 256, 4, 4096, false, false>(ta, tb, tc, taux, p, sm_count, st) \
+               : launch_gemm<T, 128, 5, 8192, false, false>(ta, tb, tc, taux, p, sm_count, st))
   switch (out_dtype) {
     case PF_F32: return PF_GEMM_DISPATCH(float);
     case PF_F16: return PF_GEMM_DISPATCH(__half);
@@ -597,7 +748,8 @@ PF_API int pf_tmap_probe(const void* base, long long inner, long long outer, lon
 // [r*rows_per_rank, (r+1)*rows_per_rank) and `shards[r]` is a pointer (peer-mapped for r != rank)
 // to its [rows_per_rank, K] shard with pitch ldb.  `w_full` is a local [N, K] buffer (pitch ldb)
 // that already holds this rank's rows; the kernel fills in the others while it computes.
-// `ready` is an int array with one entry per 256-row tile of W (zeroed here).
+// `ready` is an int array with one entry per 256-row tile of W plus one for the running total
+// (zeroed here).
 PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, int world, int rank,
                              int rows_per_rank, void* ready, void* C, int M, int N, int K,
                              long long lda, long long ldb, long long ldc, int in_dtype,
@@ -605,7 +757,7 @@ PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, i
                              const void* residual, long long ldr, void* aux, long long ldaux,
                              int epilogue, float alpha, int* status, int sm_count, void* stream) {
   if (world < 1 || world > 8 || K % 8) return -3;
-  const int tiles = (N + 255) / 256;
+  const int tiles = (N + 255) / 256 + 1;
   cudaError_t e = cudaMemsetAsync(ready, 0, sizeof(int) * tiles,
                                   reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return (int)e;

@@ -470,7 +470,7 @@ def gemm_allgather(a: torch.Tensor, w_full: torch.Tensor, shard_table, world: in
 
     ``shard_table`` is a ctypes array of per-rank shard pointers (see
     ``parallel.dp_fused.PeerMemory.share``); ``ready`` an int32 tensor with one entry per
-    256-row tile of W."""
+    256-row tile of W plus one (the running total)."""
     L = _lib.lib()
     M, K = a.shape
     N = w_full.shape[0]

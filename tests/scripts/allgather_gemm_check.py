@@ -37,7 +37,7 @@ def main():
     shard = w_all[r * rows:(r + 1) * rows].contiguous().to(dev)
     w_full = torch.zeros(N, K, dtype=torch.float16, device=dev)
     w_full[r * rows:(r + 1) * rows] = shard
-    ready = torch.zeros((N + 255) // 256, dtype=torch.int32, device=dev)
+    ready = torch.zeros((N + 255) // 256 + 1, dtype=torch.int32, device=dev)
     peers = PeerMemory(st.ctrl_dp, W, r)
     table = _table(peers.share(shard))
     torch.cuda.synchronize()

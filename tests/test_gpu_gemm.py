@@ -29,18 +29,20 @@ def _close(out, ref, K, dtype):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 200, 136),
                                    (6168, 1408, 1408), (1000, 128, 72)])
-def test_gemm_layouts(a_mn, b_mn, dtype, M, N, K):
+@pytest.mark.parametrize("form", [4096, 2048])   # single-CTA tiles / CTA-pair tiles
+def test_gemm_layouts(a_mn, b_mn, dtype, M, N, K, form):
     from pfeife_b200.ops import kernels as kx
     if (a_mn and M % 8) or (b_mn and N % 8):
         pytest.skip("MN-major operands need a 16-byte aligned pitch")
     a, b = _mk(M, N, K, a_mn, b_mn, dtype)
-    out = kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    out = kx.gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=form)
     torch.cuda.synchronize()
     kx.check_status()
     _close(out, _ref(a, b, a_mn, b_mn), K, dtype)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256, 1024 + 256])   # bit 10: direct-store epilogue
+# bit 10: direct-store epilogue, bit 11: CTA-pair form, bit 12: single-CTA form
+@pytest.mark.parametrize("tile_n", [4096 + 128, 4096 + 256, 4096 + 1024 + 256, 2048, 2048 + 1024, 0])
 def test_gemm_tile_variants_and_fp32_out(tile_n):
     from pfeife_b200.ops import kernels as kx
     a, b = _mk(520, 776, 320, False, False, torch.bfloat16)
@@ -49,10 +51,11 @@ def test_gemm_tile_variants_and_fp32_out(tile_n):
     _close(out, _ref(a, b, False, False), 320, torch.float32)
 
 
-@pytest.mark.parametrize("tile_n", [0, 1024])
+@pytest.mark.parametrize("tile_n", [4096, 4096 + 1024, 2048, 2048 + 1024])
 @pytest.mark.parametrize("M,N,K", [(400, 384, 192), (6168, 1408, 320)])
 def test_gemm_epilogues(tile_n, M, N, K):
-    """Every fused epilogue through the TMA-store path (tile_n 0) and the direct-store path."""
+    """Every fused epilogue through the TMA-store path and the direct-store path (bit 10), on
+    single-CTA tiles (bit 12) and on CTA-pair tiles (bit 11)."""
     from pfeife_b200.ops import kernels as kx
     dtype = torch.bfloat16
     a, b = _mk(M, N, K, False, False, dtype)
@@ -94,3 +97,27 @@ def test_gemm_strided_views():
     kx.gemm(q, w, out=out[:, 128:])
     torch.cuda.synchronize()
     _close(out[:, 128:], q.float() @ w.float().t(), 256, torch.bfloat16)
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2)])
+def test_gemm_allgather_one_device(world, rank):
+    """The all-gather GEMM with every "peer" shard on this GPU: one launch copies the other
+    ranks' rows into the full weight while it computes, and the product must match x @ W^T."""
+    from pfeife_b200.ops import kernels as kx
+    from pfeife_b200.parallel.dp_fused import _table
+    M, N, K = 700, 1536, 320
+    rows = N // world
+    torch.manual_seed(world * 10 + rank)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    shards = [w[r * rows:(r + 1) * rows].clone() for r in range(world)]
+    w_full = torch.zeros_like(w)
+    w_full[rank * rows:(rank + 1) * rows] = shards[rank]
+    ready = torch.zeros((N + 255) // 256 + 1, dtype=torch.int32, device="cuda")
+    out = kx.gemm_allgather(x, w_full, _table([s.data_ptr() for s in shards]), world, rank, rows,
+                            ready)
+    torch.cuda.synchronize()
+    kx.check_status()
+    assert torch.equal(w_full, w)
+    assert int(ready[-1]) == N - rows
+    _close(out, x.float() @ w.float().t(), K, torch.bfloat16)
