@@ -21,6 +21,12 @@
 //     S = Q K^T ; P = exp2(S*c - lse2) ; dP = dO V^T ; dS = P * (dP - delta) * scale
 //     dV += P^T dO ; dK += dS^T Q ; dQ_tile = dS K  -> fp32 atomics into dq_accum
 // delta = rowsum(dO * O) comes from a small pre-pass; dq_accum is converted by a post-pass.
+//
+// Short tails.  A sequence length just above a multiple of 128 (ViT: 257 = 2 x 128 + the class
+// token) would spend a whole 128-row query tile on a few rows.  In the forward, when at most
+// ATT_TAIL_MAX rows are left over, the tensor-core tiles cover only the full multiples and a
+// small CUDA-core kernel computes the leftover query rows.  (The same split of the backward,
+// measured on ViT-g/14 shapes, cost more in its leftover-key kernel than the tiles it saved.)
 #include "common.cuh"
 #include "api.h"
 
@@ -31,6 +37,8 @@ constexpr int ATT_BN = 128;   // key rows per tile
 constexpr int ATT_BLK = 16384;  // bytes of one [128 rows x 64 x 16-bit] swizzled block
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+constexpr int ATT_TAIL_MAX = 4;      // leftover rows handled on CUDA cores
+constexpr int ATT_TAIL_SEQ_MAX = 2048;  // longest other dimension the CUDA-core paths stage in smem
 
 struct AttnParams {
   int B, H, Sq, Sk, D;
@@ -46,7 +54,125 @@ struct AttnParams {
   void* dv;
   long long sdkv[3];
   int* status;
+  // raw views for the CUDA-core tail path of the forward (element strides: batch, seq, head)
+  const void* q; const void* k; const void* v;
+  long long sq[3], sk[3], sv[3];
+  int q_tiles, q_tail;  // tensor-core query tiles; leftover query rows after them
 };
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+  // red: 32 floats of shared memory; every thread of the CTA calls
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = is_max ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = is_max ? -INFINITY : 0.f;
+  for (int i = 0; i < nw; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+  return r;
+}
+
+// dot product of a 16-bit global row (16-byte aligned, D a multiple of 8) with fp32 values in
+// shared memory
+template <typename T>
+__device__ __forceinline__ float dot_row(const T* row, const float* sv, int D) {
+  // D <= 128: up to 16 vectors, requested together so that one memory latency covers the row
+  uint4 u[16];
+  const int nv = D / 8;
+#pragma unroll
+  for (int c = 0; c < 16; ++c)
+    if (c < nv) u[c] = __ldg(reinterpret_cast<const uint4*>(row) + c);
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    if (c < nv) {
+      const T* e = reinterpret_cast<const T*>(&u[c]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(to_f32<T>(e[j]), sv[c * 8 + j], s);
+    }
+  }
+  return s;
+}
+
+// acc[0..7] += w * (8 consecutive 16-bit values at `src`)
+template <typename T>
+__device__ __forceinline__ void axpy8(float (&acc)[8], float w, const uint4& u) {
+  const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, to_f32<T>(e[j]), acc[j]);
+}
+
+// Forward for one leftover query row on CUDA cores (128 threads).
+template <typename T>
+__device__ void attn_fwd_tail_row(const AttnParams& p, uint8_t* smem, int qi, int h, int b) {
+  float* qs = reinterpret_cast<float*>(smem);       // [128]
+  float* red = qs + 128;                            // [32]
+  float* sc = red + 32;                             // [Sk]
+  const int tid = threadIdx.x;
+  const T* qrow = reinterpret_cast<const T*>(p.q) + b * p.sq[0] + (long long)qi * p.sq[1] +
+                  h * p.sq[2];
+  for (int d = tid; d < p.D; d += blockDim.x) qs[d] = to_f32<T>(qrow[d]);
+  __syncthreads();
+  const float c2 = p.scale * LOG2E;
+  const int shift = p.Sk - p.Sq;
+  const T* kb = reinterpret_cast<const T*>(p.k) + b * p.sk[0] + h * p.sk[2];
+  float mx = -INFINITY;
+  for (int j = tid; j < p.Sk; j += blockDim.x) {
+    const bool vis = !(p.causal && j > qi + shift);
+    const float sj = vis ? dot_row<T>(kb + (long long)j * p.sk[1], qs, p.D) * c2 : -INFINITY;
+    sc[j] = sj;
+    mx = fmaxf(mx, sj);
+  }
+  mx = block_reduce(mx, red, true);
+  const float m_use = (mx == -INFINITY) ? 0.f : mx;
+  float sum = 0.f;
+  for (int j = tid; j < p.Sk; j += blockDim.x) {
+    const float pj = exp2f(sc[j] - m_use);
+    sc[j] = pj;
+    sum += pj;
+  }
+  const float l = block_reduce(sum, red, false);    // its barriers also publish sc[]
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  {
+    // thread = (key group g of 8, column vector cv of 16): keys g, g+8, ... ; 8 columns each
+    const int cv = tid & 15, g = tid >> 4;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (cv * 8 < p.D) {
+      const T* vb = reinterpret_cast<const T*>(p.v) + b * p.sv[0] + h * p.sv[2] + cv * 8;
+      int j = g;
+      for (; j + 24 < p.Sk; j += 32) {
+        const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(vb + (long long)j * p.sv[1]));
+        const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(vb + (long long)(j + 8) * p.sv[1]));
+        const uint4 u2 = __ldg(reinterpret_cast<const uint4*>(vb + (long long)(j + 16) * p.sv[1]));
+        const uint4 u3 = __ldg(reinterpret_cast<const uint4*>(vb + (long long)(j + 24) * p.sv[1]));
+        axpy8<T>(acc, sc[j], u0); axpy8<T>(acc, sc[j + 8], u1);
+        axpy8<T>(acc, sc[j + 16], u2); axpy8<T>(acc, sc[j + 24], u3);
+      }
+      for (; j < p.Sk; j += 8)
+        axpy8<T>(acc, sc[j], __ldg(reinterpret_cast<const uint4*>(vb + (long long)j * p.sv[1])));
+    }
+    __syncthreads();                 // sc[] is dead after this point: reuse it for the fold
+    float* fold = sc;                // [8 groups][128 columns]
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fold[g * 128 + cv * 8 + e] = acc[e];
+    __syncthreads();
+    if (tid < p.D) {
+      float a = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 8; ++gg) a += fold[gg * 128 + tid];
+      T* dst = reinterpret_cast<T*>(p.o) + (((long long)b * p.Sq + qi) * p.H + h) * p.D;
+      dst[tid] = from_f32<T>(a * inv);
+    }
+  }
+  if (tid == 0)
+    p.lse[((long long)b * p.H + h) * p.Sq + qi] = (l > 0.f) ? (mx + log2f(l)) * LN2 : -INFINITY;
+}
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -117,6 +243,15 @@ __device__ __forceinline__ void mma_mn_mn(uint32_t d_tmem, uint32_t sa, uint32_t
   }
 }
 
+
+// Leftover rows in kernels of their own: small shared memory and block size, so that many of
+// these latency-bound CTAs share an SM instead of each holding a tensor-core CTA's resources.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_fwd_tail_kernel(const AttnParams p) {
+  extern __shared__ uint8_t tail_smem[];
+  attn_fwd_tail_row<T>(p, tail_smem, p.q_tiles * ATT_BM + (int)blockIdx.x, blockIdx.y, blockIdx.z);
+}
 // ================================================================================ forward
 template <typename T, int DP>
 __global__ void __launch_bounds__(128)
@@ -142,7 +277,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int q0 = blockIdx.x * ATT_BM, h = blockIdx.y, b = blockIdx.z;
-
   if (tid == 0) {
     tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
     for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
@@ -287,15 +421,26 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* __restrict__ delta,
                   int B, int S, int H, int D) {
-  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);   // over B*S*H
-  if (row >= (long long)B * S * H) return;
-  const int lane = threadIdx.x & 31;
-  const T* a = dout + row * D;
-  const T* c = out + row * D;
+  // eight lanes per row, 16-byte loads (D is a multiple of 8): four rows per warp
+  const int lane = threadIdx.x & 31, sub = lane & 7;
+  const long long row = ((long long)blockIdx.x * 4 + (threadIdx.x >> 5)) * 4 + (lane >> 3);
+  const bool live = row < (long long)B * S * H;
   float s = 0.f;
-  for (int i = lane; i < D; i += 32) s += to_f32<T>(a[i]) * to_f32<T>(c[i]);
-  s = warp_sum(s);
-  if (lane == 0) {
+  if (live) {
+    const uint4* a = reinterpret_cast<const uint4*>(dout + row * D);
+    const uint4* c = reinterpret_cast<const uint4*>(out + row * D);
+    for (int i = sub; i < D / 8; i += 8) {
+      const uint4 ua = __ldg(a + i), uc = __ldg(c + i);
+      const T* ea = reinterpret_cast<const T*>(&ua);
+      const T* ec = reinterpret_cast<const T*>(&uc);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(to_f32<T>(ea[j]), to_f32<T>(ec[j]), s);
+    }
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (live && sub == 0) {
     const int h = (int)(row % H);
     const long long bs = row / H;
     const int i = (int)(bs % S);
@@ -328,12 +473,6 @@ attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, long l
   }
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
-               "f"(c), "f"(d)
-               : "memory");
-}
-
 template <typename T, int DP>
 __global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -360,7 +499,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int row_t = (warp & 3) * 32 + lane;     // TMEM lane / tile row of this thread
   const int half = warp >> 2;                   // which half of the columns this warp handles
   const int k0 = blockIdx.x * ATT_BN, h = blockIdx.y, b = blockIdx.z;
-
   if (tid == 0) {
     tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
     tma_prefetch_desc(&tdo);
@@ -404,11 +542,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int q0 = qt * ATT_BM;
     const int qi = q0 + row_t;
     if (tid == 0) {
-      mbar_expect_tx(bar_q, 2 * TILE);
+      if (first) {   // later tiles were requested at the end of the previous iteration
+        mbar_expect_tx(bar_q, 2 * TILE);
 #pragma unroll
-      for (int i = 0; i < NBLK; ++i) {
-        tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0, b);
-        tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0, b);
+        for (int i = 0; i < NBLK; ++i) {
+          tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0, b);
+          tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0, b);
+        }
       }
       if (first) ok = mbar_wait(bar_kv, 0, p.status, PF_ERR_TIMEOUT_FULL);
       ok = ok && mbar_wait(bar_q, ph, p.status, PF_ERR_TIMEOUT_FULL);
@@ -464,6 +604,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     ok = mbar_wait(bar_dq, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
     if (!ok) break;
     tc_fence_after();
+    if (tid == 0 && qt + 1 < n_q) {
+      // every MMA that read sQ / sdO has completed (commits complete in issue order): the next
+      // tile's loads overlap the dQ reduction below
+      mbar_expect_tx(bar_q, 2 * TILE);
+#pragma unroll
+      for (int i = 0; i < NBLK; ++i) {
+        tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0 + ATT_BM, b);
+        tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0 + ATT_BM, b);
+      }
+    }
     {
       // the TMEM loads are warp-collective: every lane executes them, only valid rows add
       float* dst = p.dq_accum + (((long long)b * p.Sq + (row_ok ? qi : 0)) * p.H + h) * p.D;
@@ -597,9 +747,15 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   static bool done[64] = {};
   int r = set_smem(kern, SMEM, done);
   if (r) return r;
-  dim3 grid((p.Sq + ATT_BM - 1) / ATT_BM, p.H, p.B);
+  dim3 grid(p.q_tiles, p.H, p.B);
   kern<<<grid, 128, SMEM, st>>>(tq, tk, tv, p);
   PF_CHECK_LAUNCH();
+  if (p.q_tail > 0) {
+    // [q 128 | red 32 | scores max(Sk, 8 x 128 for the fold)] floats
+    const int bytes = (160 + (p.Sk > 1024 ? p.Sk : 1024)) * 4;
+    attn_fwd_tail_kernel<T><<<dim3(p.q_tail, p.H, p.B), 128, bytes, st>>>(p);
+    PF_CHECK_LAUNCH();
+  }
   return 0;
 }
 
@@ -620,6 +776,26 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 static bool strides_ok(const void* ptr, long long sb, long long ss, long long sh) {
   return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && sb % 8 == 0 && ss % 8 == 0 && sh % 8 == 0;
+}
+
+// Tensor-core tiles and leftover rows of a sequence of length S: a short leftover (at most
+// ATT_TAIL_MAX rows after at least one full tile) goes to the CUDA-core paths, which stage the
+// other sequence dimension (`other`) in shared memory; otherwise the last tile is ragged.
+static void split_tail(int S, int other, int* tiles, int* tail) {
+  const int left = S % ATT_BM;
+  if (S > ATT_BM && left > 0 && left <= ATT_TAIL_MAX && other <= ATT_TAIL_SEQ_MAX) {
+    *tiles = S / ATT_BM;
+    *tail = left;
+  } else {
+    *tiles = (S + ATT_BM - 1) / ATT_BM;
+    *tail = 0;
+  }
+}
+
+static void set_views(AttnParams& p, const void* q, const void* k, const void* v,
+                      const long long* sq, const long long* sk, const long long* sv) {
+  p.q = q; p.k = k; p.v = v;
+  for (int i = 0; i < 3; ++i) { p.sq[i] = sq[i]; p.sk[i] = sk[i]; p.sv[i] = sv[i]; }
 }
 
 }  // namespace pf
@@ -666,6 +842,8 @@ PF_API int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, voi
   AttnParams p = {};
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.D = D; p.causal = causal; p.scale = scale;
   p.fmt = fmt; p.o = o; p.lse = (float*)lse; p.status = status;
+  set_views(p, q, k, v, sq, sk, sv);
+  split_tail(Sq, Sk, &p.q_tiles, &p.q_tail);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   PF_ATTN_DISPATCH(launch_fwd, tq, tk, tv, p, st);
 }
@@ -682,6 +860,7 @@ PF_API int pf_attn_bwd(const void* dout, const void* q, const void* k, const voi
   if (D % 8 || D > 128) return -3;
   if (!strides_ok(q, sq[0], sq[1], sq[2]) || !strides_ok(k, sk[0], sk[1], sk[2]) ||
       !strides_ok(v, sv[0], sv[1], sv[2]) || (reinterpret_cast<uintptr_t>(dout) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15) ||
       !strides_ok(dq, sdq[0], sdq[1], sdq[2]) || !strides_ok(dk, sdkv[0], sdkv[1], sdkv[2]) ||
       !strides_ok(dv, sdkv[0], sdkv[1], sdkv[2]))
     return -2;
@@ -689,10 +868,10 @@ PF_API int pf_attn_bwd(const void* dout, const void* q, const void* k, const voi
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long rows = (long long)B * Sq * H;
   if (dtype == PF_F16)
-    attn_delta_kernel<__half><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(
+    attn_delta_kernel<__half><<<(unsigned)((rows + 15) / 16), 128, 0, st>>>(
         (const __half*)dout, (const __half*)out, (float*)delta, B, Sq, H, D);
   else
-    attn_delta_kernel<__nv_bfloat16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(
+    attn_delta_kernel<__nv_bfloat16><<<(unsigned)((rows + 15) / 16), 128, 0, st>>>(
         (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, (float*)delta, B, Sq, H, D);
   PF_CHECK_LAUNCH();
   cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * D, st);

@@ -56,6 +56,19 @@ def _slot(t: Tensor) -> Optional[ParamSlot]:
     return _PARAMS.get(t.data_ptr())
 
 
+def _grad_bucket(t: Optional[Tensor]) -> Optional[Tensor]:
+    """The flat fp32 gradient view registered for parameter `t` (bias, norm weight), or None.
+    Backward kernels add into it directly, which saves the temporary, its zero-fill and the
+    accumulation kernel autograd would launch."""
+    if t is None or not t.is_cuda:
+        return None
+    s = _slot(t)
+    if s is None or s.main_grad is None or s.main_grad.dtype != torch.float32 \
+            or s.main_grad.numel() != t.numel():
+        return None
+    return s.main_grad.view(-1)
+
+
 def compute_dtype(x: Tensor) -> torch.dtype:
     """dtype GEMM-like ops run in: the autocast dtype when autocast is on, else x's dtype."""
     dev = "cuda" if x.is_cuda else "cpu"
@@ -159,7 +172,8 @@ def _(x, w, bias, residual, act):
 
 @torch.library.custom_op("pfeife::linear_bwd", mutates_args=())
 def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx: bool,
-               need_dw: bool, need_db: bool) -> Tuple[Tensor, Tensor, Tensor]:
+               need_dw: bool, need_db: bool, bias: Optional[Tensor] = None
+               ) -> Tuple[Tensor, Tensor, Tensor]:
     """-> (dx, dw, db); an output that is not needed, or that was accumulated directly into a
     registered gradient bucket, comes back as an empty tensor."""
     cd = dy.dtype
@@ -191,7 +205,11 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
             if dw.numel() and w.dtype != torch.float32:
                 dw = dw.to(w.dtype)
         if need_db:
-            db = kx.colsum(dy2)
+            bucket = _grad_bucket(bias)
+            if bucket is not None:
+                kx.colsum(dy2, out=bucket)      # adds into the registered gradient
+            else:
+                db = kx.colsum(dy2)
         return dx, dw, db
     dz = dy if not act else (dy.float() * _dact_ref(aux, act)).to(cd)
     dz2 = dz.reshape(-1, N)
@@ -202,7 +220,7 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
 
 
 @linear_bwd.register_fake
-def _(dy, x, w, aux, act, need_dx, need_dw, need_db):
+def _(dy, x, w, aux, act, need_dx, need_dw, need_db, bias=None):
     e = dy.new_empty(0)
     dx = dy.new_empty(x.shape[:-1] + (w.shape[1],)) if need_dx else e
     slot_acc = False
@@ -214,7 +232,8 @@ def _(dy, x, w, aux, act, need_dx, need_dw, need_db):
 def _linear_setup(ctx, inputs, output):
     x, w, bias, residual, act = inputs
     y, aux = output
-    ctx.save_for_backward(x, w, aux)
+    ctx.set_materialize_grads(False)     # no zero tensor for the unused gradient of `aux`
+    ctx.save_for_backward(x, w, aux, bias)
     ctx.act = act
     ctx.has_bias = bias is not None
     ctx.bias_dtype = bias.dtype if bias is not None else None
@@ -224,13 +243,16 @@ def _linear_setup(ctx, inputs, output):
 
 
 def _linear_backward(ctx, dy, daux):
-    x, w, aux = ctx.saved_tensors
+    x, w, aux, bias = ctx.saved_tensors
     need = ctx.needs_input_grad
+    if dy is None:
+        return None, None, None, None, None
     dy = dy.contiguous()
-    dx, dw, db = linear_bwd(dy, x, w, aux, ctx.act, need[0], need[1], ctx.has_bias and need[2])
+    dx, dw, db = linear_bwd(dy, x, w, aux, ctx.act, need[0], need[1], ctx.has_bias and need[2],
+                            bias)
     gx = dx.to(ctx.x_dtype) if need[0] else None
     gw = dw if (need[1] and dw.numel()) else None
-    gb = db.to(ctx.bias_dtype) if (ctx.has_bias and need[2]) else None
+    gb = db.to(ctx.bias_dtype) if (ctx.has_bias and need[2] and db.numel()) else None
     gr = dy.to(ctx.res_dtype) if (ctx.has_res and need[3]) else None
     return gx, gw, gb, gr, None
 
@@ -263,8 +285,8 @@ def _(x, w1, b1, w2, b2, residual, act):
 
 @torch.library.custom_op("pfeife::mlp_bwd", mutates_args=())
 def mlp_bwd(dy: Tensor, x: Tensor, w1: Tensor, w2: Tensor, z1: Tensor, a1: Tensor, act: int,
-            need_dx: bool, has_b1: bool, has_b2: bool
-            ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+            need_dx: bool, has_b1: bool, has_b2: bool, b1: Optional[Tensor] = None,
+            b2: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     """-> (dx, dw1, db1, dw2, db2).  On the native path the dgrad GEMM of the second layer
     applies act'(z1) in its epilogue, so dz1 is produced without an elementwise pass."""
     cd = dy.dtype
@@ -277,16 +299,17 @@ def mlp_bwd(dy: Tensor, x: Tensor, w1: Tensor, w2: Tensor, z1: Tensor, a1: Tenso
         w2c = _weight_as(w2, cd)
         epi = kx.EPI_DGELU if act == ACT_GELU else kx.EPI_DGELU_TANH
         dz1 = kx.gemm(dy2, w2c, b_mn=True, aux=z2, epilogue=epi)          # [M, H]
-        _, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, False, True, has_b2)
-        dx, dw1, db1 = linear_bwd(dz1.view(z1.shape), x, w1, empty, ACT_NONE, need_dx, True, has_b1)
+        _, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, False, True, has_b2, b2)
+        dx, dw1, db1 = linear_bwd(dz1.view(z1.shape), x, w1, empty, ACT_NONE, need_dx, True,
+                                  has_b1, b1)
         return dx, dw1, db1, dw2, db2
-    da1, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, True, True, has_b2)
-    dx, dw1, db1 = linear_bwd(da1, x, w1, z1, act, need_dx, True, has_b1)
+    da1, dw2, db2 = linear_bwd(dy, a1, w2, empty, ACT_NONE, True, True, has_b2, b2)
+    dx, dw1, db1 = linear_bwd(da1, x, w1, z1, act, need_dx, True, has_b1, b1)
     return dx, dw1, db1, dw2, db2
 
 
 @mlp_bwd.register_fake
-def _(dy, x, w1, w2, z1, a1, act, need_dx, has_b1, has_b2):
+def _(dy, x, w1, w2, z1, a1, act, need_dx, has_b1, has_b2, b1=None, b2=None):
     e = dy.new_empty(0)
     f32 = torch.float32
     return (torch.empty_like(x, dtype=dy.dtype) if need_dx else e, torch.empty_like(w1),
@@ -297,24 +320,27 @@ def _(dy, x, w1, w2, z1, a1, act, need_dx, has_b1, has_b2):
 def _mlp_setup(ctx, inputs, output):
     x, w1, b1, w2, b2, residual, act = inputs
     y, z1, a1 = output
-    ctx.save_for_backward(x, w1, w2, z1, a1)
+    ctx.set_materialize_grads(False)     # z1 / a1 are saved state, not differentiable outputs
+    ctx.save_for_backward(x, w1, w2, z1, a1, b1, b2)
     ctx.act = act
     ctx.meta = (x.dtype, None if b1 is None else b1.dtype, None if b2 is None else b2.dtype,
                 None if residual is None else residual.dtype)
 
 
 def _mlp_backward(ctx, dy, dz1_unused, da1_unused):
-    x, w1, w2, z1, a1 = ctx.saved_tensors
+    x, w1, w2, z1, a1, b1, b2 = ctx.saved_tensors
     xd, b1d, b2d, rd = ctx.meta
     need = ctx.needs_input_grad
+    if dy is None:
+        return (None,) * 7
     dy = dy.contiguous()
     dx, dw1, db1, dw2, db2 = mlp_bwd(dy, x, w1, w2, z1, a1, ctx.act, need[0], b1d is not None,
-                                     b2d is not None)
+                                     b2d is not None, b1, b2)
     return (dx.to(xd) if need[0] else None,
             dw1 if dw1.numel() else None,
-            db1.to(b1d) if b1d is not None else None,
+            db1.to(b1d) if (b1d is not None and db1.numel()) else None,
             dw2 if dw2.numel() else None,
-            db2.to(b2d) if b2d is not None else None,
+            db2.to(b2d) if (b2d is not None and db2.numel()) else None,
             dy.to(rd) if (rd is not None and need[5]) else None,
             None)
 
@@ -367,13 +393,22 @@ def _(x, gamma, beta, residual, eps, rms):
 
 @torch.library.custom_op("pfeife::norm_bwd", mutates_args=())
 def norm_bwd(dy: Tensor, dh: Optional[Tensor], h: Tensor, gamma: Tensor, mean: Tensor,
-             rstd: Tensor, rms: bool, has_beta: bool) -> Tuple[Tensor, Tensor, Tensor]:
+             rstd: Tensor, rms: bool, has_beta: bool, beta: Optional[Tensor] = None
+             ) -> Tuple[Tensor, Tensor, Tensor]:
     """-> (dx [= dh_total], dgamma fp32, dbeta fp32).  `dh` is the gradient arriving through
-    the residual-stream output, added in the same pass."""
+    the residual-stream output, added in the same pass.  When gamma (and beta) have registered
+    gradient buckets the sums are added there and come back empty."""
     N = h.shape[-1]
     if _native(h) or (h.is_cuda and h.dtype == torch.float32 and N % 4 == 0):
+        e32 = dy.new_empty(0, dtype=torch.float32)
+        gbucket = _grad_bucket(gamma)
+        bbucket = _grad_bucket(beta) if has_beta else None
+        if gbucket is not None and (bbucket is not None or not has_beta or rms):
+            dx, _, _ = kx.norm_bwd(dy, h, gamma, mean, rstd, rms, dres=dh, dgamma=gbucket,
+                                   dbeta=bbucket, accumulate=True, want_dbeta=False)
+            return dx, e32, dy.new_empty(0, dtype=torch.float32)
         dx, dg, db = kx.norm_bwd(dy, h, gamma, mean, rstd, rms, dres=dh, want_dbeta=has_beta)
-        return dx, dg, (db if (db is not None and has_beta) else dy.new_empty(0, dtype=torch.float32))
+        return dx, dg, (db if (db is not None and has_beta) else e32)
     hf = h.float()
     shp = hf.shape[:-1] + (1,)
     xhat = (hf - (0 if rms else mean.view(shp))) * rstd.view(shp)
@@ -391,7 +426,7 @@ def norm_bwd(dy: Tensor, dh: Optional[Tensor], h: Tensor, gamma: Tensor, mean: T
 
 
 @norm_bwd.register_fake
-def _(dy, dh, h, gamma, mean, rstd, rms, has_beta):
+def _(dy, dh, h, gamma, mean, rstd, rms, has_beta, beta=None):
     N = h.shape[-1]
     return (torch.empty_like(h), h.new_empty(N, dtype=torch.float32),
             h.new_empty(N if has_beta else 0, dtype=torch.float32))
@@ -400,18 +435,25 @@ def _(dy, dh, h, gamma, mean, rstd, rms, has_beta):
 def _norm_setup(ctx, inputs, output):
     x, gamma, beta, residual, eps, rms = inputs
     y, h, mean, rstd = output
-    ctx.save_for_backward(x if residual is None else h, gamma, mean, rstd)
+    ctx.set_materialize_grads(False)     # mean / rstd (and an unused h) carry no gradient
+    ctx.save_for_backward(x if residual is None else h, gamma, mean, rstd, beta)
     ctx.rms = rms
     ctx.meta = (gamma.dtype, None if beta is None else beta.dtype, residual is not None,
                 x.dtype, None if residual is None else residual.dtype)
 
 
 def _norm_backward(ctx, dy, dh, dmean, drstd):
-    h, gamma, mean, rstd = ctx.saved_tensors
+    h, gamma, mean, rstd, beta = ctx.saved_tensors
     gd, bd, has_res, xd, rd = ctx.meta
     dh_in = dh.contiguous() if (has_res and dh is not None) else None
-    dx, dg, db = norm_bwd(dy.contiguous(), dh_in, h, gamma, mean, rstd, ctx.rms, bd is not None)
-    return (dx.to(xd), dg.to(gd), db.to(bd) if bd is not None else None,
+    if dy is None:
+        if dh_in is None:
+            return (None,) * 6
+        dy = torch.zeros_like(h)
+    dx, dg, db = norm_bwd(dy.contiguous(), dh_in, h, gamma, mean, rstd, ctx.rms, bd is not None,
+                          beta)
+    return (dx.to(xd), dg.to(gd) if dg.numel() else None,
+            db.to(bd) if (bd is not None and db.numel()) else None,
             dx.to(rd) if has_res else None, None, None)
 
 
@@ -553,13 +595,16 @@ def _(dloss, logits, target, lse, ignore_index):
 
 def _ce_setup(ctx, inputs, output):
     logits, target, ignore_index = inputs
+    ctx.set_materialize_grads(False)
     ctx.save_for_backward(logits, target, output[1])
     ctx.ignore_index = ignore_index
 
 
 ce_fwd.register_autograd(
-    lambda ctx, dloss, dlse: (ce_bwd(dloss.contiguous(), ctx.saved_tensors[0], ctx.saved_tensors[1],
-                                     ctx.saved_tensors[2], ctx.ignore_index), None, None),
+    lambda ctx, dloss, dlse: ((None if dloss is None else
+                               ce_bwd(dloss.contiguous(), ctx.saved_tensors[0],
+                                      ctx.saved_tensors[1], ctx.saved_tensors[2],
+                                      ctx.ignore_index)), None, None),
     setup_context=_ce_setup)
 
 
@@ -767,12 +812,15 @@ def _(do, q, k, v, o, lse, causal, scale):
 def _attn_setup(ctx, inputs, output):
     q, k, v, causal, scale = inputs
     o, lse = output
+    ctx.set_materialize_grads(False)
     ctx.save_for_backward(q, k, v, o, lse)
     ctx.causal, ctx.scale = causal, scale
 
 
 def _attn_backward(ctx, do, dlse):
     q, k, v, o, lse = ctx.saved_tensors
+    if do is None:
+        return (None,) * 5
     dq, dk, dv = attn_bwd(do.contiguous(), q, k, v, o, lse, ctx.causal, ctx.scale)
     return dq, dk, dv, None, None
 
@@ -823,12 +871,15 @@ def _(do, qkv, o, lse, causal, scale):
 def _attn_qkv_setup(ctx, inputs, output):
     qkv, causal, scale = inputs
     o, lse = output
+    ctx.set_materialize_grads(False)
     ctx.save_for_backward(qkv, o, lse)
     ctx.causal, ctx.scale = causal, scale
 
 
 def _attn_qkv_backward(ctx, do, dlse):
     qkv, o, lse = ctx.saved_tensors
+    if do is None:
+        return None, None, None
     return attn_qkv_bwd(do.contiguous(), qkv, o, lse, ctx.causal, ctx.scale), None, None
 
 
@@ -1019,12 +1070,15 @@ def _(dy, x, mean, rstd, gamma, beta, groups, silu_act):
 
 def _gn_setup(ctx, inputs, output):
     x, gamma, beta, groups, eps, silu_act = inputs
+    ctx.set_materialize_grads(False)
     ctx.save_for_backward(x, output[1], output[2], gamma, beta)
     ctx.groups, ctx.silu_act = groups, silu_act
 
 
 def _gn_backward(ctx, dy, dmean, drstd):
     x, mean, rstd, gamma, beta = ctx.saved_tensors
+    if dy is None:
+        return (None,) * 6
     dx, dg, db = group_norm_bwd(dy.contiguous(), x, mean, rstd, gamma, beta, ctx.groups,
                                 ctx.silu_act)
     return dx, dg.to(gamma.dtype), db.to(beta.dtype), None, None, None

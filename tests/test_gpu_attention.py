@@ -25,6 +25,13 @@ CASES = [  # B, H, Sq, Sk, D, causal
     (2, 2, 128, 77, 64, False),      # UNet cross attention
     (1, 1, 1024, 1024, 64, False),
     (1, 2, 64, 64, 32, True),
+    # a few rows past a multiple of 128: leftover queries / keys run on CUDA cores
+    (2, 2, 259, 259, 64, True),
+    (1, 2, 130, 257, 96, False),
+    (1, 2, 260, 384, 32, False),
+    (1, 2, 256, 258, 64, False),
+    (1, 2, 261, 261, 64, False),     # five leftover rows: a ragged tensor-core tile instead
+    (1, 2, 258, 300, 64, True),      # causal with Sq != Sk: ragged key tiles in the backward
 ]
 
 
