@@ -13,7 +13,9 @@ Prints ONE JSON line on the global main process.  ``value`` is whole-job samples
 device-timed loop (CUDA events, barrier + synchronize on both sides, max over ranks) with the
 inputs resident on the device; ``e2e.value`` repeats the measurement with every step copying
 its inputs from pinned host memory and reading the loss back.  With more than one GPU the
-PPxDP mesh is chosen by the planner from a profile taken on rank 0 (``--dp_mesh`` overrides).
+PPxDP mesh is chosen by the planner from a profile taken on rank 0 before the process groups
+are built (``--dp_mesh`` overrides; the table it chose from is reported as
+``planner_mesh_table``).
 Synthetic data, random-init weights.
 """
 from __future__ import annotations
@@ -124,6 +126,56 @@ def emit_result(args, impl, n_gpus, ms, ms_e2e, samples, clocks, launches, paral
 
 
 # ------------------------------------------------------------------------------ native arm
+def _planned_mesh(args, cfg, world, rank, cpu):
+    """The PP x DP mesh for `world` GPUs, chosen by the planner: rank 0 profiles one micro-batch
+    of the model on its GPU and evaluates every factorisation of the world size; the others read
+    its answer from a key-value store (the process groups do not exist yet -- they depend on
+    the answer).  Falls back to pure data parallelism if planning fails on rank 0."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 17
+    store = dist.TCPStore(host, port, world, is_master=(rank == 0),
+                          timeout=datetime.timedelta(seconds=1200))
+    if rank == 0:
+        mesh, table = f"-{world},1", None
+        try:
+            from pfeife_b200 import PipeOption
+            from pfeife_b200.models.vit import ViT
+            from pfeife_b200.parallel.mesh_plan import plan_mesh
+            dev = torch.device("cpu") if cpu else torch.device(
+                "cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            if not cpu:
+                torch.cuda.set_device(dev)
+            torch.manual_seed(0)
+            model = ViT(cfg).to(dev)
+            opt = PipeOption(device_cnt=1, batch_size=args.batch_size, batch_cnt=args.batch_cnt,
+                             mixed_precision=None if cpu else "fp16", cpu_test=cpu,
+                             no_bench_optimizer=True, verbosity="warning")
+            x = torch.randn(args.batch_size, 3, 224, 224, device=dev,
+                            dtype=torch.float32 if cpu else torch.float16)
+            choice = plan_mesh(model, (x,), opt, world, dev)
+            mesh = choice.dp_mesh
+            table = [{"pp": a, "dp": b, "step_ms": round(c, 2), "samples_per_s": round(d, 1),
+                      "fits": bool(e)} for a, b, c, d, e in choice.table]
+            del model, choice, x
+            if not cpu:
+                torch.cuda.empty_cache()
+        except Exception as exc:   # planning must never take the benchmark down
+            print(f"[bench] mesh planning failed ({type(exc).__name__}: {exc}); "
+                  f"using pure data parallelism", file=sys.stderr, flush=True)
+        store.set("mesh", json.dumps({"mesh": mesh, "table": table}))
+    got = json.loads(store.get("mesh").decode())
+    # every rank has read the answer before rank 0 (the store's server) moves on
+    store.add("mesh_read", 1)
+    if rank == 0:
+        deadline = time.time() + 600
+        while int(store.add("mesh_read", 0)) < world and time.time() < deadline:
+            time.sleep(0.05)
+    return got["mesh"], got["table"]
+
+
 def run_native(args) -> int:
     import torch
     import torch.distributed as dist
@@ -145,8 +197,9 @@ def run_native(args) -> int:
                     num_layers=args.layers, num_heads=args.heads, mlp_dim=args.mlp,
                     num_classes=1000)
     dp_mesh = args.dp_mesh
-    if dp_mesh is None and world > 1:
-        dp_mesh = f"-{world},1"      # ViT-g fits one GPU: data parallel is the planner's pick
+    planned = None
+    if dp_mesh in (None, "auto") and world > 1:
+        dp_mesh, planned = _planned_mesh(args, cfg, world, rank, cpu)
     state = initialize_pfeife(dp_mesh=dp_mesh, cpu=cpu)
     dev = state.device
     mp = None if cpu else "fp16"
@@ -247,6 +300,7 @@ def run_native(args) -> int:
                     h2d=host_x16.numel() * host_x16.element_size() + host_y.numel() * 8, d2h=4,
                     extra={"dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
                            if state.dp_size > 1 else None,
+                           "planner_mesh_table": planned,
                            "optimizer_and_dp_exposed_ms": runner.worker.last_optimizer_ms(),
                            "pipeline_bubble_pct": 100.0 * bubble})
     runner.close()

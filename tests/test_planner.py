@@ -204,3 +204,19 @@ def test_mesh_choice_prefers_dp_for_a_model_that_fits_and_pp_when_it_does_not():
     small = choose_mesh(cg, 8, opt, bench, device_mem=60e6)   # 64 MB of weights do not fit
     assert small.pp > 1 and small.pp * small.dp == 8
     assert dp_exposed_time(4e9, 1, bench) == 0.0 and dp_exposed_time(4e9, 8, bench) > 0
+
+
+def test_plan_mesh_profiles_a_model_and_ranks_every_factorisation():
+    """`plan_mesh` captures, profiles (CPU pass here) and returns one row per PP x DP = world."""
+    import torch
+    from pfeife_b200 import PipeOption, plan_mesh
+    from pfeife_b200.models.vit import ViT, vit_config
+    torch.manual_seed(0)
+    model = ViT(vit_config("vit_tiny", num_layers=4, image_size=32, patch_size=8))
+    opt = PipeOption(device_cnt=1, batch_size=4, batch_cnt=4, cpu_test=True)
+    choice = plan_mesh(model, (torch.randn(4, 3, 32, 32),), opt, 4, torch.device("cpu"))
+    assert sorted((pp, dp) for pp, dp, *_ in choice.table) == [(1, 4), (2, 2), (4, 1)]
+    assert choice.pp * choice.dp == 4
+    best = max(choice.table, key=lambda r: (r[4], r[3]))
+    assert (choice.pp, choice.dp) == (best[0], best[1])
+    assert choice.dp_mesh == (f"-{choice.dp},{choice.pp}" if choice.dp > 1 else f"{choice.pp}")
