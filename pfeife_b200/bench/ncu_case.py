@@ -1,7 +1,7 @@
 """Small single-kernel workloads for Nsight Compute captures (a few launches, inputs larger than
 L2, a few hundred MB on the device at most).
 
-    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_wgrad,attn,norm,adamw,ce}
+    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_wgrad,attn,norm,adamw,ce,unet,llama}
 
 Each case launches its kernel(s) a handful of times and checks the kernel status word, so the
 same command can first be run plainly (must exit 0) and then under
@@ -73,6 +73,28 @@ def main(argv=None) -> int:
         for _ in range(reps):
             loss, lse = kx.ce_fwd(logits, tgt)
             kx.ce_bwd(logits, tgt, lse, torch.full((rows,), 1.0 / rows, device=dev))
+    elif which == "unet":     # SDXL UNet block kernels: GroupNorm+SiLU fwd/bwd, im2col, col2im
+        B, H, W, C = 4, 64, 64, 640
+        x = torch.randn(B, H, W, C, device=dev).to(torch.bfloat16)
+        g, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+        for _ in range(reps):
+            y, mean, rstd = kx.groupnorm_fwd(x, g, b, 32, 1e-5, True)
+            kx.groupnorm_bwd(y, x, mean, rstd, g, b, 32, True)
+            cols = kx.im2col(x, 3, 3, 1, 1)
+            kx.col2im(cols, (B, H, W, C), 3, 3, 1, 1)
+    elif which == "llama":    # Llama-2-7B elementwise kernels: SwiGLU fwd/bwd, RoPE, embedding
+        rows, Hd = 2048, 11008
+        gu = torch.randn(rows, 2 * Hd, device=dev).to(torch.bfloat16)
+        do = torch.randn(rows, Hd, device=dev).to(torch.bfloat16)
+        q = torch.randn(1, 2048, 32, 128, device=dev).to(torch.bfloat16)
+        ang = torch.rand(2048, 64, device=dev)
+        table = torch.randn(32000, 4096, device=dev)
+        ids = torch.randint(0, 32000, (8, 2048), device=dev)
+        for _ in range(reps):
+            kx.glu_fwd(gu, False)
+            kx.glu_bwd(gu, do, False)
+            kx.rope(q, ang.cos(), ang.sin())
+            kx.embed_fwd(table, ids, torch.bfloat16)
     else:
         print(f"unknown case {which}", file=sys.stderr)
         return 2

@@ -95,11 +95,13 @@ PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const vo
 // ---- dp_fused.cu : reduce-scatter + AdamW + all-gather over NVLink peer memory, IPC plumbing
 PF_DECL int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                              void* const* lp, void* const* flags, void* m, void* v,
-                             void* local_sync, long long shard_lo, long long shard_hi, float lr,
-                             float beta1, float beta2, float eps, float weight_decay, int step,
-                             float grad_scale, int adamw, int lp_dtype, int check_inf,
-                             const void* loss_scale, void* found_inf, int epoch, int calls_before,
-                             int* status, int sm_count, void* stream);
+                             void* local_sync, long long shard_lo, long long shard_hi,
+                             long long lp_local_below, float lr, float beta1, float beta2,
+                             float eps, float weight_decay, int step, float grad_scale, int adamw,
+                             int lp_dtype, int check_inf, const void* loss_scale, void* found_inf,
+                             int epoch, int calls_before, int* status, int sm_count, void* stream);
+PF_DECL int pf_gather_rows(void* dst, void* const* copies, const int* row_end, int world, int rank,
+                           int rows, long long row_bytes, int sm_count, void* stream);
 PF_DECL int pf_ipc_get_handle(void* ptr, void* handle_out_64);
 PF_DECL int pf_ipc_open(const void* handle_64, void** ptr_out);
 PF_DECL int pf_ipc_close(void* ptr);
@@ -124,8 +126,8 @@ PF_DECL int pf_upsample2x(const void* x, void* y, int B, int H, int W, int C, in
                           int dtype, int sm_count, void* stream);
 
 // ---- gemm_sm100.cu : GEMM with the all-gather of a row-sharded weight fused in
-PF_DECL int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, int world,
-                              int rank, int rows_per_rank, void* ready, void* C, int M, int N,
+PF_DECL int pf_gemm_allgather(const void* A, void* w_full, void* const* copies, int world,
+                              int rank, const int* row_end, void* ready, void* C, int M, int N,
                               int K, long long lda, long long ldb, long long ldc, int in_dtype,
                               int out_dtype, const void* bias, int bias_dtype,
                               const void* residual, long long ldr, void* aux, long long ldaux,

@@ -40,6 +40,8 @@ struct DpArgs {
   float* v;
   int* local_sync;             // local: [0] arrival counter, [1] release word
   long long shard_lo, shard_hi;
+  long long lp_local_below;    // 16-bit weights at flat indices below this are written locally
+                               // only: their consumers gather them (fused all-gather GEMM)
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
   int adamw, lp_dtype, check_inf;
   const float* loss_scale;     // local device scalar (identical on every rank) or null
@@ -193,9 +195,11 @@ dp_fused_kernel(const DpArgs a) {
         q = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&y));
       }
     }
+    const bool push_lp = e >= a.lp_local_below;
     for (int p = 0; p < a.world; ++p) {
       *reinterpret_cast<float4*>(a.master[p] + e) = nw;
-      if (a.lp[p]) *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q;
+      if (a.lp[p] && (push_lp || p == a.rank))
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q;
     }
   }
 
@@ -211,7 +215,8 @@ using namespace pf;
 // (number of earlier calls) * 3 * grid.  Returns the grid size used through *grid_out.
 PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                             void* const* lp, void* const* flags, void* m, void* v,
-                            void* local_sync, long long shard_lo, long long shard_hi, float lr,
+                            void* local_sync, long long shard_lo, long long shard_hi,
+                            long long lp_local_below, float lr,
                             float beta1, float beta2, float eps, float weight_decay, int step,
                             float grad_scale, int adamw, int lp_dtype, int check_inf,
                             const void* loss_scale, void* found_inf, int epoch, int calls_before,
@@ -228,6 +233,7 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   }
   a.m = (float*)m; a.v = (float*)v; a.local_sync = (int*)local_sync;
   a.shard_lo = shard_lo; a.shard_hi = shard_hi;
+  a.lp_local_below = lp_local_below;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
   a.bc1 = 1.f - powf(beta1, (float)step);
   a.bc2 = 1.f - powf(beta2, (float)step);
@@ -238,6 +244,64 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   const int grid = 2 * (sm_count > 0 ? sm_count : 148);
   a.sync_base = calls_before * 3 * grid;
   dp_fused_kernel<<<grid, DP_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  PF_CHECK_LAUNCH();
+  return 0;
+}
+
+// ---- rows of a weight owned by other ranks, copied into the local copy (plain peer loads).
+// Used when the first consumer of a freshly updated weight is not the fused all-gather GEMM.
+namespace pf {
+struct RowGatherArgs {
+  const void* src[DP_MAX];     // every rank's full-size copy [rows, row_bytes]
+  void* dst;                   // the local copy
+  int row_end[DP_MAX];
+  int world, rank, rows;
+  long long row_bytes;         // multiple of 16
+};
+__global__ void __launch_bounds__(256)
+row_gather_kernel(const RowGatherArgs a) {
+  const long long vec_per_row = a.row_bytes / 16;
+  const long long total = (long long)a.rows * vec_per_row;
+  const int own0 = a.rank > 0 ? a.row_end[a.rank - 1] : 0, own1 = a.row_end[a.rank];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  constexpr int U = 4;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total;
+       i0 += stride * U) {
+    uint4 buf[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      live[u] = false;
+      if (i < total) {
+        const int r = (int)(i / vec_per_row);
+        if (r < own0 || r >= own1) {
+          int owner = 0;
+          while (owner < a.world - 1 && r >= a.row_end[owner]) ++owner;
+          buf[u] = reinterpret_cast<const uint4*>(a.src[owner])[i];
+          live[u] = true;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (live[u]) reinterpret_cast<uint4*>(a.dst)[i0 + u * stride] = buf[u];
+  }
+}
+}  // namespace pf
+
+PF_API int pf_gather_rows(void* dst, void* const* copies, const int* row_end, int world, int rank,
+                          int rows, long long row_bytes, int sm_count, void* stream) {
+  if (world < 1 || world > DP_MAX || row_bytes % 16) return -3;
+  if (rows <= 0 || world == 1) return 0;
+  RowGatherArgs a = {};
+  for (int i = 0; i < DP_MAX; ++i) {
+    a.src[i] = i < world ? copies[i] : nullptr;
+    a.row_end[i] = i < world ? row_end[i] : rows;
+  }
+  a.dst = dst; a.world = world; a.rank = rank; a.rows = rows; a.row_bytes = row_bytes;
+  const int grid = 4 * (sm_count > 0 ? sm_count : 148);
+  row_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   PF_CHECK_LAUNCH();
   return 0;
 }

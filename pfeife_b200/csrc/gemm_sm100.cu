@@ -57,8 +57,9 @@ struct GemmParams {
   // ---- fused all-gather of the B operand (weights sharded by rows over `gather_world` ranks)
   int gather_world;            // 0: B is an ordinary local operand
   int gather_rank;
-  int gather_rows;             // rows of B owned by each rank
-  const void* gather_src[8];   // peer pointers to every rank's shard [gather_rows, K] (pitch ldb)
+  int gather_row_end[8];       // rank r owns rows [gather_row_end[r-1], gather_row_end[r]) of B
+  const void* gather_src[8];   // every rank's copy of B [N, K] (pitch ldb), peer-mapped; only
+                               // the rows a rank owns are valid (and read) in its copy
   void* gather_dst;            // local full-size B [N, K] (pitch ldb); own rows already in place
   int* gather_ready;           // local counters, one per BN-row tile of B, zeroed before launch
   long long gather_ld;
@@ -177,7 +178,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   // with a fused all-gather the tiles whose rows of B this rank owns are computed first, while
   // the remote rows are still arriving
-  const int n_rot = (GATHER && p.gather_world > 1) ? (p.gather_rank * p.gather_rows) / BNT : 0;
+  const int own0 = (GATHER && p.gather_rank > 0) ? p.gather_row_end[p.gather_rank - 1] : 0;
+  const int own1 = GATHER ? p.gather_row_end[p.gather_rank] : 0;
+  const int n_rot = (GATHER && p.gather_world > 1) ? own0 / BNT : 0;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -225,7 +228,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (GATHER && p.gather_world > 1 && !all_gathered) {
           // rows of this B tile that other ranks own must have landed in the local buffer
           const int n1 = min(p.N, n0 + BNT);
-          const int own0 = p.gather_rank * p.gather_rows, own1 = own0 + p.gather_rows;
           const int expect = (n1 - n0) - max(0, min(n1, own1) - max(n0, own0));
           if (expect > 0) {
             long long t0 = clock64();
@@ -344,11 +346,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n_ew = gridDim.x * GEMM_GATHER_WARPS;
       const int kvec = p.K / 8;
       for (int r = ew; r < p.N; r += n_ew) {
-        const int owner = r / p.gather_rows;
-        if (owner == p.gather_rank) continue;
+        if (r >= own0 && r < own1) continue;
+        int owner = 0;
+        while (owner < p.gather_world - 1 && r >= p.gather_row_end[owner]) ++owner;
         const uint4* src = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const uint16_t*>(p.gather_src[owner]) +
-            (long long)(r - owner * p.gather_rows) * p.gather_ld);
+            reinterpret_cast<const uint16_t*>(p.gather_src[owner]) + (long long)r * p.gather_ld);
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.gather_dst) +
                                               (long long)r * p.gather_ld);
         // up to 8 vectors per lane are requested before any is stored (latency hiding)
@@ -648,7 +650,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 using namespace pf;
 
 // all-gather arguments of the call in flight on this thread (set by pf_gemm_allgather)
-struct GatherArgs { int world = 0, rank = 0, rows = 0; int* ready = nullptr; const void* src[8] = {}; };
+struct GatherArgs { int world = 0, rank = 0; int row_end[8] = {}; int* ready = nullptr; const void* src[8] = {}; };
 static thread_local GatherArgs g_gather;
 
 PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -700,7 +702,8 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
   p.epilogue = epilogue; p.accumulate = accumulate;
   p.alpha = alpha; p.a_mn = a_mn; p.b_mn = b_mn; p.fmt = fmt; p.status = status;
   p.gather_world = g_gather.world; p.gather_rank = g_gather.rank;
-  p.gather_rows = g_gather.rows; p.gather_dst = const_cast<void*>(B);
+  for (int i = 0; i < 8; ++i) p.gather_row_end[i] = g_gather.row_end[i];
+  p.gather_dst = const_cast<void*>(B);
   p.gather_ready = g_gather.ready; p.gather_ld = ldb;
   for (int i = 0; i < 8; ++i) p.gather_src[i] = g_gather.src[i];
   const size_t es = out_dtype == PF_F32 ? 4 : 2;
@@ -744,26 +747,32 @@ PF_API int pf_tmap_probe(const void* base, long long inner, long long outer, lon
   return make_tmap_2d_16bit(&m, base, 1, inner, outer, ld, box_inner, box_outer);
 }
 
-// C[M,N] = epi(A[M,K] . W[N,K]^T) where W is sharded by rows over `world` ranks: rank r owns rows
-// [r*rows_per_rank, (r+1)*rows_per_rank) and `shards[r]` is a pointer (peer-mapped for r != rank)
-// to its [rows_per_rank, K] shard with pitch ldb.  `w_full` is a local [N, K] buffer (pitch ldb)
-// that already holds this rank's rows; the kernel fills in the others while it computes.
-// `ready` is an int array with one entry per 256-row tile of W plus one for the running total
-// (zeroed here).
-PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* shards, int world, int rank,
-                             int rows_per_rank, void* ready, void* C, int M, int N, int K,
+// C[M,N] = epi(A[M,K] . W[N,K]^T) where the rows of W are owned by `world` ranks: rank r owns
+// rows [row_end[r-1], row_end[r]) (row_end[world-1] == N) and `copies[r]` points at rank r's
+// full-size copy of W (pitch ldb, peer-mapped for r != rank) in which at least the rows it owns
+// are current.  `w_full` is this rank's copy; the kernel fills in the other ranks' rows while it
+// computes.  `ready` is an int array with one entry per 256-row tile of W plus one for the
+// running total (zeroed here).
+PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* copies, int world, int rank,
+                             const int* row_end, void* ready, void* C, int M, int N, int K,
                              long long lda, long long ldb, long long ldc, int in_dtype,
                              int out_dtype, const void* bias, int bias_dtype,
                              const void* residual, long long ldr, void* aux, long long ldaux,
                              int epilogue, float alpha, int* status, int sm_count, void* stream) {
   if (world < 1 || world > 8 || K % 8) return -3;
+  for (int i = 0; i < world; ++i)
+    if (row_end[i] < (i ? row_end[i - 1] : 0) || row_end[i] > N) return -3;
+  if (row_end[world - 1] != N) return -3;
   const int tiles = (N + 255) / 256 + 1;
   cudaError_t e = cudaMemsetAsync(ready, 0, sizeof(int) * tiles,
                                   reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return (int)e;
-  g_gather.world = world; g_gather.rank = rank; g_gather.rows = rows_per_rank;
+  g_gather.world = world; g_gather.rank = rank;
   g_gather.ready = (int*)ready;
-  for (int i = 0; i < 8; ++i) g_gather.src[i] = i < world ? shards[i] : nullptr;
+  for (int i = 0; i < 8; ++i) {
+    g_gather.src[i] = i < world ? copies[i] : nullptr;
+    g_gather.row_end[i] = i < world ? row_end[i] : N;
+  }
   const int r = pf_gemm(A, w_full, C, M, N, K, lda, ldb, ldc, 0, 0, in_dtype, out_dtype, bias,
                         bias_dtype, residual, ldr, aux, ldaux, epilogue, 0, alpha, status,
                         sm_count, 256, stream);

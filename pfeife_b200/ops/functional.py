@@ -36,6 +36,19 @@ _ACT_NAMES = {None: 0, "none": 0, "gelu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh"
 class ParamSlot:
     lp: Optional[Tensor] = None          # 16-bit shadow of the master weight
     main_grad: Optional[Tensor] = None   # fp32 view into the flat gradient bucket
+    # Deferred all-gather (sharded data parallelism): after an optimizer step only the rows this
+    # rank owns are current in `lp`; the first consumer pulls the other rows from their owners.
+    gather: Optional["GatherInfo"] = None
+    fresh_epoch: int = 0                 # optimizer step whose weights `lp` holds in full
+
+
+@dataclass
+class GatherInfo:
+    copies: object                       # ctypes array: every rank's pointer to its copy of lp
+    row_end: Tuple[int, ...]             # rank r owns rows [row_end[r-1], row_end[r])
+    world: int
+    rank: int
+    ready: Tensor                        # int32 scratch: one counter per 256-row tile + 1
 
 
 _PARAMS: Dict[int, ParamSlot] = {}
@@ -43,13 +56,42 @@ _PARAMS: Dict[int, ParamSlot] = {}
 
 def register_param(master: Tensor, lp: Optional[Tensor] = None,
                    main_grad: Optional[Tensor] = None) -> None:
-    _PARAMS[master.data_ptr()] = ParamSlot(lp, main_grad)
+    slot = ParamSlot(lp, main_grad)
+    _PARAMS[master.data_ptr()] = slot
     if lp is not None:
-        _PARAMS[lp.data_ptr()] = ParamSlot(lp, main_grad)
+        _PARAMS[lp.data_ptr()] = slot
 
 
 def unregister_params() -> None:
     _PARAMS.clear()
+
+
+_weights_epoch = 0   # bumped by the data-parallel layer after every optimizer step
+
+
+def weights_updated() -> None:
+    """The optimizer step of the data-parallel layer has run: 16-bit weights with a deferred
+    all-gather now hold current values only in the rows their rank owns."""
+    global _weights_epoch
+    _weights_epoch += 1
+
+
+def set_gather(master: Tensor, info: GatherInfo) -> None:
+    """Marks the registered parameter `master` as row-sharded between optimizer steps."""
+    slot = _PARAMS[master.data_ptr()]
+    slot.gather = info
+    slot.fresh_epoch = -1
+
+
+def _stale(slot: Optional[ParamSlot]) -> bool:
+    return slot is not None and slot.gather is not None and slot.fresh_epoch != _weights_epoch
+
+
+def _gather_now(slot: ParamSlot) -> None:
+    """Stand-alone gather of the other ranks' rows (first consumer is not the fused GEMM)."""
+    g = slot.gather
+    kx.gather_rows(slot.lp.view(slot.lp.shape[0], -1), g.copies, g.world, g.rank, g.row_end)
+    slot.fresh_epoch = _weights_epoch
 
 
 def _slot(t: Tensor) -> Optional[ParamSlot]:
@@ -83,6 +125,8 @@ def _weight_as(w: Tensor, dtype: torch.dtype) -> Tensor:
         return w
     s = _slot(w)
     if s is not None and s.lp is not None and s.lp.dtype == dtype:
+        if _stale(s):
+            _gather_now(s)
         return s.lp
     return kx.cast(w, dtype) if w.is_cuda else w.to(dtype)
 
@@ -141,7 +185,10 @@ def linear_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], residual: Optional[
     out_shape = x.shape[:-1] + (N,)
     if x.is_cuda and cd in (torch.float16, torch.bfloat16):
         x2 = _rows(x if x.dtype == cd else kx.cast(x, cd))
-        w2 = _weight_as(w, cd)
+        slot = _slot(w)
+        fused_gather = _stale(slot) and slot.lp is not None and slot.lp.dtype == cd and \
+            slot.lp.dim() == 2 and x2.shape[1] % 8 == 0
+        w2 = slot.lp if fused_gather else _weight_as(w, cd)
         if x2.shape[1] % 8:
             x2, w2 = _pad_k(x2), _pad_k(w2)
         r2 = None
@@ -152,7 +199,15 @@ def linear_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], residual: Optional[
         aux = torch.empty((M, N), dtype=cd, device=x.device) if act else None
         epi = {ACT_NONE: kx.EPI_NONE, ACT_GELU: kx.EPI_GELU, ACT_GELU_TANH: kx.EPI_GELU_TANH,
                ACT_SILU: kx.EPI_SILU}[act]
-        kx.gemm(x2, w2, out=y, bias=bias, residual=r2, aux=aux, epilogue=epi)
+        if fused_gather:
+            # first use of this weight since the optimizer step: the GEMM pulls the other
+            # ranks' rows over NVLink while it computes the tiles whose rows are local
+            g = slot.gather
+            kx.gemm_allgather(x2, w2, g.copies, g.world, g.rank, g.row_end, g.ready, out=y,
+                              bias=bias, residual=r2, aux=aux, epilogue=epi)
+            slot.fresh_epoch = _weights_epoch
+        else:
+            kx.gemm(x2, w2, out=y, bias=bias, residual=r2, aux=aux, epilogue=epi)
         return y.view(out_shape), (aux.view(out_shape) if act else x.new_empty(0))
     # reference path (CPU, or fp32 on CUDA)
     xw = x.to(cd)

@@ -462,21 +462,24 @@ def upsample2x(x: torch.Tensor, backward: bool = False) -> torch.Tensor:
     return y
 
 
-def gemm_allgather(a: torch.Tensor, w_full: torch.Tensor, shard_table, world: int, rank: int,
-                   rows_per_rank: int, ready: torch.Tensor, *, bias=None, residual=None, aux=None,
+def gemm_allgather(a: torch.Tensor, w_full: torch.Tensor, copies_table, world: int, rank: int,
+                   row_end, ready: torch.Tensor, *, bias=None, residual=None, aux=None,
                    epilogue: int = EPI_NONE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = epi(a @ W^T) with W sharded by rows over `world` ranks; the kernel pulls the other
-    ranks' rows into ``w_full`` over NVLink while it computes the tiles it already has.
+    """out = epi(a @ W^T) where the rows of W are owned by `world` ranks (rank r owns rows
+    [row_end[r-1], row_end[r])); the kernel pulls the other ranks' rows into ``w_full`` over
+    NVLink while it computes the tiles it already has.
 
-    ``shard_table`` is a ctypes array of per-rank shard pointers (see
-    ``parallel.dp_fused.PeerMemory.share``); ``ready`` an int32 tensor with one entry per
-    256-row tile of W plus one (the running total)."""
+    ``copies_table`` is a ctypes array with every rank's pointer to its full-size copy of W
+    (peer-mapped, see ``parallel.dp_fused.PeerMemory.share``); a copy only has to be current in
+    the rows its rank owns.  ``ready`` is an int32 tensor with one entry per 256-row tile of W
+    plus one (the running total)."""
     L = _lib.lib()
     M, K = a.shape
     N = w_full.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=a.dtype, device=a.device)
-    check(L.pf_gemm_allgather(ptr(a), ptr(w_full), shard_table, world, rank, rows_per_rank,
+    ends = (ctypes.c_int * world)(*[int(x) for x in row_end])
+    check(L.pf_gemm_allgather(ptr(a), ptr(w_full), copies_table, world, rank, ends,
                               ptr(ready), ptr(out), M, N, K, c_ll(a.stride(0)),
                               c_ll(w_full.stride(0)), c_ll(out.stride(0)), dt(a.dtype),
                               dt(out.dtype), ptr(bias), dt(bias.dtype) if bias is not None else 0,
@@ -485,3 +488,14 @@ def gemm_allgather(a: torch.Tensor, w_full: torch.Tensor, shard_table, world: in
                               c_f(1.0), ptr(status_word(a.device)), sm_count(a.device), stream()),
           "pf_gemm_allgather")
     return out
+
+
+def gather_rows(w_full: torch.Tensor, copies_table, world: int, rank: int, row_end) -> None:
+    """Copies the rows of a [rows, K] weight that other ranks own from their copies into
+    ``w_full`` (stand-alone form of the gather, for first consumers that are not a GEMM)."""
+    L = _lib.lib()
+    assert w_full.dim() == 2 and w_full.is_contiguous()
+    ends = (ctypes.c_int * world)(*[int(x) for x in row_end])
+    check(L.pf_gather_rows(ptr(w_full), copies_table, ends, world, rank, w_full.shape[0],
+                           c_ll(w_full.shape[1] * w_full.element_size()),
+                           sm_count(w_full.device), stream()), "pf_gather_rows")

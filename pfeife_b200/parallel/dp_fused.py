@@ -13,7 +13,7 @@ Optimizers other than Adam / AdamW fall back to the NCCL path.
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -117,6 +117,36 @@ def _table(ptrs: List[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
 
+def shard_bounds(numel: int, world: int, matrices=()) -> List[int]:
+    """Ownership boundaries [b_0 = 0, ..., b_world = numel] of the flat parameter buffer: an even
+    split in units of ALIGN elements, except that a boundary falling inside one of `matrices`
+    ((offset, cols, rows) of a weight whose 16-bit copy is gathered row by row) moves to the
+    nearest boundary between two of its rows, so that every row has one owner."""
+    per = (numel + world - 1) // world
+    per = (per + ALIGN - 1) // ALIGN * ALIGN
+    bounds = [min(numel, r * per) for r in range(world + 1)]
+    bounds[world] = numel
+    for i in range(1, world):
+        b = bounds[i]
+        for off, cols, rows in matrices:
+            if off < b < off + rows * cols:
+                b = off + int(round((b - off) / cols)) * cols
+                break
+        bounds[i] = max(bounds[i - 1], b)
+    return bounds
+
+
+def row_ends(offset: int, cols: int, rows: int, bounds: Sequence[int]) -> List[int]:
+    """For a [rows, cols] matrix at `offset` of the flat buffer: row_end[r] such that rank r owns
+    rows [row_end[r-1], row_end[r]) under the ownership `bounds`."""
+    ends = []
+    for r in range(len(bounds) - 1):
+        hi = min(max(bounds[r + 1] - offset, 0), rows * cols)
+        ends.append(hi // cols)
+    ends[-1] = rows
+    return ends
+
+
 class FusedDP(NcclDP):
     fused = True
 
@@ -137,9 +167,11 @@ class FusedDP(NcclDP):
             self.fused = False
             return
         n = params.numel
-        per = (n + self.size - 1) // self.size
-        per = (per + ALIGN - 1) // ALIGN * ALIGN
-        self.shard = (min(n, self.rank * per), min(n, (self.rank + 1) * per))
+        deferred = [s for s in params.slots.values() if getattr(s, "deferred", False)]
+        bounds = shard_bounds(n, self.size, [(s.offset, s.entry.tensor.shape[1],
+                                              s.entry.tensor.shape[0]) for s in deferred])
+        self.bounds = bounds
+        self.shard = (bounds[self.rank], bounds[self.rank + 1])
         ln = max(self.shard[1] - self.shard[0], 4)
         self.m = torch.zeros(ln, dtype=torch.float32, device=self.device)
         self.v = torch.zeros(ln, dtype=torch.float32, device=self.device)
@@ -150,6 +182,17 @@ class FusedDP(NcclDP):
         self.t_master = _table(self.peers.share(params.master))
         self.t_lp = _table(self.peers.share(params.lp)) if params.lp is not None else None
         self.t_flags = _table(self.peers.share(self.flags))
+        self.deferred_below = dict(getattr(params, "deferred_below", {})) if deferred else {}
+        if deferred and self.t_lp is not None:
+            from ..ops import functional as Fn
+            es = params.lp.element_size()
+            for s in deferred:
+                rows, cols = s.entry.tensor.shape
+                ends = tuple(row_ends(s.offset, cols, rows, bounds))
+                copies = _table([int(base) + s.offset * es for base in self.t_lp])
+                ready = torch.zeros((rows + 255) // 256 + 1, dtype=torch.int32,
+                                    device=self.device)
+                Fn.set_gather(s.master, Fn.GatherInfo(copies, ends, self.size, self.rank, ready))
         dist.barrier(group=self.state.ctrl_dp)
 
     def reduce_and_step(self, params, scaler, fp16: bool) -> None:
@@ -168,7 +211,8 @@ class FusedDP(NcclDP):
             v = self.v[off:] if off < self.v.numel() else self.v
             code = L.pf_dp_fused_step(
                 self.rank, self.size, self.t_grad, self.t_master, self.t_lp, self.t_flags,
-                ptr(m), ptr(v), ptr(self.local_sync), c_ll(a), c_ll(b), c_f(h.get("lr", 1e-3)),
+                ptr(m), ptr(v), ptr(self.local_sync), c_ll(a), c_ll(b),
+                c_ll(self.deferred_below.get(g, 0)), c_f(h.get("lr", 1e-3)),
                 c_f(b1), c_f(b2), c_f(h.get("eps", 1e-8)),
                 c_f(h.get("weight_decay", 0.01 if adamw else 0.0)), int(params.step_count),
                 c_f(1.0 / self.size), int(adamw),
@@ -177,6 +221,9 @@ class FusedDP(NcclDP):
                 ptr(kx.status_word(self.device)), sm_count(self.device), stream())
             check(code, "pf_dp_fused_step")
             self.calls += 1
+        if self.deferred_below:
+            from ..ops import functional as Fn
+            Fn.weights_updated()
         if fp16:
             scaler.update(params.found_inf)
 

@@ -32,6 +32,13 @@ _HYPER_KEYS = ("lr", "betas", "eps", "weight_decay", "momentum", "dampening", "n
                "amsgrad", "maximize")
 
 
+def gather_deferrable(t: torch.Tensor) -> bool:
+    """A weight whose 16-bit copy may stay row-sharded between the optimizer step and its first
+    consumer: a matrix a linear layer reads (rows = output features), wide enough for 16-byte
+    row transfers and large enough for the transfer to matter."""
+    return t.dim() == 2 and t.shape[1] % 8 == 0 and t.shape[0] >= 256 and t.numel() >= (1 << 18)
+
+
 def snapshot_hyper(optimizer) -> List[Dict[str, Any]]:
     """The picklable hyper-parameters of every param group of a torch optimizer."""
     out = []
@@ -60,15 +67,19 @@ class _Slot:
     master: Optional[torch.Tensor] = None
     grad: Optional[torch.Tensor] = None
     lp: Optional[torch.Tensor] = None
+    deferred: bool = False    # all-gather of `lp` left to its first consumer
 
 
 class RankParams:
     def __init__(self, entries: Sequence[StateEntry], device: torch.device,
                  lp_dtype: Optional[torch.dtype], optimizer_type: str,
                  hyper: List[Dict[str, Any]], native: Optional[bool] = None,
-                 alloc=None):
+                 alloc=None, defer_gather: bool = False):
         """`alloc(numel, dtype) -> Tensor` lets the data-parallel layer place the flat buffers
-        in peer-accessible memory."""
+        in peer-accessible memory.  With `defer_gather` the matrices that linear layers consume
+        are packed first within their optimizer group, so that the data-parallel step can leave
+        the all-gather of their 16-bit copies to the first GEMM that reads them
+        (``deferred_below`` = end of that region per group)."""
         self.device = device
         self.lp_dtype = lp_dtype
         self.optimizer_type = optimizer_type.lower()
@@ -79,9 +90,12 @@ class RankParams:
 
         packed = [e for e in entries if e.kind == "param" and e.requires_grad
                   and e.tensor.dtype.is_floating_point]
-        packed.sort(key=lambda e: (e.group, e.ph_index))
+        defer = bool(defer_gather and lp_dtype is not None and self.native)
+        deferrable = (lambda e: defer and gather_deferrable(e.tensor))
+        packed.sort(key=lambda e: (e.group, not deferrable(e), e.ph_index))
         self.slots: Dict[int, _Slot] = {}
         self.group_ranges: List[Tuple[int, int, int]] = []   # (group, lo, hi)
+        self.deferred_below: Dict[int, int] = {}             # group -> end of its deferred region
         off = 0
         cur_group, group_lo = None, 0
         for e in packed:
@@ -89,9 +103,12 @@ class RankParams:
                 if cur_group is not None:
                     self.group_ranges.append((cur_group, group_lo, off))
                 cur_group, group_lo = e.group, off
+                self.deferred_below[e.group] = off
             n = e.tensor.numel()
-            self.slots[e.ph_index] = _Slot(e, off, n)
+            self.slots[e.ph_index] = _Slot(e, off, n, deferred=deferrable(e))
             off += (n + ALIGN - 1) // ALIGN * ALIGN
+            if deferrable(e):
+                self.deferred_below[e.group] = off
         if cur_group is not None:
             self.group_ranges.append((cur_group, group_lo, off))
         self.numel = off

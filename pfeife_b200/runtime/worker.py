@@ -222,7 +222,12 @@ class StageWorker:
         lp = self.option.mixed_precision
         alloc = self.dp.allocator() if (self.dp is not None and hasattr(self.dp, "allocator")) \
             else None
-        self.params = RankParams(entries, self.device, lp, optimizer_type, hyper, alloc=alloc)
+        # --use_fsdp with the fused data-parallel step: weight matrices stay row-sharded after
+        # the optimizer step and are gathered by the first GEMM that reads them
+        defer = bool(getattr(self.option, "use_fsdp", False)) and self.dp is not None and \
+            getattr(self.dp, "fused", False)
+        self.params = RankParams(entries, self.device, lp, optimizer_type, hyper, alloc=alloc,
+                                 defer_gather=defer)
         self.stage_mods: Dict[int, Any] = {}
         for sp in part.stages_of_rank(self.pp_rank):
             gm = sp.gm

@@ -35,19 +35,23 @@ def main():
     w_all = (torch.randn(N, K, generator=g) * 0.05).to(torch.float16)
     x = torch.randn(M, K, generator=g).to(torch.float16).to(dev)
     shard = w_all[r * rows:(r + 1) * rows].contiguous().to(dev)
+    # every rank's copy of W is full size and current only in the rows the rank owns
     w_full = torch.zeros(N, K, dtype=torch.float16, device=dev)
     w_full[r * rows:(r + 1) * rows] = shard
+    ends = [(i + 1) * rows for i in range(W)]
+    ends[-1] = N
     ready = torch.zeros((N + 255) // 256 + 1, dtype=torch.int32, device=dev)
     peers = PeerMemory(st.ctrl_dp, W, r)
-    table = _table(peers.share(shard))
+    table = _table(peers.share(w_full))
     torch.cuda.synchronize()
     dist.barrier()
-    out = kx.gemm_allgather(x, w_full, table, W, r, rows, ready)
+    out = kx.gemm_allgather(x, w_full, table, W, r, ends, ready)
     torch.cuda.synchronize()
     kx.check_status()
     ref = x.float() @ w_all.to(dev).float().t()
     err = float((out.float() - ref).abs().max())
     gathered_ok = bool(torch.equal(w_full.cpu(), w_all))
+    dist.barrier()    # nobody clears its copy below while a peer may still be reading it
 
     def timed(fn):
         for _ in range(3):
@@ -67,7 +71,7 @@ def main():
     def fused():
         w_full[:r * rows].zero_()
         w_full[(r + 1) * rows:].zero_()
-        kx.gemm_allgather(x, w_full, table, W, r, rows, ready, out=out)
+        kx.gemm_allgather(x, w_full, table, W, r, ends, ready, out=out)
 
     gathered = torch.empty(N, K, dtype=torch.float16, device=dev)
 

@@ -42,6 +42,10 @@ def build(name):
     if name == "vit_small":
         cfg = vit_config("vit_tiny", num_layers=4, image_size=32, patch_size=8)
         return _clf(ViT(cfg), (lambda n: torch.randn(n, 3, 32, 32)), 10)
+    if name == "vit_wide":      # matrices large enough for the row-sharded (deferred gather) path
+        cfg = vit_config("vit_tiny", num_layers=2, hidden_size=512, num_heads=8, mlp_dim=2048,
+                         image_size=32, patch_size=8)
+        return _clf(ViT(cfg), (lambda n: torch.randn(n, 3, 32, 32)), 10)
     if name == "llama_tiny":
         from pfeife_b200.models.llama import Llama, causal_lm_loss, llama_config
         model = Llama(llama_config("llama_tiny", tie_embeddings=True))

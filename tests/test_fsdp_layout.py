@@ -1,0 +1,74 @@
+"""Row-sharded weights between optimizer steps (--use_fsdp with the fused data-parallel step):
+ownership boundaries, packing order and the freshness bookkeeping, all on the CPU."""
+import torch
+
+from pfeife_b200.parallel.dp_fused import ALIGN, row_ends, shard_bounds
+from pfeife_b200.runtime.params import RankParams, StateEntry, gather_deferrable
+
+
+def test_bounds_fall_between_rows_of_the_matrix_they_cut():
+    # two matrices of 1000 x 520 and a tail of small parameters
+    mats = [(0, 520, 1000), (520000, 520, 1000)]
+    n = 2 * 520000 + 4096
+    for world in (2, 3, 4, 8):
+        b = shard_bounds(n, world, mats)
+        assert b[0] == 0 and b[-1] == n and all(x <= y for x, y in zip(b, b[1:]))
+        for off, cols, rows in mats:
+            for x in b[1:-1]:
+                if off < x < off + rows * cols:
+                    assert (x - off) % cols == 0
+            ends = row_ends(off, cols, rows, b)
+            assert ends[-1] == rows and all(x <= y for x, y in zip(ends, ends[1:]))
+            # every row's flat range lies inside its owner's range
+            start = 0
+            for r, e in enumerate(ends):
+                if e > start:
+                    assert b[r] <= off + start * cols and off + e * cols <= max(b[r + 1], off + e * cols)
+                    assert off + e * cols <= b[r + 1] or r == world - 1
+                start = e
+        # shards stay vector-aligned for the kernel
+        assert all(x % 4 == 0 for x in b)
+
+
+def test_even_split_without_matrices():
+    b = shard_bounds(10 * ALIGN + 5, 4)
+    assert b[0] == 0 and b[-1] == 10 * ALIGN + 5
+    assert all((x % ALIGN == 0) for x in b[:-1])
+
+
+def test_deferrable_matrices_are_packed_first_within_a_group():
+    big = torch.zeros(512, 512)
+    entries = [StateEntry(0, "bias", "param", torch.zeros(512), True, 0),
+               StateEntry(1, "w1", "param", big.clone(), True, 0),
+               StateEntry(2, "ln", "param", torch.zeros(512), True, 0),
+               StateEntry(3, "w2", "param", big.clone(), True, 1),
+               StateEntry(4, "small", "param", torch.zeros(8, 8), True, 1)]
+    assert gather_deferrable(big) and not gather_deferrable(torch.zeros(8, 8))
+    p = RankParams(entries, torch.device("cpu"), torch.bfloat16, "adamw", [{}, {}], native=True,
+                   defer_gather=True)
+    assert p.slots[1].deferred and p.slots[3].deferred and not p.slots[0].deferred
+    assert p.slots[1].offset == 0                        # the matrix leads its group
+    assert p.deferred_below[0] == 512 * 512
+    g1_lo = [lo for g, lo, hi in p.group_ranges if g == 1][0]
+    assert p.slots[3].offset == g1_lo and p.deferred_below[1] == g1_lo + 512 * 512
+    # without the flag the order is the placeholder order
+    q = RankParams(entries, torch.device("cpu"), torch.bfloat16, "adamw", [{}, {}], native=True)
+    assert q.slots[0].offset == 0 and not q.slots[1].deferred
+
+
+def test_freshness_follows_the_optimizer_epoch():
+    from pfeife_b200.ops import functional as Fn
+    w = torch.zeros(256, 1024)
+    lp = w.to(torch.bfloat16)
+    Fn.register_param(w, lp, None)
+    try:
+        slot = Fn._slot(w)
+        assert Fn._slot(lp) is slot and not Fn._stale(slot)
+        Fn.set_gather(w, Fn.GatherInfo(None, (128, 256), 2, 0, torch.zeros(2, dtype=torch.int32)))
+        assert Fn._stale(slot)
+        slot.fresh_epoch = Fn._weights_epoch
+        assert not Fn._stale(slot)
+        Fn.weights_updated()
+        assert Fn._stale(slot)
+    finally:
+        Fn.unregister_params()

@@ -99,25 +99,49 @@ def test_gemm_strided_views():
     _close(out[:, 128:], q.float() @ w.float().t(), 256, torch.bfloat16)
 
 
-@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2)])
-def test_gemm_allgather_one_device(world, rank):
-    """The all-gather GEMM with every "peer" shard on this GPU: one launch copies the other
-    ranks' rows into the full weight while it computes, and the product must match x @ W^T."""
+@pytest.mark.parametrize("world,rank,ends", [(2, 0, None), (2, 1, None), (4, 2, None),
+                                             (3, 1, (500, 1100, 1536)), (2, 1, (1536, 1536))])
+def test_gemm_allgather_one_device(world, rank, ends):
+    """The all-gather GEMM with every "peer" copy on this GPU: one launch copies the rows the
+    other ranks own into the local weight while it computes, and the product must match
+    x @ W^T.  Each copy is current only in the rows its rank owns (the rest is poisoned)."""
     from pfeife_b200.ops import kernels as kx
     from pfeife_b200.parallel.dp_fused import _table
     M, N, K = 700, 1536, 320
-    rows = N // world
+    ends = ends or tuple((r + 1) * (N // world) for r in range(world))
+    starts = (0,) + tuple(ends[:-1])
     torch.manual_seed(world * 10 + rank)
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
-    shards = [w[r * rows:(r + 1) * rows].clone() for r in range(world)]
-    w_full = torch.zeros_like(w)
-    w_full[rank * rows:(rank + 1) * rows] = shards[rank]
+    copies = []
+    for r in range(world):
+        c = torch.full_like(w, float("nan"))
+        c[starts[r]:ends[r]] = w[starts[r]:ends[r]]
+        copies.append(c)
+    w_full = copies[rank]
     ready = torch.zeros((N + 255) // 256 + 1, dtype=torch.int32, device="cuda")
-    out = kx.gemm_allgather(x, w_full, _table([s.data_ptr() for s in shards]), world, rank, rows,
+    out = kx.gemm_allgather(x, w_full, _table([c.data_ptr() for c in copies]), world, rank, ends,
                             ready)
     torch.cuda.synchronize()
     kx.check_status()
     assert torch.equal(w_full, w)
-    assert int(ready[-1]) == N - rows
+    assert int(ready[-1]) == N - (ends[rank] - starts[rank])
     _close(out, x.float() @ w.float().t(), K, torch.bfloat16)
+
+
+def test_gather_rows_one_device():
+    """Stand-alone row gather: rows owned by the other ranks arrive from their copies."""
+    from pfeife_b200.ops import kernels as kx
+    from pfeife_b200.parallel.dp_fused import _table
+    N, K, world, rank = 1000, 264, 4, 2
+    ends = (100, 400, 650, 1000)
+    starts = (0,) + ends[:-1]
+    w = torch.randn(N, K, device="cuda").to(torch.float16)
+    copies = []
+    for r in range(world):
+        c = torch.zeros_like(w)
+        c[starts[r]:ends[r]] = w[starts[r]:ends[r]]
+        copies.append(c)
+    kx.gather_rows(copies[rank], _table([c.data_ptr() for c in copies]), world, rank, ends)
+    torch.cuda.synchronize()
+    assert torch.equal(copies[rank], w)

@@ -51,6 +51,25 @@ def test_fused_dp_equals_nccl_dp(tmp_path):
         assert a == pytest.approx(b, rel=2e-2, abs=2e-2)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_row_sharded_weights_match_replicated_weights(tmp_path, graphs):
+    """--use_fsdp with the fused data-parallel step: after the optimizer step every weight matrix
+    is current only in the rows its rank owns and the first GEMM that reads it gathers the rest.
+    Training must land where the fully replicated run lands, eagerly and under CUDA graphs."""
+    common = ["--model", "vit_wide", "--device_cnt", "1", "--batch_size", "4", "--batch_cnt", "2",
+              "--steps", "5", "--optimizer", "adamw", "--lr", "0.001", "--mixed_precision", "bf16"]
+    if graphs:
+        common.append("--cuda_graphs")
+    sharded, out_s = launch(tmp_path, 2, common + ["--use_fsdp"], dp_mesh="-2,1", tag="sharded")
+    repl, _ = launch(tmp_path, 2, common, dp_mesh="-2,1", tag="repl")
+    with open(out_s + ".dp0") as f:
+        other = json.load(f)
+    assert sharded["param_checksum"] == pytest.approx(other["param_checksum"], rel=1e-7)
+    assert sharded["param_checksum"] == pytest.approx(repl["param_checksum"], rel=1e-6, abs=1e-4)
+    for a, b in zip(sharded["losses"], repl["losses"]):
+        assert a == pytest.approx(b, rel=1e-3, abs=1e-3)
+
+
 def test_allgather_fused_into_gemm(tmp_path):
     out = str(tmp_path / "ag.json")
     _port[0] += 1
