@@ -100,21 +100,28 @@ def baseline_number():
 
 
 def emit_result(args, impl, n_gpus, ms, ms_e2e, samples, clocks, launches, parallelism, h2d, d2h,
-                extra=None):
+                extra=None, workload=None):
     value = samples / ms * 1e3
     base = baseline_number()
+    if workload is not None:
+        config = {"model": workload.model_name, **workload.config,
+                  "micro_batch": workload.micro_batch, "batch_cnt": workload.batch_cnt}
+        dtype, data = workload.precision or "fp32", workload.data
+    else:
+        config = {"model": args.model_name, "layers": args.layers, "hidden": args.hidden,
+                  "heads": args.heads, "mlp": args.mlp, "patch": args.patch,
+                  "micro_batch": args.batch_size, "batch_cnt": args.batch_cnt,
+                  "seq_len": (224 // args.patch) ** 2 + 1, "optimizer": "AdamW"}
+        dtype, data = "fp16", "synthetic (N(0,1) images, uniform labels), random-init weights"
+    config.update({"global_batch": samples, "parallelism": parallelism,
+                   "l2": "per-step working set (weights + activations, several GB) exceeds L2"})
     rec = {
         "metric": "train samples/sec", "value": value, "unit": "samples/s", "impl": impl,
         "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (value / base) if base else None,
-        "dtype": "fp16", "data": "synthetic (N(0,1) images, uniform labels), random-init weights",
-        "config": {"model": args.model_name, "layers": args.layers, "hidden": args.hidden,
-                   "heads": args.heads, "mlp": args.mlp, "patch": args.patch,
-                   "micro_batch": args.batch_size, "batch_cnt": args.batch_cnt,
-                   "global_batch": samples, "seq_len": (224 // args.patch) ** 2 + 1,
-                   "optimizer": "AdamW", "parallelism": parallelism,
-                   "l2": "per-step working set (weights + activations, several GB) exceeds L2"},
+        "dtype": dtype, "data": data,
+        "config": config,
         "clocks": clocks,
         "e2e": {"value": samples / ms_e2e * 1e3, "unit": "samples/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -126,7 +133,15 @@ def emit_result(args, impl, n_gpus, ms, ms_e2e, samples, clocks, launches, paral
 
 
 # ------------------------------------------------------------------------------ native arm
-def _planned_mesh(args, cfg, world, rank, cpu):
+def _compute_dtype(torch, precision):
+    return {"fp16": torch.float16, "bf16": torch.bfloat16}.get(precision, torch.float32)
+
+
+def _to_compute(t, dtype):
+    return t.to(dtype) if t.is_floating_point() else t
+
+
+def _planned_mesh(args, wl, world, rank, cpu):
     """The PP x DP mesh for `world` GPUs, chosen by the planner: rank 0 profiles one micro-batch
     of the model on its GPU and evaluates every factorisation of the world size; the others read
     its answer from a key-value store (the process groups do not exist yet -- they depend on
@@ -142,24 +157,24 @@ def _planned_mesh(args, cfg, world, rank, cpu):
         mesh, table = f"-{world},1", None
         try:
             from pfeife_b200 import PipeOption
-            from pfeife_b200.models.vit import ViT
             from pfeife_b200.parallel.mesh_plan import plan_mesh
             dev = torch.device("cpu") if cpu else torch.device(
                 "cuda", int(os.environ.get("LOCAL_RANK", "0")))
             if not cpu:
                 torch.cuda.set_device(dev)
             torch.manual_seed(0)
-            model = ViT(cfg).to(dev)
-            opt = PipeOption(device_cnt=1, batch_size=args.batch_size, batch_cnt=args.batch_cnt,
-                             mixed_precision=None if cpu else "fp16", cpu_test=cpu,
+            model = wl.build_model().to(dev)
+            opt = PipeOption(device_cnt=1, batch_size=wl.micro_batch, batch_cnt=wl.batch_cnt,
+                             mixed_precision=None if cpu else wl.precision, cpu_test=cpu,
                              no_bench_optimizer=True, verbosity="warning")
-            x = torch.randn(args.batch_size, 3, 224, 224, device=dev,
-                            dtype=torch.float32 if cpu else torch.float16)
-            choice = plan_mesh(model, (x,), opt, world, dev)
+            cd = _compute_dtype(torch, None if cpu else wl.precision)
+            mb = wl.make_batch(wl.micro_batch, torch.Generator().manual_seed(0))
+            x = tuple(_to_compute(t, cd).to(dev) for t in mb[:wl.n_model_inputs])
+            choice = plan_mesh(model, x, opt, world, dev)
             mesh = choice.dp_mesh
             table = [{"pp": a, "dp": b, "step_ms": round(c, 2), "samples_per_s": round(d, 1),
                       "fits": bool(e)} for a, b, c, d, e in choice.table]
-            del model, choice, x
+            del model, choice, x, mb
             if not cpu:
                 torch.cuda.empty_cache()
         except Exception as exc:   # planning must never take the benchmark down
@@ -182,8 +197,7 @@ def run_native(args) -> int:
     import torch.nn.functional as F
 
     from pfeife_b200 import PartialRunner, PipeOption, initialize_pfeife, partial_compiler
-    from pfeife_b200 import ops
-    from pfeife_b200.models.vit import ViT, ViTConfig
+    from pfeife_b200.bench.workloads import get_workload
     from pfeife_b200.ops import _lib
     from pfeife_b200.runtime.partial import worker_loop
     from pfeife_b200.utils import get_logger, set_logger_level
@@ -193,55 +207,53 @@ def run_native(args) -> int:
     cpu = args.cpu or not torch.cuda.is_available()
     set_logger_level(20 if args.verbose else 30)
 
-    cfg = ViTConfig(image_size=224, patch_size=args.patch, hidden_size=args.hidden,
-                    num_layers=args.layers, num_heads=args.heads, mlp_dim=args.mlp,
-                    num_classes=1000)
+    wl = get_workload(args.workload, args)
     dp_mesh = args.dp_mesh
     planned = None
+    if dp_mesh is None and world == 8 and wl.mesh_for_8:
+        dp_mesh = wl.mesh_for_8             # the layout the configuration names
     if dp_mesh in (None, "auto") and world > 1:
-        dp_mesh, planned = _planned_mesh(args, cfg, world, rank, cpu)
+        dp_mesh, planned = _planned_mesh(args, wl, world, rank, cpu)
     state = initialize_pfeife(dp_mesh=dp_mesh, cpu=cpu)
     dev = state.device
-    mp = None if cpu else "fp16"
-    option = PipeOption(device_cnt=state.pp_size, batch_size=args.batch_size,
-                        batch_cnt=args.batch_cnt, mixed_precision=mp, cpu_test=cpu,
+    mp = None if cpu else wl.precision
+    extra_opt = dict(wl.option)
+    if state.pp_size == 1:
+        extra_opt.pop("loop_cnt", None)
+    if args.use_fsdp:
+        extra_opt["use_fsdp"] = True
+    option = PipeOption(device_cnt=state.pp_size, batch_size=wl.micro_batch,
+                        batch_cnt=wl.batch_cnt, mixed_precision=mp, cpu_test=cpu,
                         no_bench_optimizer=True, optimizer={"type": "adamw", "lr": 1e-4},
-                        fused_dp=not args.nccl_dp, cuda_graphs=not args.no_graphs, verbosity="info" if args.verbose else "warning")
+                        fused_dp=not args.nccl_dp, cuda_graphs=not args.no_graphs,
+                        verbosity="info" if args.verbose else "warning", **extra_opt)
     if not state.is_main_rank:
         worker_loop()
         return 0
 
     torch.manual_seed(0)
-    model = ViT(cfg).to(dev)
+    model = wl.build_model().to(dev)
     optimizer = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01)
     runner = PartialRunner(option, optimizer)
     cmodel = torch.compile(model, backend=partial_compiler)
 
-    def exec_fn(pixel_values, labels):
-        logits = cmodel(pixel_values)
-        loss = ops.cross_entropy(logits, labels)
+    def exec_fn(*batch):
+        loss = wl.loss(cmodel, *batch)
         runner.scaler.scale(loss).backward()
         return loss.detach()
 
     runner.set_exec_fn(exec_fn)
-    n = args.batch_size * args.batch_cnt
+    n = wl.micro_batch * wl.batch_cnt
     g = torch.Generator(device="cpu").manual_seed(1 + state.dp_rank)
-    host_x = torch.randn(n, 3, 224, 224, generator=g)
-    host_y = torch.randint(0, 1000, (n,), generator=g)
+    cd = _compute_dtype(torch, mp)
+    host = [_to_compute(t, cd) for t in wl.make_batch(n, g)]
     if not cpu:
-        host_x, host_y = host_x.pin_memory(), host_y.pin_memory()
-        host_x16 = host_x.to(torch.float16).pin_memory()
-    else:
-        host_x16 = host_x
-    x_dev, y_dev = host_x16.to(dev), host_y.to(dev)
+        host = [t.pin_memory() for t in host]
+    resident = [t.to(dev) for t in host]
 
     def one_step(e2e: bool):
-        if e2e:
-            x = host_x16.to(dev, non_blocking=True)
-            y = host_y.to(dev, non_blocking=True)
-        else:
-            x, y = x_dev, y_dev
-        losses = runner.step(x, y)
+        batch = [t.to(dev, non_blocking=True) for t in host] if e2e else resident
+        losses = runner.step(*batch)
         if e2e:
             return float(torch.stack([l.float() for l in losses]).sum().cpu())
         return losses
@@ -297,10 +309,11 @@ def run_native(args) -> int:
         emit_result(args, impl="pfeife_b200", n_gpus=world, ms=ms, ms_e2e=ms_e2e, samples=samples,
                     clocks=clocks, launches=launches,
                     parallelism=f"pp{state.pp_size}xdp{state.dp_size}",
-                    h2d=host_x16.numel() * host_x16.element_size() + host_y.numel() * 8, d2h=4,
+                    h2d=sum(t.numel() * t.element_size() for t in host), d2h=4, workload=wl,
                     extra={"dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
                            if state.dp_size > 1 else None,
                            "planner_mesh_table": planned,
+                           "use_fsdp": bool(option.use_fsdp),
                            "optimizer_and_dp_exposed_ms": runner.worker.last_optimizer_ms(),
                            "pipeline_bubble_pct": 100.0 * bubble})
     runner.close()
@@ -320,19 +333,32 @@ def main(argv=None) -> int:
     ap.add_argument("--nccl_dp", action="store_true", help="NCCL all-reduce DP baseline")
     ap.add_argument("--no_graphs", action="store_true",
                     help="run stages eagerly instead of replaying captured CUDA graphs")
+    ap.add_argument("--use_fsdp", action="store_true",
+                    help="keep weight matrices row-sharded between optimizer steps; the first "
+                         "GEMM that reads one gathers the other ranks' rows (needs DP > 1)")
     ap.add_argument("--cpu", action="store_true", help="plumbing check without a GPU")
     ap.add_argument("--verbose", action="store_true")
-    # model shape (defaults: ViT-g/14 of the headline configuration)
-    ap.add_argument("--model_name", default="ViT-g/14")
-    ap.add_argument("--layers", type=int, default=40)
-    ap.add_argument("--hidden", type=int, default=1408)
-    ap.add_argument("--heads", type=int, default=16)
-    ap.add_argument("--mlp", type=int, default=6144)
-    ap.add_argument("--patch", type=int, default=14)
-    ap.add_argument("--batch_size", type=int, default=24)
-    ap.add_argument("--batch_cnt", type=int, default=8)
+    ap.add_argument("--workload", default="vitg",
+                    help="vitg (headline, default) | vitl | llama7b | llama7b_fsdp | sdxl | "
+                         "vit_tiny | llama_tiny | unet_tiny; on 8 GPUs a workload runs on the "
+                         "mesh its configuration names unless --dp_mesh is given")
+    # shape of the vitg workload (defaults: ViT-g/14 of the headline configuration)
+    ap.add_argument("--model_name", default=None)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--hidden", type=int, default=None)
+    ap.add_argument("--heads", type=int, default=None)
+    ap.add_argument("--mlp", type=int, default=None)
+    ap.add_argument("--patch", type=int, default=None)
+    ap.add_argument("--batch_size", type=int, default=None)
+    ap.add_argument("--batch_cnt", type=int, default=None)
     args = ap.parse_args(argv)
     if args.impl == "reference":
+        # the reference arm runs the headline configuration (or the shape given on the command
+        # line) of the ViT workload
+        for k, v in (("model_name", "ViT-g/14"), ("layers", 40), ("hidden", 1408), ("heads", 16),
+                     ("mlp", 6144), ("patch", 14), ("batch_size", 24), ("batch_cnt", 8)):
+            if getattr(args, k) is None:
+                setattr(args, k, v)
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_arm
         try:
