@@ -96,7 +96,8 @@ PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const vo
 PF_DECL int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                              void* const* lp, void* const* flags, void* m, void* v,
                              void* local_sync, long long shard_lo, long long shard_hi,
-                             long long lp_local_below, float lr, float beta1, float beta2,
+                             long long local_below, long long zero_lo, long long zero_hi,
+                             float lr, float beta1, float beta2,
                              float eps, float weight_decay, int step, float grad_scale, int adamw,
                              int lp_dtype, int check_inf, const void* loss_scale, void* found_inf,
                              int epoch, int calls_before, int* status, int sm_count, void* stream);

@@ -77,99 +77,151 @@ col2im_kernel(const T* __restrict__ dcols, T* __restrict__ dx, int B, int H, int
 }
 
 // ------------------------------------------------------------------------------ GroupNorm
-// stats[b, g] = (mean, rstd) over HW x (C/G) elements.  One CTA per (b, g).
+// NHWC, C a multiple of 8.  All four passes read 16 bytes (8 channels) per thread and request.
+//
+// The statistics passes give every thread one fixed 8-channel vector and a stripe of pixels:
+// the CTA is (C/8) columns x R rows of threads, a grid of (slabs, B) CTAs splits the pixels of
+// each image, per-channel partial sums meet in shared memory, and one thread per group folds
+// its channels and adds the result to the global sums (zeroed by the host function).
+
+// threads per CTA for the statistics passes: a whole number of rows of C/8 threads
+static inline int gn_rows(int C) { const int ncv = C / 8; return ncv >= 256 ? 1 : 256 / ncv; }
+
 template <typename T>
-__global__ void __launch_bounds__(256)
-gn_stats_kernel(const T* __restrict__ x, float* __restrict__ mean, float* __restrict__ rstd,
-                int HW, int C, int G, float eps) {
-  __shared__ float red[2][8];
-  const int b = blockIdx.x / G, g = blockIdx.x % G;
-  const int cpg = C / G;
-  const T* base = x + (long long)b * HW * C + g * cpg;
-  const long long n = (long long)HW * cpg;
-  float s = 0.f, ss = 0.f;
-  for (long long i = threadIdx.x; i < n; i += 256) {
-    const long long p = i / cpg;
-    const int c = (int)(i - p * cpg);
-    const float v = to_f32<T>(base[p * C + c]);
-    s += v; ss += v * v;
-  }
-  s = warp_sum(s); ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = s; red[1][threadIdx.x >> 5] = ss; }
+__global__ void gn_stats_kernel(const T* __restrict__ x, float* __restrict__ sum,
+                                float* __restrict__ sumsq, int HW, int C, int G, int rows) {
+  extern __shared__ float chan[];       // [2][C]
+  const int ncv = C / 8, cpg = C / G;
+  const int cv = threadIdx.x % ncv, r = threadIdx.x / ncv;
+  const int b = blockIdx.y;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) chan[i] = 0.f;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float a = 0.f, q = 0.f;
-    for (int i = 0; i < 8; ++i) { a += red[0][i]; q += red[1][i]; }
-    const float m = a / n;
-    const float var = fmaxf(q / n - m * m, 0.f);
-    mean[blockIdx.x] = m;
-    rstd[blockIdx.x] = rsqrtf(var + eps);
+  const int per = (HW + gridDim.x - 1) / gridDim.x;
+  const int p0 = blockIdx.x * per, p1 = min(HW, p0 + per);
+  float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const T* base = x + (long long)b * HW * C + cv * 8;
+  for (int p = p0 + r; p < p1; p += rows) {
+    const uint4 u = *reinterpret_cast<const uint4*>(base + (long long)p * C);
+    const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float v = to_f32<T>(e[j]); s[j] += v; q[j] = fmaf(v, v, q[j]); }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    atomicAdd(&chan[cv * 8 + j], s[j]);
+    atomicAdd(&chan[C + cv * 8 + j], q[j]);
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    float a = 0.f, c = 0.f;
+    for (int i = 0; i < cpg; ++i) { a += chan[g * cpg + i]; c += chan[C + g * cpg + i]; }
+    atomicAdd(&sum[b * G + g], a);
+    atomicAdd(&sumsq[b * G + g], c);
   }
 }
 
-// y = act((x - mean) * rstd * gamma + beta), act = SiLU or identity; elementwise over NHWC
+// (sum, sumsq) -> (mean, rstd), in place
+__global__ void gn_finalize_kernel(float* __restrict__ mean, float* __restrict__ rstd, int n_groups,
+                                   float inv_n, float eps) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_groups) return;
+  const float m = mean[i] * inv_n;
+  const float var = fmaxf(rstd[i] * inv_n - m * m, 0.f);
+  mean[i] = m;
+  rstd[i] = rsqrtf(var + eps);
+}
+
+// group of channel c0 + j for the 8 channels of one vector
+__device__ __forceinline__ int gn_group(int c0, int j, int cpg) { return (c0 + j) / cpg; }
+
+// y = act((x - mean) * rstd * gamma + beta), act = SiLU or identity
 template <typename T>
 __global__ void __launch_bounds__(256)
 gn_apply_kernel(const T* __restrict__ x, const float* __restrict__ mean,
                 const float* __restrict__ rstd, const float* __restrict__ gamma,
-                const float* __restrict__ beta, T* __restrict__ y, long long total, int HW, int C,
-                int G, int act_silu) {
-  const int cpg = C / G;
+                const float* __restrict__ beta, T* __restrict__ y, long long total_vec, int HW,
+                int C, int G, int act_silu) {
+  const int ncv = C / 8, cpg = C / G;
   const long long gstride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
-    const int c = (int)(i % C);
-    const long long b = i / ((long long)HW * C);
-    const int sg = (int)(b * G + c / cpg);
-    float v = (to_f32<T>(x[i]) - mean[sg]) * rstd[sg] * gamma[c] + beta[c];
-    if (act_silu) v = silu(v);
-    y[i] = from_f32<T>(v);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec;
+       i += gstride) {
+    const int cv = (int)(i % ncv);
+    const int b = (int)(i / ((long long)HW * ncv));
+    const int c0 = cv * 8;
+    const uint4 u = reinterpret_cast<const uint4*>(x)[i];
+    const T* e = reinterpret_cast<const T*>(&u);
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sg = b * G + gn_group(c0, j, cpg);
+      float v = (to_f32<T>(e[j]) - mean[sg]) * rstd[sg] * gamma[c0 + j] + beta[c0 + j];
+      if (act_silu) v = silu(v);
+      oe[j] = from_f32<T>(v);
+    }
+    reinterpret_cast<uint4*>(y)[i] = o;
   }
 }
 
-// Backward pass 1: per (b, g) sums  A = sum(dz * gamma), Bq = sum(dz * gamma * xhat), and the
-// parameter gradients dgamma[c] += sum dz * xhat, dbeta[c] += sum dz  (dz = dy * act'(z)).
+// Backward pass 1: per-channel sums of dz and dz * xhat (dz = dy * act'(z)); they are the
+// parameter gradients (dbeta, dgamma) and, weighted by gamma and folded per group, the two sums
+// A = sum(dz * gamma), Bq = sum(dz * gamma * xhat) the second pass needs.
 template <typename T>
-__global__ void __launch_bounds__(256)
-gn_bwd_stats_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                    const float* __restrict__ mean, const float* __restrict__ rstd,
-                    const float* __restrict__ gamma, const float* __restrict__ beta,
-                    float* __restrict__ sumA, float* __restrict__ sumB,
-                    float* __restrict__ dgamma, float* __restrict__ dbeta, int HW, int C, int G,
-                    int act_silu) {
-  __shared__ float red[2][8];
-  extern __shared__ float chan[];   // [2][cpg]
-  const int b = blockIdx.x / G, g = blockIdx.x % G;
-  const int cpg = C / G;
-  for (int i = threadIdx.x; i < 2 * cpg; i += 256) chan[i] = 0.f;
+__global__ void gn_bwd_stats_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                    float* __restrict__ sumA, float* __restrict__ sumB,
+                                    float* __restrict__ dgamma, float* __restrict__ dbeta, int HW,
+                                    int C, int G, int act_silu, int rows) {
+  extern __shared__ float chan[];       // [2][C]: sum dz * xhat, sum dz
+  const int ncv = C / 8, cpg = C / G;
+  const int cv = threadIdx.x % ncv, r = threadIdx.x / ncv;
+  const int b = blockIdx.y, c0 = cv * 8;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) chan[i] = 0.f;
   __syncthreads();
-  const long long off = (long long)b * HW * C + g * cpg;
-  const float m = mean[blockIdx.x], rs = rstd[blockIdx.x];
-  const long long n = (long long)HW * cpg;
-  float a = 0.f, q = 0.f;
-  for (long long i = threadIdx.x; i < n; i += 256) {
-    const long long p = i / cpg;
-    const int c = (int)(i - p * cpg);
-    const int ch = g * cpg + c;
-    const float xhat = (to_f32<T>(x[off + p * C + c]) - m) * rs;
-    float dz = to_f32<T>(dy[off + p * C + c]);
-    if (act_silu) dz *= dsilu(xhat * gamma[ch] + beta[ch]);
-    a += dz * gamma[ch];
-    q += dz * gamma[ch] * xhat;
-    atomicAdd(&chan[c], dz * xhat);
-    atomicAdd(&chan[cpg + c], dz);
+  float m[8], rs[8], ga[8], be[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int sg = b * G + gn_group(c0, j, cpg);
+    m[j] = mean[sg]; rs[j] = rstd[sg]; ga[j] = gamma[c0 + j]; be[j] = beta[c0 + j];
   }
-  a = warp_sum(a); q = warp_sum(q);
-  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = a; red[1][threadIdx.x >> 5] = q; }
+  const int per = (HW + gridDim.x - 1) / gridDim.x;
+  const int p0 = blockIdx.x * per, p1 = min(HW, p0 + per);
+  float sx[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sd[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long off = (long long)b * HW * C + c0;
+  for (int p = p0 + r; p < p1; p += rows) {
+    const uint4 ux = *reinterpret_cast<const uint4*>(x + off + (long long)p * C);
+    const uint4 ud = *reinterpret_cast<const uint4*>(dy + off + (long long)p * C);
+    const T* ex = reinterpret_cast<const T*>(&ux);
+    const T* ed = reinterpret_cast<const T*>(&ud);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float xhat = (to_f32<T>(ex[j]) - m[j]) * rs[j];
+      float dz = to_f32<T>(ed[j]);
+      if (act_silu) dz *= dsilu(fmaf(xhat, ga[j], be[j]));
+      sd[j] += dz;
+      sx[j] = fmaf(dz, xhat, sx[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    atomicAdd(&chan[c0 + j], sx[j]);
+    atomicAdd(&chan[C + c0 + j], sd[j]);
+  }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float s0 = 0.f, s1 = 0.f;
-    for (int i = 0; i < 8; ++i) { s0 += red[0][i]; s1 += red[1][i]; }
-    sumA[blockIdx.x] = s0;
-    sumB[blockIdx.x] = s1;
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    float a = 0.f, q = 0.f;
+    for (int i = 0; i < cpg; ++i) {
+      const int c = g * cpg + i;
+      a = fmaf(gamma[c], chan[C + c], a);
+      q = fmaf(gamma[c], chan[c], q);
+    }
+    atomicAdd(&sumA[b * G + g], a);
+    atomicAdd(&sumB[b * G + g], q);
   }
-  for (int i = threadIdx.x; i < cpg; i += 256) {
-    atomicAdd(&dgamma[g * cpg + i], chan[i]);
-    atomicAdd(&dbeta[g * cpg + i], chan[cpg + i]);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    atomicAdd(&dgamma[c], chan[c]);
+    atomicAdd(&dbeta[c], chan[C + c]);
   }
 }
 
@@ -180,19 +232,32 @@ gn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                     const float* __restrict__ mean, const float* __restrict__ rstd,
                     const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ sumA, const float* __restrict__ sumB,
-                    T* __restrict__ dx, long long total, int HW, int C, int G, int act_silu) {
-  const int cpg = C / G;
+                    T* __restrict__ dx, long long total_vec, int HW, int C, int G, int act_silu) {
+  const int ncv = C / 8, cpg = C / G;
   const float inv_n = 1.f / ((float)HW * cpg);
   const long long gstride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
-    const int c = (int)(i % C);
-    const long long b = i / ((long long)HW * C);
-    const int sg = (int)(b * G + c / cpg);
-    const float rs = rstd[sg];
-    const float xhat = (to_f32<T>(x[i]) - mean[sg]) * rs;
-    float dz = to_f32<T>(dy[i]);
-    if (act_silu) dz *= dsilu(xhat * gamma[c] + beta[c]);
-    dx[i] = from_f32<T>(rs * (dz * gamma[c] - sumA[sg] * inv_n - xhat * sumB[sg] * inv_n));
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec;
+       i += gstride) {
+    const int cv = (int)(i % ncv);
+    const int b = (int)(i / ((long long)HW * ncv));
+    const int c0 = cv * 8;
+    const uint4 ux = reinterpret_cast<const uint4*>(x)[i];
+    const uint4 ud = reinterpret_cast<const uint4*>(dy)[i];
+    const T* ex = reinterpret_cast<const T*>(&ux);
+    const T* ed = reinterpret_cast<const T*>(&ud);
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sg = b * G + gn_group(c0, j, cpg);
+      const float rs = rstd[sg];
+      const float xhat = (to_f32<T>(ex[j]) - mean[sg]) * rs;
+      float dz = to_f32<T>(ed[j]);
+      const float g = gamma[c0 + j];
+      if (act_silu) dz *= dsilu(fmaf(xhat, g, beta[c0 + j]));
+      oe[j] = from_f32<T>(rs * (dz * g - sumA[sg] * inv_n - xhat * sumB[sg] * inv_n));
+    }
+    reinterpret_cast<uint4*>(dx)[i] = o;
   }
 }
 
@@ -281,39 +346,56 @@ PF_API int pf_col2im(const void* dcols, void* dx, int B, int H, int W, int C, in
 PF_API int pf_groupnorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
                             void* mean, void* rstd, int B, int HW, int C, int G, float eps,
                             int act_silu, int dtype, int sm_count, void* stream) {
-  if (C % G) return -2;
+  if (C % G || C % 8) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long total = (long long)B * HW * C;
+  const long long total_vec = (long long)B * HW * (C / 8);
+  const int rows = gn_rows(C);
+  const int threads = rows * (C / 8);
+  if (threads > 1024) return -2;
+  int slabs = (4 * (sm_count > 0 ? sm_count : 148) + B - 1) / B;
+  if (slabs > (HW + rows - 1) / rows) slabs = (HW + rows - 1) / rows;
+  if (slabs < 1) slabs = 1;
+  // mean / rstd first hold the sums, then are converted in place
+  cudaMemsetAsync(mean, 0, sizeof(float) * B * G, st);
+  cudaMemsetAsync(rstd, 0, sizeof(float) * B * G, st);
   PF_DISPATCH_H(dtype, {
-    gn_stats_kernel<T><<<B * G, 256, 0, st>>>((const T*)x, (float*)mean, (float*)rstd, HW, C, G,
-                                              eps);
-    gn_apply_kernel<T><<<grid_for(total, sm_count), 256, 0, st>>>(
+    gn_stats_kernel<T><<<dim3(slabs, B), threads, 2 * C * sizeof(float), st>>>(
+        (const T*)x, (float*)mean, (float*)rstd, HW, C, G, rows);
+    gn_finalize_kernel<<<(B * G + 255) / 256, 256, 0, st>>>(
+        (float*)mean, (float*)rstd, B * G, 1.f / ((float)HW * (C / G)), eps);
+    gn_apply_kernel<T><<<grid_for(total_vec, sm_count), 256, 0, st>>>(
         (const T*)x, (const float*)mean, (const float*)rstd, (const float*)gamma,
-        (const float*)beta, (T*)y, total, HW, C, G, act_silu);
+        (const float*)beta, (T*)y, total_vec, HW, C, G, act_silu);
   });
   PF_CHECK_LAUNCH();
   return 0;
 }
 
-// sums: fp32 scratch [2][B*G]; dgamma / dbeta fp32 [C], accumulated into (zero them first for a
-// fresh gradient)
+// sums: fp32 scratch [2][B*G] (zeroed here); dgamma / dbeta fp32 [C], accumulated into (zero
+// them first for a fresh gradient)
 PF_API int pf_groupnorm_bwd(const void* dy, const void* x, const void* mean, const void* rstd,
                             const void* gamma, const void* beta, void* dx, void* dgamma,
                             void* dbeta, void* sums, int B, int HW, int C, int G, int act_silu,
                             int dtype, int sm_count, void* stream) {
-  if (C % G) return -2;
+  if (C % G || C % 8) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long total = (long long)B * HW * C;
+  const long long total_vec = (long long)B * HW * (C / 8);
   float* sA = (float*)sums;
   float* sB = sA + (long long)B * G;
-  const int cpg = C / G;
+  const int rows = gn_rows(C);
+  const int threads = rows * (C / 8);
+  if (threads > 1024) return -2;
+  int slabs = (4 * (sm_count > 0 ? sm_count : 148) + B - 1) / B;
+  if (slabs > (HW + rows - 1) / rows) slabs = (HW + rows - 1) / rows;
+  if (slabs < 1) slabs = 1;
+  cudaMemsetAsync(sums, 0, sizeof(float) * 2 * B * G, st);
   PF_DISPATCH_H(dtype, {
-    gn_bwd_stats_kernel<T><<<B * G, 256, 2 * cpg * sizeof(float), st>>>(
+    gn_bwd_stats_kernel<T><<<dim3(slabs, B), threads, 2 * C * sizeof(float), st>>>(
         (const T*)dy, (const T*)x, (const float*)mean, (const float*)rstd, (const float*)gamma,
-        (const float*)beta, sA, sB, (float*)dgamma, (float*)dbeta, HW, C, G, act_silu);
-    gn_bwd_apply_kernel<T><<<grid_for(total, sm_count), 256, 0, st>>>(
+        (const float*)beta, sA, sB, (float*)dgamma, (float*)dbeta, HW, C, G, act_silu, rows);
+    gn_bwd_apply_kernel<T><<<grid_for(total_vec, sm_count), 256, 0, st>>>(
         (const T*)dy, (const T*)x, (const float*)mean, (const float*)rstd, (const float*)gamma,
-        (const float*)beta, sA, sB, (T*)dx, total, HW, C, G, act_silu);
+        (const float*)beta, sA, sB, (T*)dx, total_vec, HW, C, G, act_silu);
   });
   PF_CHECK_LAUNCH();
   return 0;

@@ -40,8 +40,10 @@ struct DpArgs {
   float* v;
   int* local_sync;             // local: [0] arrival counter, [1] release word
   long long shard_lo, shard_hi;
-  long long lp_local_below;    // 16-bit weights at flat indices below this are written locally
-                               // only: their consumers gather them (fused all-gather GEMM)
+  long long local_below;       // 16-bit weights at flat indices below this are written locally
+                               // only: their first consumer gathers the rows other ranks own
+                               // (fused all-gather GEMM); fp32 masters always go to every rank
+  long long zero_lo, zero_hi;  // range of the local gradient bucket this call clears
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
   int adamw, lp_dtype, check_inf;
   const float* loss_scale;     // local device scalar (identical on every rank) or null
@@ -130,8 +132,6 @@ dp_fused_kernel(const DpArgs a) {
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
         s[u].x += g[u].x; s[u].y += g[u].y; s[u].z += g[u].z; s[u].w += g[u].w;
-        if (p != a.rank && i < nvec)
-          *reinterpret_cast<float4*>(a.grad[p] + lo + i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
 #pragma unroll
@@ -150,6 +150,17 @@ dp_fused_kernel(const DpArgs a) {
   }
 
   job_barrier(a, 1);                            // everybody's non-finite flag is published
+
+  // ---- every rank has read what it needed of this bucket: clear the part of it that other
+  //      ranks own (local stores; the own shard is cleared by the update loop below)
+  {
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long n_before = (lo - a.zero_lo) / 4, n_after = (a.zero_hi - hi) / 4;
+    for (long long i = tid; i < n_before; i += stride)
+      *reinterpret_cast<float4*>(a.grad[a.rank] + a.zero_lo + i * 4) = z4;
+    for (long long i = tid; i < n_after; i += stride)
+      *reinterpret_cast<float4*>(a.grad[a.rank] + hi + i * 4) = z4;
+  }
 
   bool skip = false;
   if (a.check_inf) {
@@ -195,7 +206,7 @@ dp_fused_kernel(const DpArgs a) {
         q = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&y));
       }
     }
-    const bool push_lp = e >= a.lp_local_below;
+    const bool push_lp = e >= a.local_below;
     for (int p = 0; p < a.world; ++p) {
       *reinterpret_cast<float4*>(a.master[p] + e) = nw;
       if (a.lp[p] && (push_lp || p == a.rank))
@@ -211,12 +222,15 @@ dp_fused_kernel(const DpArgs a) {
 using namespace pf;
 
 // Pointer tables are arrays of `world` device pointers (entry `rank` is the local buffer).
+// [shard_lo, shard_hi) is the part of this call's range [zero_lo, zero_hi) that this rank owns:
+// it reduces and updates its shard and clears the whole range of its own gradient bucket.
 // `epoch` must grow by at least 3 per call and be identical on every rank; `sync_base` is
 // (number of earlier calls) * 3 * grid.  Returns the grid size used through *grid_out.
 PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                             void* const* lp, void* const* flags, void* m, void* v,
                             void* local_sync, long long shard_lo, long long shard_hi,
-                            long long lp_local_below, float lr,
+                            long long local_below, long long zero_lo, long long zero_hi,
+                            float lr,
                             float beta1, float beta2, float eps, float weight_decay, int step,
                             float grad_scale, int adamw, int lp_dtype, int check_inf,
                             const void* loss_scale, void* found_inf, int epoch, int calls_before,
@@ -233,7 +247,9 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   }
   a.m = (float*)m; a.v = (float*)v; a.local_sync = (int*)local_sync;
   a.shard_lo = shard_lo; a.shard_hi = shard_hi;
-  a.lp_local_below = lp_local_below;
+  if (zero_lo > shard_lo || zero_hi < shard_hi || (zero_lo % 4) || (zero_hi % 4)) return -2;
+  a.local_below = local_below;
+  a.zero_lo = zero_lo; a.zero_hi = zero_hi;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
   a.bc1 = 1.f - powf(beta1, (float)step);
   a.bc2 = 1.f - powf(beta2, (float)step);

@@ -17,6 +17,7 @@ gradient for the weight), which is what the fused data-parallel reduce consumes.
 from __future__ import annotations
 
 import math
+import threading
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -39,7 +40,7 @@ class ParamSlot:
     # Deferred all-gather (sharded data parallelism): after an optimizer step only the rows this
     # rank owns are current in `lp`; the first consumer pulls the other rows from their owners.
     gather: Optional["GatherInfo"] = None
-    fresh_epoch: int = 0                 # optimizer step whose weights `lp` holds in full
+    gathered_in: int = 0                 # gather session that last completed `lp`
 
 
 @dataclass
@@ -66,32 +67,38 @@ def unregister_params() -> None:
     _PARAMS.clear()
 
 
-_weights_epoch = 0   # bumped by the data-parallel layer after every optimizer step
+# Gather sessions.  The runtime knows when a stage runs its first forward after an optimizer step
+# (the only time its row-sharded weights are incomplete) and brackets that forward with
+# ``gather_session(True)`` ... ``gather_session(False)``: inside, the first consumer of each
+# sharded weight gathers it; outside, weights are taken as complete.  Keeping this decision out
+# of per-weight state makes a captured CUDA graph of that forward replay the same gathers.
+_session_tls = threading.local()
+_session_counter = [0]
 
 
-def weights_updated() -> None:
-    """The optimizer step of the data-parallel layer has run: 16-bit weights with a deferred
-    all-gather now hold current values only in the rows their rank owns."""
-    global _weights_epoch
-    _weights_epoch += 1
+def gather_session(active: bool) -> None:
+    if active:
+        _session_counter[0] += 1
+        _session_tls.id = _session_counter[0]
+    else:
+        _session_tls.id = 0
 
 
 def set_gather(master: Tensor, info: GatherInfo) -> None:
     """Marks the registered parameter `master` as row-sharded between optimizer steps."""
-    slot = _PARAMS[master.data_ptr()]
-    slot.gather = info
-    slot.fresh_epoch = -1
+    _PARAMS[master.data_ptr()].gather = info
 
 
 def _stale(slot: Optional[ParamSlot]) -> bool:
-    return slot is not None and slot.gather is not None and slot.fresh_epoch != _weights_epoch
+    sid = getattr(_session_tls, "id", 0)
+    return slot is not None and slot.gather is not None and sid != 0 and slot.gathered_in != sid
 
 
 def _gather_now(slot: ParamSlot) -> None:
     """Stand-alone gather of the other ranks' rows (first consumer is not the fused GEMM)."""
     g = slot.gather
     kx.gather_rows(slot.lp.view(slot.lp.shape[0], -1), g.copies, g.world, g.rank, g.row_end)
-    slot.fresh_epoch = _weights_epoch
+    slot.gathered_in = _session_tls.id
 
 
 def _slot(t: Tensor) -> Optional[ParamSlot]:
@@ -205,7 +212,7 @@ def linear_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], residual: Optional[
             g = slot.gather
             kx.gemm_allgather(x2, w2, g.copies, g.world, g.rank, g.row_end, g.ready, out=y,
                               bias=bias, residual=r2, aux=aux, epilogue=epi)
-            slot.fresh_epoch = _weights_epoch
+            slot.gathered_in = _session_tls.id
         else:
             kx.gemm(x2, w2, out=y, bias=bias, residual=r2, aux=aux, epilogue=epi)
         return y.view(out_shape), (aux.view(out_shape) if act else x.new_empty(0))
@@ -1072,7 +1079,7 @@ def conv2d(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, stride: int
 def group_norm_fwd(x: Tensor, gamma: Tensor, beta: Tensor, groups: int, eps: float,
                    silu_act: bool) -> Tuple[Tensor, Tensor, Tensor]:
     """NHWC GroupNorm with optional fused SiLU -> (y, mean[B*G], rstd[B*G])."""
-    if _native(x):
+    if _native(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
         return kx.groupnorm_fwd(x, gamma, beta, groups, eps, silu_act)
     B, H, W, C = x.shape
     xf = x.float().reshape(B, H * W, groups, C // groups)
@@ -1095,7 +1102,7 @@ def _(x, gamma, beta, groups, eps, silu_act):
 @torch.library.custom_op("pfeife::group_norm_bwd", mutates_args=())
 def group_norm_bwd(dy: Tensor, x: Tensor, mean: Tensor, rstd: Tensor, gamma: Tensor, beta: Tensor,
                    groups: int, silu_act: bool) -> Tuple[Tensor, Tensor, Tensor]:
-    if _native(x):
+    if _native(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
         return kx.groupnorm_bwd(dy, x, mean, rstd, gamma, beta, groups, silu_act)
     B, H, W, C = x.shape
     cpg = C // groups

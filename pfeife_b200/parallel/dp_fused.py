@@ -182,7 +182,8 @@ class FusedDP(NcclDP):
         self.t_master = _table(self.peers.share(params.master))
         self.t_lp = _table(self.peers.share(params.lp)) if params.lp is not None else None
         self.t_flags = _table(self.peers.share(self.flags))
-        self.deferred_below = dict(getattr(params, "deferred_below", {})) if deferred else {}
+        self.deferred_below = dict(getattr(params, "deferred_below", {})) \
+            if (deferred and self.t_lp is not None) else {}
         if deferred and self.t_lp is not None:
             from ..ops import functional as Fn
             es = params.lp.element_size()
@@ -203,16 +204,16 @@ class FusedDP(NcclDP):
             h = params.hyper[min(g, len(params.hyper) - 1)]
             a, b = max(lo, lo_s), min(hi, hi_s)
             if b < a:
-                a = b = lo_s
+                a = b = lo       # nothing of this group is owned here: only clear its gradients
             b1, b2 = h.get("betas", (0.9, 0.999))
             adamw = params.optimizer_type == "adamw"
-            off = a - lo_s
+            off = max(a - lo_s, 0)
             m = self.m[off:] if off < self.m.numel() else self.m
             v = self.v[off:] if off < self.v.numel() else self.v
             code = L.pf_dp_fused_step(
                 self.rank, self.size, self.t_grad, self.t_master, self.t_lp, self.t_flags,
                 ptr(m), ptr(v), ptr(self.local_sync), c_ll(a), c_ll(b),
-                c_ll(self.deferred_below.get(g, 0)), c_f(h.get("lr", 1e-3)),
+                c_ll(self.deferred_below.get(g, 0)), c_ll(lo), c_ll(hi), c_f(h.get("lr", 1e-3)),
                 c_f(b1), c_f(b2), c_f(h.get("eps", 1e-8)),
                 c_f(h.get("weight_decay", 0.01 if adamw else 0.0)), int(params.step_count),
                 c_f(1.0 / self.size), int(adamw),
@@ -221,9 +222,6 @@ class FusedDP(NcclDP):
                 ptr(kx.status_word(self.device)), sm_count(self.device), stream())
             check(code, "pf_dp_fused_step")
             self.calls += 1
-        if self.deferred_below:
-            from ..ops import functional as Fn
-            Fn.weights_updated()
         if fp16:
             scaler.update(params.found_inf)
 

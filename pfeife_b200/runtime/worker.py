@@ -209,9 +209,12 @@ class StageWorker:
         self.idle_mem = 0
         self.use_graphs = bool(getattr(option, "cuda_graphs", False)) and device.type == "cuda"
         self.graph_warmup_steps = 1       # eager steps before capture (lazy inits, autotune)
-        self.graphs: Dict[Tuple[int, int], _GraphedStage] = {}
+        self.graphs: Dict[Tuple[int, int, int], _GraphedStage] = {}
         self.graph_pool = None
         self.slot_of: Dict[Tuple[int, int], int] = {}
+        self.graph_key: Dict[Tuple[int, int], Tuple[int, int, int]] = {}
+        # stages whose row-sharded weights were completed since the last optimizer step
+        self.gathered_stages: set = set()
         self.train_steps_done = 0
         self._reset_step_state()
 
@@ -377,9 +380,13 @@ class StageWorker:
         sp = self.part.stages[stage]
         ins = self._stage_inputs(comm, sp, mb)
         start = self.recorder.record_event(self.device)
+        # the first forward of a stage after an optimizer step completes its row-sharded weights
+        # (deferred all-gather); it is a graph of its own, since later forwards must not gather
+        gather = self._defers_gather() and stage not in self.gathered_stages
+        self.gathered_stages.add(stage)
         if self.use_graphs and torch.is_grad_enabled() and \
                 self.train_steps_done >= self.graph_warmup_steps:
-            gs = self._graph_for(sp, stage, mb, ins)
+            gs = self._graph_for(sp, stage, mb, ins, int(gather))
             if gs is not None:
                 for dst, src in zip(gs.static_ins, ins):
                     if dst is not src and torch.is_tensor(dst):
@@ -390,8 +397,16 @@ class StageWorker:
                 self.fw_inputs[(stage, mb)] = gs.static_ins
                 self.fw_outputs[(stage, mb)] = gs.static_outs
                 return
-        with gen_amp_context(self.device, self.option.mixed_precision):
-            outs = self.stage_mods[stage](*ins)
+        self.graph_key.pop((stage, mb), None)
+        if gather:
+            from ..ops import functional as Fn
+            Fn.gather_session(True)
+        try:
+            with gen_amp_context(self.device, self.option.mixed_precision):
+                outs = self.stage_mods[stage](*ins)
+        finally:
+            if gather:
+                Fn.gather_session(False)
         self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
         if not isinstance(outs, (tuple, list)):
             outs = (outs,)
@@ -399,16 +414,27 @@ class StageWorker:
         self.fw_outputs[(stage, mb)] = tuple(outs)
 
     # ------------------------------------------------------------------ CUDA graphs
-    def _graph_for(self, sp: StageSpec, stage: int, mb: int, ins: List[Any]
+    def _defers_gather(self) -> bool:
+        return bool(getattr(self.dp, "deferred_below", None)) and getattr(self.dp, "fused", False)
+
+    def _graph_for(self, sp: StageSpec, stage: int, mb: int, ins: List[Any], gather: int = 0
                    ) -> Optional[_GraphedStage]:
-        key = (stage, self.slot_of.get((stage, mb), 0))
+        key = (stage, self.slot_of.get((stage, mb), 0), gather)
+        self.graph_key[(stage, mb)] = key
         gs = self.graphs.get(key)
         if gs is not None:
             return None if gs.failed else gs
         gs = _GraphedStage()
         self.graphs[key] = gs
         try:
-            self._capture(gs, sp, stage, ins)
+            if gather:
+                from ..ops import functional as Fn
+                Fn.gather_session(True)
+            try:
+                self._capture(gs, sp, stage, ins)
+            finally:
+                if gather:
+                    Fn.gather_session(False)
         except Exception as e:   # the stage stays on the eager path
             gs.failed = True
             self.log.warning("CUDA graph capture of stage %d failed (%s: %s); running it eagerly",
@@ -506,7 +532,7 @@ class StageWorker:
             tensors.append(o)
             grads.append(g.reshape(o.shape))
         start = self.recorder.record_event(self.device)
-        gs = self.graphs.get((stage, self.slot_of.get((stage, mb), 0))) if self.use_graphs else None
+        gs = self.graphs.get(self.graph_key.get((stage, mb))) if self.use_graphs else None
         if gs is not None and not gs.failed and gs.static_outs is outs:
             if gs.bwd is not None:
                 for j, buf in gs.grad_outs:
@@ -571,6 +597,7 @@ class StageWorker:
         fp16 = self.scaler.enabled
         if self.dp is not None and self.dp.fused:
             self.dp.reduce_and_step(self.params, self.scaler, fp16)
+            self.gathered_stages.clear()    # 16-bit weight matrices are row-sharded again
             return
         if self.dp is not None:
             self.dp.all_reduce(self.params)

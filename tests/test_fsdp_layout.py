@@ -56,7 +56,7 @@ def test_deferrable_matrices_are_packed_first_within_a_group():
     assert q.slots[0].offset == 0 and not q.slots[1].deferred
 
 
-def test_freshness_follows_the_optimizer_epoch():
+def test_weights_are_gathered_once_per_gather_session():
     from pfeife_b200.ops import functional as Fn
     w = torch.zeros(256, 1024)
     lp = w.to(torch.bfloat16)
@@ -65,10 +65,15 @@ def test_freshness_follows_the_optimizer_epoch():
         slot = Fn._slot(w)
         assert Fn._slot(lp) is slot and not Fn._stale(slot)
         Fn.set_gather(w, Fn.GatherInfo(None, (128, 256), 2, 0, torch.zeros(2, dtype=torch.int32)))
+        assert not Fn._stale(slot)            # outside a session weights count as complete
+        Fn.gather_session(True)
         assert Fn._stale(slot)
-        slot.fresh_epoch = Fn._weights_epoch
+        slot.gathered_in = Fn._session_tls.id  # what the gathering op records
+        assert not Fn._stale(slot)            # a second use in the same forward does not gather
+        Fn.gather_session(False)
         assert not Fn._stale(slot)
-        Fn.weights_updated()
+        Fn.gather_session(True)               # the next optimizer step's first forward
         assert Fn._stale(slot)
+        Fn.gather_session(False)
     finally:
         Fn.unregister_params()
