@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-    python -m pfeife_b200.bench.kernels [--which gemm,norm,adamw] [--json out.jsonl]
+    python -m pfeife_b200.bench.kernels [--which gemm,conv,norm,adamw] [--json out.jsonl]
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MiB buffer, median of `--iters`.  Fractions are against the measured
@@ -83,6 +83,27 @@ def bench_gemm(timer, out):
                  "torch_matmul_ms": ms_ref, "vs_torch": ms_ref / ms})
 
 
+def bench_conv(timer, out):
+    """SDXL UNet 3x3 convolutions (NHWC, bf16): implicit GEMM vs im2col + GEMM vs cuDNN."""
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    shapes = [("sdxl_320_128", 4, 128, 320, 320), ("sdxl_640_64", 4, 64, 640, 640),
+              ("sdxl_1280_32", 4, 32, 1280, 1280), ("sdxl_up_1920_640_64", 4, 64, 1920, 640)]
+    for name, B, HW, Cin, Cout in shapes:
+        x = torch.randn(B, HW, HW, Cin, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(Cout, Cin, 3, 3, device="cuda") * 0.02).to(torch.bfloat16)
+        w2 = w.permute(0, 2, 3, 1).reshape(Cout, 9 * Cin).contiguous()
+        ms = timer(lambda: kx.conv_gemm(x, w2, 3, 3, 1, 1))
+        ms_cols = timer(lambda: kx.gemm(kx.im2col(x, 3, 3, 1, 1), w2))
+        xn = x.permute(0, 3, 1, 2)     # channels-last view for cuDNN
+        wn = w.contiguous(memory_format=torch.channels_last)
+        ms_ref = timer(lambda: torch.nn.functional.conv2d(xn, wn, padding=1))
+        flops = 2.0 * B * HW * HW * Cout * 9 * Cin
+        out({"kernel": "conv_implicit_gemm", "case": name, "ms": ms, "tflops": flops / ms / 1e9,
+             "frac_peak": flops / ms / 1e9 / tf, "peak_ref": tag, "ms_im2col_gemm": ms_cols,
+             "torch_conv2d_ms": ms_ref, "vs_torch": ms_ref / ms})
+
+
 def bench_norm(timer, out):
     from pfeife_b200.ops import kernels as kx
     hbm, tf, tag = peaks()
@@ -129,7 +150,7 @@ def main(argv=None):
             sink.write(line + "\n")
 
     timer = Timer(a.iters)
-    table = {"gemm": bench_gemm, "norm": bench_norm, "adamw": bench_adamw}
+    table = {"gemm": bench_gemm, "conv": bench_conv, "norm": bench_norm, "adamw": bench_adamw}
     for k in a.which.split(","):
         table[k](timer, out)
     from pfeife_b200.ops import kernels as kx

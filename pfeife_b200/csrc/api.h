@@ -126,6 +126,13 @@ PF_DECL int pf_groupnorm_bwd(const void* dy, const void* x, const void* mean, co
 PF_DECL int pf_upsample2x(const void* x, void* y, int B, int H, int W, int C, int backward,
                           int dtype, int sm_count, void* stream);
 
+// ---- gemm_sm100.cu : convolution as an implicit GEMM over an NHWC activation
+PF_DECL int pf_conv_gemm(const void* x, const void* w2, void* y, int B, int H, int W, int C,
+                         int Cout, int KH, int KW, int stride, int pad, long long ldw,
+                         long long ldy, int in_dtype, int out_dtype, const void* bias,
+                         int bias_dtype, const void* residual, long long ldr, int epilogue,
+                         int* status, int sm_count, void* stream);
+
 // ---- gemm_sm100.cu : GEMM with the all-gather of a row-sharded weight fused in
 PF_DECL int pf_gemm_allgather(const void* A, void* w_full, void* const* copies, int world,
                               int rank, const int* row_end, void* ready, void* C, int M, int N,

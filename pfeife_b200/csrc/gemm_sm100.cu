@@ -63,6 +63,14 @@ struct GemmParams {
   void* gather_dst;            // local full-size B [N, K] (pitch ldb); own rows already in place
   int* gather_ready;           // local counters, one per BN-row tile of B, zeroed before launch
   long long gather_ld;
+  // ---- implicit-GEMM convolution: A is an NHWC activation [B, H, W, C] read through a 4-D
+  //      tensor map; row m of the GEMM is output pixel m (tiles of 128 rows = whole output rows
+  //      of one image), k-block kb is filter tap (r, s) = kb / (C/64) and channels
+  //      64 * (kb % (C/64)); padding comes from the TMA out-of-bounds fill
+  int conv;                    // 0: A is a plain matrix
+  int conv_c64;                // C / 64
+  int conv_kw, conv_pad, conv_stride;
+  int conv_wo, conv_howo;      // output width, output pixels per image
 };
 
 template <int BN, int STAGES, int SPW>
@@ -248,10 +256,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
           const int k0 = kb * GEMM_BK;
+          // implicit-GEMM convolution: coordinates of this k-block's 128-pixel window
+          int cv_c = 0, cv_w = 0, cv_h = 0, cv_b = 0;
+          if (p.conv) {
+            const int tap = kb / p.conv_c64;
+            cv_c = (kb - tap * p.conv_c64) * 64;
+            const int r = tap / p.conv_kw, sx = tap - r * p.conv_kw;
+            cv_b = m0 / p.conv_howo;
+            const int ho0 = (m0 - cv_b * p.conv_howo) / p.conv_wo;
+            cv_w = sx - p.conv_pad;
+            cv_h = ho0 * p.conv_stride + r - p.conv_pad;
+          }
           if (PAIR) {
             if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
             const uint32_t bar = mapa_u32(&full_bar[stage], 0);
-            if (!p.a_mn) {
+            if (p.conv) {
+              tma_load_4d_pair(sa, &tmap_a, bar, cv_c, cv_w, cv_h, cv_b);
+            } else if (!p.a_mn) {
               tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
             } else {
 #pragma unroll
@@ -267,7 +288,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           } else {
             mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
-            if (!p.a_mn) {
+            if (p.conv) {
+              tma_load_4d(sa, &tmap_a, &full_bar[stage], cv_c, cv_w, cv_h, cv_b);
+            } else if (!p.a_mn) {
               tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
             } else {
 #pragma unroll
@@ -649,6 +672,29 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 
 using namespace pf;
 
+// 4-D map over an NHWC activation [B, H, W, C] (16-bit): box = 64 channels x `box_w` x `box_h`
+// pixels of one image, traversed with `stride` in both spatial dimensions
+static int make_tmap_nhwc(CUtensorMap* map, const void* base, int fmt, int B, int H, int W, int C,
+                          int box_w, int box_h, int stride) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -100;
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+  // a box dimension is the extent it spans in the tensor: `stride` times the pixels it delivers
+  cuuint32_t box[4] = {64, (cuuint32_t)(box_w * stride), (cuuint32_t)(box_h * stride), 1};
+  cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
+  CUresult r = enc(map, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
+}
+
+// convolution geometry of the call in flight on this thread (set by pf_conv_gemm)
+struct ConvArgs { int on = 0, B = 0, H = 0, W = 0, C = 0, KH = 0, KW = 0, stride = 1, pad = 0,
+                  Ho = 0, Wo = 0; };
+static thread_local ConvArgs g_conv;
+
 // all-gather arguments of the call in flight on this thread (set by pf_gemm_allgather)
 struct GatherArgs { int world = 0, rank = 0; int row_end[8] = {}; int* ready = nullptr; const void* src[8] = {}; };
 static thread_local GatherArgs g_gather;
@@ -660,7 +706,7 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
                    int* status, int sm_count, int tile_n, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (in_dtype != PF_F16 && in_dtype != PF_BF16) return -1;
-  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+  if ((!g_conv.on && (lda % 8)) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;  // TMA needs 16-byte aligned bases and pitches
   const int fmt = in_dtype == PF_BF16 ? 1 : 0;
@@ -682,11 +728,23 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
       pair = 4 * w2 <= 5 * w1;
     }
   }
-  const int BN = pair ? 128 : (tn == 128 || tn == 256) ? tn : (N <= 128 ? 128 : 256);
+  int bn_auto = N <= 128 ? 128 : 256;
+  if (!pair && tn == 0 && N > 128) {
+    // 128 x 128 tiles (0.55 of a 128 x 256 tile each) when they fill the waves better
+    const long long t1 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    const long long th = (long long)((M + 127) / 128) * ((N + 127) / 128);
+    const long long w1 = (t1 + sm_count - 1) / sm_count;
+    const long long wh = (th + sm_count - 1) / sm_count;
+    if (11 * wh < 20 * w1) bn_auto = 128;
+  }
+  const int BN = pair ? 128 : (tn == 128 || tn == 256) ? tn : bn_auto;
 
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = make_tmap_2d_16bit(&ta, A, fmt, K, M, lda, GEMM_BK, GEMM_BM);
+  if (g_conv.on)
+    r = make_tmap_nhwc(&ta, A, fmt, g_conv.B, g_conv.H, g_conv.W, g_conv.C, g_conv.Wo,
+                       GEMM_BM / g_conv.Wo, g_conv.stride);
+  else if (!a_mn) r = make_tmap_2d_16bit(&ta, A, fmt, K, M, lda, GEMM_BK, GEMM_BM);
   else       r = make_tmap_2d_16bit(&ta, A, fmt, M, K, lda, 64, GEMM_BK);
   if (r) return r;
   if (!b_mn) r = make_tmap_2d_16bit(&tb, B, fmt, K, N, ldb, GEMM_BK, BN);
@@ -706,6 +764,11 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
   p.gather_dst = const_cast<void*>(B);
   p.gather_ready = g_gather.ready; p.gather_ld = ldb;
   for (int i = 0; i < 8; ++i) p.gather_src[i] = g_gather.src[i];
+  p.conv = g_conv.on;
+  if (g_conv.on) {
+    p.conv_c64 = g_conv.C / 64; p.conv_kw = g_conv.KW; p.conv_pad = g_conv.pad;
+    p.conv_stride = g_conv.stride; p.conv_wo = g_conv.Wo; p.conv_howo = g_conv.Ho * g_conv.Wo;
+  }
   const size_t es = out_dtype == PF_F32 ? 4 : 2;
   auto aligned = [&](const void* ptr, long long ld) {
     return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0);
@@ -777,5 +840,26 @@ PF_API int pf_gemm_allgather(const void* A, void* w_full, void* const* copies, i
                         bias_dtype, residual, ldr, aux, ldaux, epilogue, 0, alpha, status,
                         sm_count, 256, stream);
   g_gather = GatherArgs();
+  return r;
+}
+
+// Convolution as an implicit GEMM (no im2col buffer): y[B*Ho*Wo, Cout] = epi(patches(x) . w2^T)
+// with x NHWC [B, H, W, C] and w2 [Cout, KH*KW*C] (taps outermost, channels innermost).  Needs
+// C % 64 == 0, 128 % Wo == 0, (Ho * Wo) % 128 == 0 (tiles are whole output rows of one image)
+// and stride 1 or 2; returns -3 otherwise so that the caller can take the im2col route.
+PF_API int pf_conv_gemm(const void* x, const void* w2, void* y, int B, int H, int W, int C,
+                        int Cout, int KH, int KW, int stride, int pad, long long ldw,
+                        long long ldy, int in_dtype, int out_dtype, const void* bias,
+                        int bias_dtype, const void* residual, long long ldr, int epilogue,
+                        int* status, int sm_count, void* stream) {
+  const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
+  if (C % 64 || Wo <= 0 || Wo > 128 || 128 % Wo || (Ho * Wo) % 128 || (stride != 1 && stride != 2))
+    return -3;
+  g_conv.on = 1; g_conv.B = B; g_conv.H = H; g_conv.W = W; g_conv.C = C; g_conv.KH = KH;
+  g_conv.KW = KW; g_conv.stride = stride; g_conv.pad = pad; g_conv.Ho = Ho; g_conv.Wo = Wo;
+  const int r = pf_gemm(x, w2, y, B * Ho * Wo, Cout, KH * KW * C, 0, ldw, ldy, 0, 0, in_dtype,
+                        out_dtype, bias, bias_dtype, residual, ldr, nullptr, 0, epilogue, 0, 1.0f,
+                        status, sm_count, 0, stream);
+  g_conv = ConvArgs();
   return r;
 }

@@ -963,7 +963,8 @@ def _pad_to8(n: int) -> int:
 @torch.library.custom_op("pfeife::conv2d_fwd", mutates_args=())
 def conv2d_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], stride: int, pad: int) -> Tensor:
     """Channels-last convolution: x [B, H, W, Cin], w [Cout, Cin, KH, KW] -> [B, Ho, Wo, Cout].
-    On the native path the convolution is a tcgen05 GEMM over im2col rows (1x1: no im2col)."""
+    On the native path the convolution is a tcgen05 implicit GEMM (patches read straight from
+    x by TMA) when the shape allows it, else a GEMM over im2col rows (1x1: no im2col)."""
     Cout, Cin, KH, KW = w.shape
     cd = compute_dtype(x)
     if x.is_cuda and cd in (torch.float16, torch.bfloat16):
@@ -978,13 +979,14 @@ def conv2d_fwd(x: Tensor, w: Tensor, bias: Optional[Tensor], stride: int, pad: i
         w2 = w2.reshape(cout8, KH * KW * cin8).contiguous()
         Ho = (H + 2 * pad - KH) // stride + 1
         Wo = (W + 2 * pad - KW) // stride + 1
-        if KH == 1 and KW == 1 and stride == 1 and pad == 0:
-            cols = xc.reshape(B * H * W, cin8)
-        else:
-            cols = kx.im2col(xc, KH, KW, stride, pad)
         b2 = None
         if bias is not None:
             b2 = bias.float() if cout8 == Cout else F.pad(bias.float(), (0, cout8 - Cout))
+        one = KH == 1 and KW == 1 and stride == 1 and pad == 0
+        if not one and cin8 == Cin and kx.conv_gemm_supported(xc.contiguous(), KH, KW, stride, pad):
+            y = kx.conv_gemm(xc.contiguous(), w2, KH, KW, stride, pad, bias=b2)
+            return y[..., :Cout].contiguous() if cout8 != Cout else y
+        cols = xc.reshape(B * H * W, cin8) if one else kx.im2col(xc, KH, KW, stride, pad)
         y = kx.gemm(cols, w2, bias=b2)
         y = y.view(B, Ho, Wo, cout8)
         return y[..., :Cout].contiguous() if cout8 != Cout else y
@@ -1028,9 +1030,20 @@ def conv2d_bwd(dy: Tensor, x: Tensor, w: Tensor, stride: int, pad: int, need_dx:
             if cin8 != Cin or cout8 != Cout:
                 w2 = F.pad(w2, (0, cin8 - Cin, 0, 0, 0, 0, 0, cout8 - Cout))
             w2 = w2.reshape(cout8, KH * KW * cin8).contiguous()
-            dcols = kx.gemm(dy2, w2, b_mn=True)                                  # [M, K]
-            dxp = dcols.view(B, H, W, cin8) if one else \
-                kx.col2im(dcols, (B, H, W, cin8), KH, KW, stride, pad)
+            dy4 = dy2.view(B, -1, dy.shape[2], cout8)
+            if not one and stride == 1 and cout8 == Cout and \
+                    kx.conv_gemm_supported(dy4, KH, KW, 1, KH - 1 - pad) and \
+                    dy4.shape[1] + 2 * (KH - 1 - pad) - KH + 1 == H:
+                # dx = correlation of dy with the taps flipped and the channel roles swapped
+                wt = _weight_as(w, cd).flip(2, 3).permute(1, 2, 3, 0)     # [Cin, KH, KW, Cout]
+                if cin8 != Cin:
+                    wt = F.pad(wt, (0, 0, 0, 0, 0, 0, 0, cin8 - Cin))
+                wt = wt.reshape(cin8, KH * KW * cout8).contiguous()
+                dxp = kx.conv_gemm(dy4, wt, KH, KW, 1, KH - 1 - pad)
+            else:
+                dcols = kx.gemm(dy2, w2, b_mn=True)                              # [M, K]
+                dxp = dcols.view(B, H, W, cin8) if one else \
+                    kx.col2im(dcols, (B, H, W, cin8), KH, KW, stride, pad)
             dx = dxp[..., :Cin].contiguous() if cin8 != Cin else dxp
         db = kx.colsum(dy2)[:Cout].contiguous() if need_db else dy.new_empty(0, dtype=torch.float32)
         return dx, dw, db

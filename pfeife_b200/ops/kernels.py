@@ -406,6 +406,40 @@ def im2col(x: torch.Tensor, KH: int, KW: int, stride: int, pad: int) -> torch.Te
     return cols
 
 
+def conv_gemm_supported(x: torch.Tensor, KH: int, KW: int, stride: int, pad: int) -> bool:
+    """True when the implicit-GEMM convolution covers this problem: x NHWC with C % 64 == 0,
+    tiles of 128 output pixels made of whole output rows of one image, stride 1 or 2."""
+    B, H, W, C = x.shape
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    return (x.is_contiguous() and C % 64 == 0 and 0 < Wo <= 128 and 128 % Wo == 0
+            and (Ho * Wo) % 128 == 0 and stride in (1, 2))
+
+
+def conv_gemm(x: torch.Tensor, w2: torch.Tensor, KH: int, KW: int, stride: int, pad: int, *,
+              bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+              epilogue: int = EPI_NONE) -> torch.Tensor:
+    """Convolution as an implicit GEMM: x NHWC [B, H, W, C], w2 [Cout, KH*KW*C] (taps outermost,
+    channels innermost) -> [B, Ho, Wo, Cout].  The patches are never materialised: the GEMM's A
+    tiles come straight from x through a 4-D tensor map whose out-of-bounds fill is the zero
+    padding."""
+    L = _lib.lib()
+    B, H, W, C = x.shape
+    Cout = w2.shape[0]
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    assert w2.shape[1] == KH * KW * C and w2.stride(1) == 1 and w2.dtype == x.dtype
+    y = torch.empty((B, Ho, Wo, Cout), dtype=x.dtype, device=x.device)
+    r2 = residual.reshape(-1, Cout) if residual is not None else None
+    check(L.pf_conv_gemm(ptr(x), ptr(w2), ptr(y), B, H, W, C, Cout, KH, KW, stride, pad,
+                         c_ll(w2.stride(0)), c_ll(Cout), dt(x.dtype), dt(y.dtype), ptr(bias),
+                         dt(bias.dtype) if bias is not None else 0, ptr(r2),
+                         c_ll(r2.stride(0) if r2 is not None else 0), epilogue,
+                         ptr(status_word(x.device)), sm_count(x.device), stream()),
+          "pf_conv_gemm")
+    return y
+
+
 def col2im(dcols: torch.Tensor, shape, KH: int, KW: int, stride: int, pad: int) -> torch.Tensor:
     L = _lib.lib()
     B, H, W, C = shape

@@ -1,4 +1,4 @@
-"""UNet kernels (im2col GEMM convolution, GroupNorm+SiLU, upsample) and the Llama / UNet model
+"""UNet kernels (implicit-GEMM and im2col convolution, GroupNorm+SiLU, upsample) and the Llama / UNet model
 families on the GPU against fp32 CPU references."""
 import pytest
 import torch
@@ -29,6 +29,41 @@ def test_conv2d_nhwc(cin, cout, k, stride):
     bg = b.cuda().requires_grad_()
     y = ops.conv2d(xg, wg, bg, stride, k // 2)
     y.float().sum().backward()
+    _close(y, yr.detach(), 3e-2)
+    _close(xg.grad, xr.grad, 3e-2)
+    _close(wg.grad, wr.grad, 3e-2)
+    _close(bg.grad, br.grad, 3e-2)
+
+
+@pytest.mark.parametrize("cin,cout,hw,k,stride", [
+    (64, 128, 16, 3, 1),      # implicit GEMM forward and dgrad, tiles of 8 output rows
+    (128, 64, 32, 3, 1),      # tiles of 4 output rows; 2048 output pixels
+    (64, 64, 32, 3, 2),       # stride 2: implicit forward (16 x 16 outputs), col2im dgrad
+    (128, 192, 64, 3, 1),     # two output rows per tile, several k-blocks per tap
+    (64, 72, 16, 3, 1),       # Cout not a multiple of 64: implicit forward, GEMM + col2im dgrad
+])
+def test_conv2d_implicit_gemm(cin, cout, hw, k, stride):
+    """Shapes the implicit-GEMM path covers (C % 64 == 0, whole output rows per 128-pixel tile):
+    values and all gradients against an fp32 reference, with a random upstream gradient so that
+    a misplaced filter tap cannot cancel out."""
+    from pfeife_b200 import ops
+    from pfeife_b200.ops import kernels as kx
+    torch.manual_seed(1)
+    x = torch.randn(2, hw, hw, cin)
+    w = torch.randn(cout, cin, k, k) * 0.05
+    b = torch.randn(cout)
+    assert kx.conv_gemm_supported(x, k, k, stride, k // 2)
+    xr, wr, br = (t.clone().requires_grad_() for t in (x, w, b))
+    yr = F.conv2d(xr.permute(0, 3, 1, 2), wr, br, stride=stride, padding=k // 2).permute(0, 2, 3, 1)
+    gy = torch.randn(yr.shape)
+    yr.backward(gy)
+    xg = x.cuda().to(torch.bfloat16).requires_grad_()
+    wg = w.cuda().to(torch.bfloat16).requires_grad_()
+    bg = b.cuda().requires_grad_()
+    y = ops.conv2d(xg, wg, bg, stride, k // 2)
+    y.backward(gy.cuda().to(y.dtype))
+    torch.cuda.synchronize()
+    kx.check_status()
     _close(y, yr.detach(), 3e-2)
     _close(xg.grad, xr.grad, 3e-2)
     _close(wg.grad, wr.grad, 3e-2)
