@@ -133,6 +133,10 @@ PF_DECL int pf_conv_gemm(const void* x, const void* w2, void* y, int B, int H, i
                          int bias_dtype, const void* residual, long long ldr, int epilogue,
                          int* status, int sm_count, void* stream);
 
+PF_DECL int pf_conv_wgrad(const void* dy, const void* x, void* dw2, int B, int H, int W, int C,
+                          int Cout, int KH, int KW, int stride, int pad, int in_dtype,
+                          int accumulate, int* status, int sm_count, void* stream);
+
 // ---- gemm_sm100.cu : GEMM with the all-gather of a row-sharded weight fused in
 PF_DECL int pf_gemm_allgather(const void* A, void* w_full, void* const* copies, int world,
                               int rank, const int* row_end, void* ready, void* C, int M, int N,

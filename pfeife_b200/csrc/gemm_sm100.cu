@@ -67,7 +67,10 @@ struct GemmParams {
   //      tensor map; row m of the GEMM is output pixel m (tiles of 128 rows = whole output rows
   //      of one image), k-block kb is filter tap (r, s) = kb / (C/64) and channels
   //      64 * (kb % (C/64)); padding comes from the TMA out-of-bounds fill
-  int conv;                    // 0: A is a plain matrix
+  //      conv == 2 (weight gradient): B is the activation instead, read as an MN-major operand:
+  //      k-block kb is 64 consecutive output pixels, column n of the GEMM is filter tap n / C
+  //      and channel n % C
+  int conv;                    // 0: plain matrices, 1: A from the activation, 2: B from it
   int conv_c64;                // C / 64
   int conv_kw, conv_pad, conv_stride;
   int conv_wo, conv_howo;      // output width, output pixels per image
@@ -258,7 +261,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int k0 = kb * GEMM_BK;
           // implicit-GEMM convolution: coordinates of this k-block's 128-pixel window
           int cv_c = 0, cv_w = 0, cv_h = 0, cv_b = 0;
-          if (p.conv) {
+          if (p.conv == 2) {     // the 64 output pixels of this k-block (part of one image)
+            const int p0 = kb * GEMM_BK;
+            cv_b = p0 / p.conv_howo;
+            const int rem = p0 - cv_b * p.conv_howo;
+            cv_h = (rem / p.conv_wo) * p.conv_stride - p.conv_pad;
+            cv_w = (rem % p.conv_wo) * p.conv_stride - p.conv_pad;
+          } else if (p.conv) {
             const int tap = kb / p.conv_c64;
             cv_c = (kb - tap * p.conv_c64) * 64;
             const int r = tap / p.conv_kw, sx = tap - r * p.conv_kw;
@@ -270,7 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (PAIR) {
             if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
             const uint32_t bar = mapa_u32(&full_bar[stage], 0);
-            if (p.conv) {
+            if (p.conv == 1) {
               tma_load_4d_pair(sa, &tmap_a, bar, cv_c, cv_w, cv_h, cv_b);
             } else if (!p.a_mn) {
               tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
@@ -279,7 +288,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int j = 0; j < GEMM_BM / 64; ++j)
                 tma_load_2d_pair(sa + j * 8192, &tmap_a, bar, m0 + j * 64, k0);
             }
-            if (!p.b_mn) {
+            if (p.conv == 2) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                const int n = nb0 + j * 64, tap = n / (p.conv_c64 * 64);
+                const int r = tap / p.conv_kw, sx = tap - r * p.conv_kw;
+                tma_load_4d_pair(sb + j * 8192, &tmap_b, bar, n - tap * p.conv_c64 * 64,
+                                 cv_w + sx, cv_h + r, cv_b);
+              }
+            } else if (!p.b_mn) {
               tma_load_2d_pair(sb, &tmap_b, bar, k0, nb0);
             } else {
 #pragma unroll
@@ -288,7 +305,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           } else {
             mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
-            if (p.conv) {
+            if (p.conv == 1) {
               tma_load_4d(sa, &tmap_a, &full_bar[stage], cv_c, cv_w, cv_h, cv_b);
             } else if (!p.a_mn) {
               tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
@@ -297,7 +314,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int j = 0; j < GEMM_BM / 64; ++j)
                 tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
             }
-            if (!p.b_mn) {
+            if (p.conv == 2) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                const int n = n0 + j * 64, tap = n / (p.conv_c64 * 64);
+                const int r = tap / p.conv_kw, sx = tap - r * p.conv_kw;
+                tma_load_4d(sb + j * 8192, &tmap_b, &full_bar[stage], n - tap * p.conv_c64 * 64,
+                            cv_w + sx, cv_h + r, cv_b);
+              }
+            } else if (!p.b_mn) {
               tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
             } else {
 #pragma unroll
@@ -706,7 +731,8 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
                    int* status, int sm_count, int tile_n, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (in_dtype != PF_F16 && in_dtype != PF_BF16) return -1;
-  if ((!g_conv.on && (lda % 8)) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+  if ((g_conv.on != 1 && (lda % 8)) || (g_conv.on != 2 && (ldb % 8)) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;  // TMA needs 16-byte aligned bases and pitches
   const int fmt = in_dtype == PF_BF16 ? 1 : 0;
@@ -741,13 +767,17 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
 
   CUtensorMap ta, tb;
   int r;
-  if (g_conv.on)
+  if (g_conv.on == 1)
     r = make_tmap_nhwc(&ta, A, fmt, g_conv.B, g_conv.H, g_conv.W, g_conv.C, g_conv.Wo,
                        GEMM_BM / g_conv.Wo, g_conv.stride);
   else if (!a_mn) r = make_tmap_2d_16bit(&ta, A, fmt, K, M, lda, GEMM_BK, GEMM_BM);
   else       r = make_tmap_2d_16bit(&ta, A, fmt, M, K, lda, 64, GEMM_BK);
   if (r) return r;
-  if (!b_mn) r = make_tmap_2d_16bit(&tb, B, fmt, K, N, ldb, GEMM_BK, BN);
+  if (g_conv.on == 2) {
+    const int bw = g_conv.Wo < GEMM_BK ? g_conv.Wo : GEMM_BK;
+    r = make_tmap_nhwc(&tb, B, fmt, g_conv.B, g_conv.H, g_conv.W, g_conv.C, bw, GEMM_BK / bw,
+                       g_conv.stride);
+  } else if (!b_mn) r = make_tmap_2d_16bit(&tb, B, fmt, K, N, ldb, GEMM_BK, BN);
   else       r = make_tmap_2d_16bit(&tb, B, fmt, N, K, ldb, 64, GEMM_BK);
   if (r) return r;
 
@@ -860,6 +890,26 @@ PF_API int pf_conv_gemm(const void* x, const void* w2, void* y, int B, int H, in
   const int r = pf_gemm(x, w2, y, B * Ho * Wo, Cout, KH * KW * C, 0, ldw, ldy, 0, 0, in_dtype,
                         out_dtype, bias, bias_dtype, residual, ldr, nullptr, 0, epilogue, 0, 1.0f,
                         status, sm_count, 0, stream);
+  g_conv = ConvArgs();
+  return r;
+}
+
+// Weight gradient of the same convolution as an implicit GEMM:
+// dw2[Cout, KH*KW*C] (+)= dy[B*Ho*Wo, Cout]^T . patches(x), fp32 output; the patches are read
+// from x (NHWC) 64 output pixels at a time.  Needs C % 64 == 0, Cout % 8 == 0, Wo dividing 64 or
+// a multiple of it, (Ho * Wo) % 64 == 0, stride 1 or 2; returns -3 otherwise.
+PF_API int pf_conv_wgrad(const void* dy, const void* x, void* dw2, int B, int H, int W, int C,
+                         int Cout, int KH, int KW, int stride, int pad, int in_dtype,
+                         int accumulate, int* status, int sm_count, void* stream) {
+  const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
+  if (C % 64 || Cout % 8 || Wo <= 0 || (64 % Wo && Wo % 64) || (Ho * Wo) % 64 ||
+      (stride != 1 && stride != 2))
+    return -3;
+  g_conv.on = 2; g_conv.B = B; g_conv.H = H; g_conv.W = W; g_conv.C = C; g_conv.KH = KH;
+  g_conv.KW = KW; g_conv.stride = stride; g_conv.pad = pad; g_conv.Ho = Ho; g_conv.Wo = Wo;
+  const int r = pf_gemm(dy, x, dw2, Cout, KH * KW * C, B * Ho * Wo, Cout, 0,
+                        (long long)KH * KW * C, 1, 1, in_dtype, PF_F32, nullptr, 0, nullptr, 0,
+                        nullptr, 0, 0, accumulate, 1.0f, status, sm_count, 0, stream);
   g_conv = ConvArgs();
   return r;
 }

@@ -1021,8 +1021,12 @@ def conv2d_bwd(dy: Tensor, x: Tensor, w: Tensor, stride: int, pad: int, need_dx:
             dy2 = F.pad(dy2, (0, cout8 - Cout))
         dy2 = dy2.contiguous()
         one = KH == 1 and KW == 1 and stride == 1 and pad == 0
-        cols = xc.reshape(B * H * W, cin8) if one else kx.im2col(xc, KH, KW, stride, pad)
-        dw2 = kx.gemm(dy2, cols, a_mn=True, b_mn=True, out_dtype=torch.float32)   # [cout8, K]
+        if not one and cin8 == Cin and \
+                kx.conv_wgrad_supported(xc.contiguous(), cout8, KH, KW, stride, pad):
+            dw2 = kx.conv_wgrad(dy2, xc.contiguous(), KH, KW, stride, pad)       # [cout8, K]
+        else:
+            cols = xc.reshape(B * H * W, cin8) if one else kx.im2col(xc, KH, KW, stride, pad)
+            dw2 = kx.gemm(dy2, cols, a_mn=True, b_mn=True, out_dtype=torch.float32)
         dw = dw2.view(cout8, KH, KW, cin8)[:Cout, :, :, :Cin].permute(0, 3, 1, 2).contiguous()
         dx = dy.new_empty(0)
         if need_dx:

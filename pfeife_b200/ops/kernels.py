@@ -440,6 +440,31 @@ def conv_gemm(x: torch.Tensor, w2: torch.Tensor, KH: int, KW: int, stride: int, 
     return y
 
 
+def conv_wgrad_supported(x: torch.Tensor, cout: int, KH: int, KW: int, stride: int, pad: int
+                         ) -> bool:
+    B, H, W, C = x.shape
+    Ho = (H + 2 * pad - KH) // stride + 1
+    Wo = (W + 2 * pad - KW) // stride + 1
+    return (x.is_contiguous() and C % 64 == 0 and cout % 8 == 0 and Wo > 0
+            and (64 % Wo == 0 or Wo % 64 == 0) and (Ho * Wo) % 64 == 0 and stride in (1, 2))
+
+
+def conv_wgrad(dy2: torch.Tensor, x: torch.Tensor, KH: int, KW: int, stride: int, pad: int,
+               out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """dw2 [Cout, KH*KW*C] fp32 (+)= dy2[B*Ho*Wo, Cout]^T . patches(x) without an im2col buffer."""
+    L = _lib.lib()
+    B, H, W, C = x.shape
+    Cout = dy2.shape[1]
+    assert dy2.is_contiguous() and dy2.dtype == x.dtype
+    if out is None:
+        out = torch.empty((Cout, KH * KW * C), dtype=torch.float32, device=x.device)
+        accumulate = False
+    check(L.pf_conv_wgrad(ptr(dy2), ptr(x), ptr(out), B, H, W, C, Cout, KH, KW, stride, pad,
+                          dt(x.dtype), int(accumulate), ptr(status_word(x.device)),
+                          sm_count(x.device), stream()), "pf_conv_wgrad")
+    return out
+
+
 def col2im(dcols: torch.Tensor, shape, KH: int, KW: int, stride: int, pad: int) -> torch.Tensor:
     L = _lib.lib()
     B, H, W, C = shape
