@@ -54,6 +54,8 @@ struct GemmParams {
   int a_mn, b_mn;
   int fmt;        // 0 = fp16 inputs, 1 = bf16 inputs
   int* status;
+  int split_k;    // > 1: each tile's k-blocks are divided among this many work items, which all
+                  // add into C (needs accumulate through the TMA reduce-add epilogue)
   // ---- fused all-gather of the B operand (weights sharded by rows over `gather_world` ranks)
   int gather_world;            // 0: B is an ordinary local operand
   int gather_rank;
@@ -185,8 +187,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int num_m = (p.M + BMT - 1) / BMT;
   const int num_n = (p.N + BNT - 1) / BNT;
-  const int num_tiles = num_m * num_n;
+  const int split_k = p.split_k > 1 ? p.split_k : 1;
+  const int num_tiles = num_m * num_n * split_k;        // work items: (tile, k-slice)
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_mn = num_m * num_n;
   // with a fused all-gather the tiles whose rows of B this rank owns are computed first, while
   // the remote rows are still arriving
   const int own0 = (GATHER && p.gather_rank > 0) ? p.gather_row_end[p.gather_rank - 1] : 0;
@@ -231,7 +235,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       bool all_gathered = false;
       // pair: both CTAs' loads of a stage are counted on the leader's barrier
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+        const int tile = item % num_mn, ks = item / num_mn;
+        const int kb_begin = (int)((long long)num_kb * ks / split_k);
+        const int kb_end = (int)((long long)num_kb * (ks + 1) / split_k);
         const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
         const int nt = (tile / num_m + n_rot) % num_n;
         const int n0 = nt * BNT;
@@ -253,7 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (!ok) break;
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -349,7 +356,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+        const int ks = item / num_mn;
+        const int kb_begin = (int)((long long)num_kb * ks / split_k);
+        const int kb_end = (int)((long long)num_kb * (ks + 1) / split_k);
         ok = PAIR ? mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, p.status,
                                       PF_ERR_TIMEOUT_TMEM_EMPTY)
                   : mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status,
@@ -357,7 +367,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BNT;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, p.status, PF_ERR_TIMEOUT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -367,8 +377,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             const uint64_t da = make_desc_sw128(sa + k * a_adv, a_lbo, 1024);
             const uint64_t db = make_desc_sw128(sb + k * b_adv, b_lbo, 1024);
-            if (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
-            else tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+            const uint32_t acc_on = (kb != kb_begin) || (k != 0);
+            if (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, acc_on);
+            else tc_mma_f16(d_tmem, da, db, idesc, acc_on);
           }
           // smem slot reusable (in both CTAs of a pair) once these MMAs retire
           if (PAIR) tc_commit_pair(&empty_bar[stage], 3);
@@ -446,7 +457,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool tma_out = p.tma_store != 0;
     const bool bias_vec = p.bias && p.bias_dtype == PF_F32 &&
                           (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+    for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+      const int tile = item % num_mn;
       const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
       const int n0 = ((tile / num_m + n_rot) % num_n) * BNT;
       ok = mbar_wait(&tmem_full[acc], acc_phase, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
@@ -655,7 +667,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   if (PAIR) {
-    const int num_tiles = ((p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((p.N + 2 * BN - 1) / (2 * BN));
+    const int num_tiles = ((p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) *
+                          ((p.N + 2 * BN - 1) / (2 * BN)) * (p.split_k > 1 ? p.split_k : 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (sm_count / 2));
     cfg.blockDim = dim3(THREADS);
@@ -686,7 +699,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     if (e != cudaSuccess) return (int)e;
     return 0;
   }
-  const int num_tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
+  const int num_tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN) *
+                        (p.split_k > 1 ? p.split_k : 1);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   kern<<<grid, THREADS, S::TOTAL, stream>>>(ta, tb, tc, taux, p);
   PF_CHECK_LAUNCH();
@@ -721,7 +735,10 @@ struct ConvArgs { int on = 0, B = 0, H = 0, W = 0, C = 0, KH = 0, KW = 0, stride
 static thread_local ConvArgs g_conv;
 
 // all-gather arguments of the call in flight on this thread (set by pf_gemm_allgather)
-struct GatherArgs { int world = 0, rank = 0; int row_end[8] = {}; int* ready = nullptr; const void* src[8] = {}; };
+struct GatherArgs {
+  int world = 0, rank = 0; int row_end[8] = {}; int* ready = nullptr; const void* src[8] = {};
+  bool on_any() const { return world > 1; }
+};
 static thread_local GatherArgs g_gather;
 
 PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -737,7 +754,8 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     return -2;  // TMA needs 16-byte aligned bases and pitches
   const int fmt = in_dtype == PF_BF16 ? 1 : 0;
   // tile_n: low bits 0 / 128 / 256 = tile width of the single-CTA form; bit 10 forces the
-  // direct-store epilogue, bit 11 forces the CTA-pair form, bit 12 forbids it (tests, benches)
+  // direct-store epilogue, bit 11 forces the CTA-pair form, bit 12 forbids it, bit 13 forbids
+  // the split reduction (tests, benches)
   const int tn = tile_n & 1023;
   if (sm_count <= 0) sm_count = 148;
   bool pair = false;
@@ -808,6 +826,22 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
   // 16-bit accumulation (unused by the framework) stays on the direct path
   p.tma_store = p.vec_ok && !(accumulate && out_dtype != PF_F32) && !(tile_n & 1024) &&
                 !(aux && out_dtype == PF_F32);
+  // Split-K: a gradient-accumulating GEMM whose tiles do not fill the GPU divides each tile's
+  // reduction among several work items; they all reduce-add into C, which costs nothing extra
+  // because the epilogue accumulates anyway.
+  p.split_k = 1;
+  if (p.tma_store && accumulate && out_dtype == PF_F32 && !g_gather.on_any() && !g_conv.on &&
+      !bias && !residual && epilogue == EPI_NONE && !(tile_n & 8192)) {
+    const int bm = pair ? 256 : 128, bn = pair ? 256 : BN;
+    const long long tiles = (long long)((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+    const long long slots = pair ? sm_count / 2 : sm_count;
+    const int nkb = (K + GEMM_BK - 1) / GEMM_BK;
+    double best = 1e30;
+    for (int sk = 1; sk <= 4 && sk * 8 <= nkb; ++sk) {
+      const double waves = (double)((tiles * sk + slots - 1) / slots) / sk + 0.03 * (sk - 1);
+      if (waves < best - 1e-9) { best = waves; p.split_k = sk; }
+    }
+  }
   CUtensorMap tc, taux;
   memset(&tc, 0, sizeof(tc));
   memset(&taux, 0, sizeof(taux));

@@ -87,6 +87,22 @@ def test_gemm_epilogues(tile_n, M, N, K):
     _close(bucket, 1.0 + 2.0 * _ref(a, b, False, False), K, torch.float32)
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 4096), (1408, 1408, 6168), (304, 704, 2048)])
+@pytest.mark.parametrize("form", [0, 4096])
+def test_gemm_accumulate_with_split_reduction(M, N, K, form):
+    """Few output tiles and a long reduction: the gradient-accumulating GEMM divides each tile's
+    k-blocks among several work items that all add into the fp32 output."""
+    from pfeife_b200.ops import kernels as kx
+    a, b = _mk(M, N, K, True, True, torch.bfloat16, seed=3)
+    a, b = a * 0.1, b * 0.1
+    out = torch.full((M, N), 0.5, device="cuda")
+    kx.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True, tile_n=form)
+    kx.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True, tile_n=form)
+    torch.cuda.synchronize()
+    kx.check_status()
+    _close(out, 0.5 + 2.0 * _ref(a, b, True, True), K, torch.float32)
+
+
 def test_gemm_strided_views():
     """Operands that are column slices of a wider tensor (fused QKV) keep their pitch."""
     from pfeife_b200.ops import kernels as kx
