@@ -12,7 +12,8 @@ micro-batch 24 x batch_cnt 8 per pipeline) on N GPUs of one node, driven through
 Prints ONE JSON line on the global main process.  ``value`` is whole-job samples/s from a
 device-timed loop (CUDA events, barrier + synchronize on both sides, max over ranks) with the
 inputs resident on the device; ``e2e.value`` repeats the measurement with every step copying
-its inputs from pinned host memory and reading the loss back.  With more than one GPU the
+its inputs from pinned host memory (prefetched one step ahead on a side stream, as a data
+loader would) and reading the loss back.  With more than one GPU the
 PPxDP mesh is chosen by the planner from a profile taken on rank 0 before the process groups
 are built (``--dp_mesh`` overrides; the table it chose from is reported as
 ``planner_mesh_table``).
@@ -251,12 +252,34 @@ def run_native(args) -> int:
         host = [t.pin_memory() for t in host]
     resident = [t.to(dev) for t in host]
 
-    def one_step(e2e: bool):
-        batch = [t.to(dev, non_blocking=True) for t in host] if e2e else resident
+    # End-to-end steps read their inputs from pinned host memory and bring the loss back.  Like
+    # a prefetching data loader, the copy of step i+1's inputs is issued on a side stream
+    # before step i is launched, so it travels while step i computes; every step still makes
+    # its own host-to-device copy inside the timed region.
+    copy_stream = None if cpu else torch.cuda.Stream(device=dev)
+    pending = []
+
+    def fetch():
+        if cpu:
+            return list(host), None
+        with torch.cuda.stream(copy_stream):
+            batch = [t.to(dev, non_blocking=True) for t in host]
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+        return batch, ev
+
+    def one_step(e2e: bool, last: bool = False):
+        if not e2e:
+            return runner.step(*resident)
+        batch, ev = pending.pop() if pending else fetch()
+        if not last:
+            pending.append(fetch())
+        if ev is not None:
+            torch.cuda.current_stream(dev).wait_event(ev)
+            for t in batch:
+                t.record_stream(torch.cuda.current_stream(dev))
         losses = runner.step(*batch)
-        if e2e:
-            return float(torch.stack([l.float() for l in losses]).sum().cpu())
-        return losses
+        return float(torch.stack([l.float() for l in losses]).sum().cpu())
 
     def sync():
         if not cpu:
@@ -270,14 +293,14 @@ def run_native(args) -> int:
         sync()
         if cpu:
             t0 = time.perf_counter()
-            for _ in range(args.steps):
-                one_step(e2e)
+            for i in range(args.steps):
+                one_step(e2e, last=(i == args.steps - 1))
             ms = (time.perf_counter() - t0) * 1e3 / args.steps
         else:
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            for _ in range(args.steps):
-                one_step(e2e)
+            for i in range(args.steps):
+                one_step(e2e, last=(i == args.steps - 1))
             e.record()
             sync()
             ms = s.elapsed_time(e) / args.steps
@@ -295,6 +318,10 @@ def run_native(args) -> int:
     l0 = _lib.launch_count()
     ms = timed(False)
     launches = _lib.launch_count() - l0
+    # the end-to-end path has first-use costs of its own (copy stream, staging buffers of the
+    # allocator): warm it up as well
+    for _ in range(min(max(args.warmup, 1), 2)):
+        one_step(True, last=True)
     ms_e2e = timed(True)
     clocks = sampler.stop() if (state.is_main_process and not cpu) else None
     if not cpu:
