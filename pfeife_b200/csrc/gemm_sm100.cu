@@ -191,6 +191,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = num_m * num_n * split_k;        // work items: (tile, k-slice)
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   const int num_mn = num_m * num_n;
+  // Work items are dealt to the CTAs (pairs) in rounds, every other round in reverse order.
+  // Items are ordered with the cheap ones last (the tiles of a narrow last column of tiles),
+  // so the CTAs that got an expensive item late in one round get a cheap one in the next.
+  const int n_workers = tile_step;
+  auto item_of = [&](int round) -> int {
+    const int slot = (round & 1) ? (n_workers - 1 - first_tile) : first_tile;
+    return round * n_workers + slot;
+  };
+  // pair tiles in the last column of tiles run a narrower MMA when at most half of their
+  // columns exist: each CTA then supplies 64 rows of B instead of 128
+  const int edge_cols = p.N - (num_n - 1) * BNT;
+  const bool narrow_edge = PAIR && BNT == 256 && edge_cols <= 128;
   // with a fused all-gather the tiles whose rows of B this rank owns are computed first, while
   // the remote rows are still arriving
   const int own0 = (GATHER && p.gather_rank > 0) ? p.gather_row_end[p.gather_rank - 1] : 0;
@@ -235,14 +247,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       bool all_gathered = false;
       // pair: both CTAs' loads of a stage are counted on the leader's barrier
-      for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+      for (int round = 0, item = item_of(0); item < num_tiles && ok; item = item_of(++round)) {
         const int tile = item % num_mn, ks = item / num_mn;
         const int kb_begin = (int)((long long)num_kb * ks / split_k);
         const int kb_end = (int)((long long)num_kb * (ks + 1) / split_k);
         const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
         const int nt = (tile / num_m + n_rot) % num_n;
         const int n0 = nt * BNT;
-        const int nb0 = n0 + int(cta_rank) * BN;     // first row of B this CTA loads
+        // first row of B this CTA loads: its half of the columns the MMA computes
+        const int nb0 = n0 + int(cta_rank) * ((narrow_edge && nt == num_n - 1) ? BN / 2 : BN);
         if (GATHER && p.gather_world > 1 && !all_gathered) {
           // rows of this B tile that other ranks own must have landed in the local buffer
           const int n1 = min(p.N, n0 + BNT);
@@ -356,10 +369,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+      const uint32_t idesc_narrow = make_idesc_f16(BMT, BNT / 2, p.fmt, p.a_mn, p.b_mn);
+      for (int round = 0, item = item_of(0); item < num_tiles && ok; item = item_of(++round)) {
         const int ks = item / num_mn;
         const int kb_begin = (int)((long long)num_kb * ks / split_k);
         const int kb_end = (int)((long long)num_kb * (ks + 1) / split_k);
+        const bool narrow = narrow_edge && ((item % num_mn) / num_m + n_rot) % num_n == num_n - 1;
+        const uint32_t idesc_t = narrow ? idesc_narrow : idesc;
         ok = PAIR ? mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, p.status,
                                       PF_ERR_TIMEOUT_TMEM_EMPTY)
                   : mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status,
@@ -378,8 +394,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t da = make_desc_sw128(sa + k * a_adv, a_lbo, 1024);
             const uint64_t db = make_desc_sw128(sb + k * b_adv, b_lbo, 1024);
             const uint32_t acc_on = (kb != kb_begin) || (k != 0);
-            if (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc, acc_on);
-            else tc_mma_f16(d_tmem, da, db, idesc, acc_on);
+            if (PAIR) tc_mma_f16_pair(d_tmem, da, db, idesc_t, acc_on);
+            else tc_mma_f16(d_tmem, da, db, idesc_t, acc_on);
           }
           // smem slot reusable (in both CTAs of a pair) once these MMAs retire
           if (PAIR) tc_commit_pair(&empty_bar[stage], 3);
@@ -457,7 +473,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool tma_out = p.tma_store != 0;
     const bool bias_vec = p.bias && p.bias_dtype == PF_F32 &&
                           (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
-    for (int item = first_tile; item < num_tiles && ok; item += tile_step) {
+    for (int round = 0, item = item_of(0); item < num_tiles && ok; item = item_of(++round)) {
       const int tile = item % num_mn;
       const int m0 = (tile % num_m) * BMT + int(cta_rank) * GEMM_BM;
       const int n0 = ((tile / num_m + n_rot) % num_n) * BNT;
@@ -763,13 +779,27 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     if (tile_n & 2048) {
       pair = true;
     } else if (tn == 0 && M > 128 && N > 128) {
-      // waves of 256 x 256 pair tiles over sm_count / 2 pairs against waves of 128 x 256 tiles
-      // over sm_count CTAs; a pair tile costs each SM about 0.8 of a single tile
-      const long long t2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+      // 256 x 256 pair tiles dealt in alternating order over sm_count / 2 pairs (the kernel's
+      // own order; a tile of a last column with at most 128 columns costs 0.55) against waves
+      // of 128 x 256 tiles over sm_count CTAs; a pair tile costs each SM about 0.8 of a single
+      // tile
+      const int P = sm_count / 2;
+      const int m2 = (M + 255) / 256, n2 = (N + 255) / 256;
+      const bool narrow = N - (n2 - 1) * 256 <= 128;
+      const long long full = (long long)m2 * (narrow ? n2 - 1 : n2), total = (long long)m2 * n2;
+      double worst = 0.0;
+      for (int w = 0; w < P; ++w) {
+        double load = 0.0;
+        for (long long round = 0;; ++round) {
+          const long long item = round * P + ((round & 1) ? (P - 1 - w) : w);
+          if (item >= total) break;
+          load += item < full ? 1.0 : 0.55;
+        }
+        if (load > worst) worst = load;
+      }
       const long long t1 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-      const long long w2 = (t2 + sm_count / 2 - 1) / (sm_count / 2);
       const long long w1 = (t1 + sm_count - 1) / sm_count;
-      pair = 4 * w2 <= 5 * w1;
+      pair = 0.8 * worst <= (double)w1 + 1e-9;
     }
   }
   int bn_auto = N <= 128 ? 128 : 256;
