@@ -779,27 +779,16 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
     if (tile_n & 2048) {
       pair = true;
     } else if (tn == 0 && M > 128 && N > 128) {
-      // 256 x 256 pair tiles dealt in alternating order over sm_count / 2 pairs (the kernel's
-      // own order; a tile of a last column with at most 128 columns costs 0.55) against waves
-      // of 128 x 256 tiles over sm_count CTAs; a pair tile costs each SM about 0.8 of a single
-      // tile
-      const int P = sm_count / 2;
-      const int m2 = (M + 255) / 256, n2 = (N + 255) / 256;
-      const bool narrow = N - (n2 - 1) * 256 <= 128;
-      const long long full = (long long)m2 * (narrow ? n2 - 1 : n2), total = (long long)m2 * n2;
-      double worst = 0.0;
-      for (int w = 0; w < P; ++w) {
-        double load = 0.0;
-        for (long long round = 0;; ++round) {
-          const long long item = round * P + ((round & 1) ? (P - 1 - w) : w);
-          if (item >= total) break;
-          load += item < full ? 1.0 : 0.55;
-        }
-        if (load > worst) worst = load;
-      }
+      // rounds of 256 x 256 pair tiles over sm_count / 2 pairs against rounds of 128 x 256 tiles
+      // over sm_count CTAs.  Measured on B200, a pair tile costs each SM 0.9-0.95 of a single
+      // tile when both fill their rounds, but more than a single tile on long-K shapes with a
+      // narrow last column of tiles (N = 1408, K = 6144: 126 us against 107 us), so pairs are
+      // taken only when 0.93 of their rounds is no more than the single-CTA rounds.
+      const long long t2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
       const long long t1 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+      const long long w2 = (t2 + sm_count / 2 - 1) / (sm_count / 2);
       const long long w1 = (t1 + sm_count - 1) / sm_count;
-      pair = 0.8 * worst <= (double)w1 + 1e-9;
+      pair = 93 * w2 <= 100 * w1;
     }
   }
   int bn_auto = N <= 128 ? 128 : 256;
