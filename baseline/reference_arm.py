@@ -27,6 +27,25 @@ def unavailable(reason: str) -> int:
     return 0
 
 
+def _start_watchdog(rank: int) -> None:
+    """The reference profiles every graph node before its first step, which at full size can
+    take tens of minutes; past the limit (PFEIFE_REF_TIMEOUT seconds, default 1500) every rank
+    leaves and rank 0 reports the arm as unavailable instead of running into the caller's own
+    time limit without a line."""
+    import threading
+    limit = float(os.environ.get("PFEIFE_REF_TIMEOUT", "1500"))
+
+    def fire():
+        if rank == 0:
+            unavailable(f"the reference did not finish profiling and {limit:.0f} s of steps "
+                        f"(its node-by-node profiling pass dominates)")
+        os._exit(0)
+
+    t = threading.Timer(limit + (0.0 if rank == 0 else 5.0), fire)
+    t.daemon = True
+    t.start()
+
+
 def run(args) -> int:
     ref_root = os.path.join(HERE, "_ref")
     if not os.path.isdir(os.path.join(ref_root, "pfeife")):
@@ -50,6 +69,7 @@ def run(args) -> int:
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    _start_watchdog(rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "24446")
     os.environ.setdefault("LOCAL_RANK", str(rank))
