@@ -348,7 +348,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 norm_bwd_param_kernel(const T* __restrict__ dy, const T* __restrict__ h,
                       const float* __restrict__ mean, const float* __restrict__ rstd,
-                      float* __restrict__ scratch, long long rows, int N, int rows_per_cta,
+                      float* __restrict__ scratch, float* __restrict__ acc_gamma,
+                      float* __restrict__ acc_beta, long long rows, int N, int rows_per_cta,
                       int rms) {
   __shared__ float red[2][8][256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -383,9 +384,16 @@ norm_bwd_param_kernel(const T* __restrict__ dy, const T* __restrict__ h,
     float g = 0.f, b = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) { g += red[0][w][threadIdx.x]; b += red[1][w][threadIdx.x]; }
-    // partial sums of this row slab: scratch[slab][0][c] (dgamma), scratch[slab][1][c] (dbeta)
-    scratch[((long long)blockIdx.y * 2) * N + c] = g;
-    scratch[((long long)blockIdx.y * 2 + 1) * N + c] = b;
+    if (acc_gamma) {
+      // accumulating into existing gradients (the framework's gradient bucket): add this row
+      // slab's sums directly, no folding pass
+      atomicAdd(acc_gamma + c, g);
+      if (acc_beta) atomicAdd(acc_beta + c, b);
+    } else {
+      // partial sums of this row slab: scratch[slab][0][c] (dgamma), scratch[slab][1][c] (dbeta)
+      scratch[((long long)blockIdx.y * 2) * N + c] = g;
+      scratch[((long long)blockIdx.y * 2 + 1) * N + c] = b;
+    }
   }
 }
 
@@ -544,7 +552,8 @@ static int norm_fwd_launch(const void* x, const void* res, const float* gamma, c
 template <typename T>
 static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, const float* mean,
                            const float* rstd, const void* dres, void* dx, float* scratch, int& G,
-                           long long rows, int N, int rms, cudaStream_t st) {
+                           long long rows, int N, int rms, cudaStream_t st,
+                           float* acc_gamma = nullptr, float* acc_beta = nullptr) {
   constexpr int V = 16 / sizeof(T);
   if (N % V) return -2;
   const int nvec = N / V;
@@ -569,8 +578,9 @@ static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, co
     const int rows_per = (int)((rows + slabs - 1) / slabs);
     slabs = (int)((rows + rows_per - 1) / rows_per);
     norm_bwd_param_kernel<T><<<dim3((N + 255) / 256, slabs), 256, 0, st>>>(
-        (const T*)dy, (const T*)h, mean, rstd, scratch, rows, N, rows_per, rms);
-    G = slabs;
+        (const T*)dy, (const T*)h, mean, rstd, scratch, acc_gamma, acc_beta, rows, N, rows_per,
+        rms);
+    G = acc_gamma ? 0 : slabs;      // 0: the sums are already where they belong
     return 0;
   }
   if (nvec <= 128 * NORM_MAX_VEC)
@@ -623,17 +633,23 @@ PF_API int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const v
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int G = pf_norm_bwd_ctas(rows, sm_count);   // rows of scratch; the launch may use fewer
+  // when the sums are added to existing gradients the row slabs add them directly (G comes
+  // back 0) instead of leaving partial sums for the folding kernel
+  float* ag = accumulate ? (float*)dgamma : nullptr;
+  float* ab = accumulate ? (float*)dbeta : nullptr;
   int r = -1;
   switch (dtype) {
-    case PF_F32: r = norm_bwd_launch<float>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
-    case PF_F16: r = norm_bwd_launch<__half>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
-    case PF_BF16: r = norm_bwd_launch<__nv_bfloat16>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st); break;
+    case PF_F32: r = norm_bwd_launch<float>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st, ag, ab); break;
+    case PF_F16: r = norm_bwd_launch<__half>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st, ag, ab); break;
+    case PF_BF16: r = norm_bwd_launch<__nv_bfloat16>(dy, h, (const float*)gamma, (const float*)mean, (const float*)rstd, dres, dx, (float*)scratch, G, rows, N, rms, st, ag, ab); break;
   }
   if (r) return r;
   PF_CHECK_LAUNCH();
-  norm_bwd_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>((const float*)scratch, (float*)dgamma,
-                                                          (float*)dbeta, G, N, accumulate);
-  PF_CHECK_LAUNCH();
+  if (G > 0) {
+    norm_bwd_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>((const float*)scratch, (float*)dgamma,
+                                                            (float*)dbeta, G, N, accumulate);
+    PF_CHECK_LAUNCH();
+  }
   return 0;
 }
 

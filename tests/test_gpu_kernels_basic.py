@@ -48,6 +48,29 @@ def test_norm_fwd_bwd(dtype, rows, N, rms):
         assert torch.allclose(db, bf.grad, atol=rows ** 0.5 * 8 * t, rtol=4 * t)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_bwd_adds_into_existing_gradients(rms):
+    """accumulate=True: the weight / bias gradients are added to what the buffers already hold
+    (the framework's gradient bucket), two calls in a row."""
+    from pfeife_b200.ops import kernels as kx
+    rows, N, dtype = 3000, 1408, torch.bfloat16
+    x = _t(rows, N, dtype=dtype)
+    gamma = torch.randn(N, device="cuda") * 0.5 + 1.0
+    beta = None if rms else torch.zeros(N, device="cuda")
+    dy = _t(rows, N, dtype=dtype, seed=2)
+    y, h, mean, rstd = kx.norm_fwd(x, gamma, beta, 1e-5, rms)
+    _, dg_ref, db_ref = kx.norm_bwd(dy, x, gamma, mean, rstd, rms)
+    dg = torch.full((N,), 2.0, device="cuda")
+    db = None if rms else torch.full((N,), -1.0, device="cuda")
+    for _ in range(2):
+        kx.norm_bwd(dy, x, gamma, mean, rstd, rms, dgamma=dg, dbeta=db, accumulate=True,
+                    want_dbeta=not rms)
+    torch.cuda.synchronize()
+    assert torch.allclose(dg, 2.0 + 2.0 * dg_ref, atol=0.05, rtol=1e-3)
+    if not rms:
+        assert torch.allclose(db, -1.0 + 2.0 * db_ref, atol=0.05, rtol=1e-3)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_elementwise_family(dtype):
     from pfeife_b200.ops import kernels as kx
