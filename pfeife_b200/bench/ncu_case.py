@@ -1,7 +1,7 @@
 """Small single-kernel workloads for Nsight Compute captures (a few launches, inputs larger than
 L2, a few hundred MB on the device at most).
 
-    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_wgrad,attn,norm,adamw,ce,unet,llama}
+    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_plain_pair,gemm_wgrad,attn,norm,adamw,ce,unet,llama}
 
 Each case launches its kernel(s) a handful of times and checks the kernel status word, so the
 same command can first be run plainly (must exit 0) and then under
@@ -30,13 +30,15 @@ def main(argv=None) -> int:
         aux = torch.empty_like(out)
         for _ in range(reps):
             kx.gemm(a, b, out=out, bias=bias, aux=aux, epilogue=kx.EPI_GELU)
-    elif which in ("gemm_plain", "gemm_plain_single"):   # same shape, no epilogue work
+    elif which in ("gemm_plain", "gemm_plain_single", "gemm_plain_pair"):
+        # same shape, no epilogue work; tile form chosen by the library, or forced
         M, N, K = 6168, 6144, 1408
         a = torch.randn(M, K, device=dev).to(torch.float16)
         b = torch.randn(N, K, device=dev).to(torch.float16) * 0.02
         out = torch.empty(M, N, device=dev, dtype=torch.float16)
+        form = 4096 if which.endswith("single") else 2048 if which.endswith("pair") else 0
         for _ in range(reps):
-            kx.gemm(a, b, out=out, tile_n=4096 if which.endswith("single") else 0)
+            kx.gemm(a, b, out=out, tile_n=form)
     elif which == "gemm_wgrad":   # both operands MN-major, fp32 accumulate into the bucket
         M, N, K = 6144, 1408, 6168
         a = torch.randn(K, M, device=dev).to(torch.float16)
