@@ -252,6 +252,8 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
             w2 = _weight_as(w, cd)
             if N % 8 == 0 and K % 8 == 0:
                 dx = kx.gemm(dy2, w2, b_mn=True).view(x.shape[:-1] + (K,))
+            elif N % 8 == 0:
+                dx = kx.gemm(dy2, _pad_k(w2), b_mn=True)[:, :K].reshape(x.shape[:-1] + (K,))
             else:
                 dx = (dy2 @ w2).view(x.shape[:-1] + (K,))
         if need_dw:
@@ -262,6 +264,11 @@ def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, aux: Tensor, act: int, need_dx:
                         accumulate=True)
             elif ok:
                 dw = kx.gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
+            elif N % 8 == 0:
+                # input width not a multiple of 8 (ViT patch embedding: 3 * 14 * 14 = 588):
+                # the same tensor-core GEMM on zero-padded columns, padding sliced off
+                dw = kx.gemm(dy2, _pad_k(x2), a_mn=True, b_mn=True,
+                             out_dtype=torch.float32)[:, :K].contiguous()
             else:
                 dw = dy2.float().t() @ x2.float()
             if dw.numel() and w.dtype != torch.float32:

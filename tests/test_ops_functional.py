@@ -53,6 +53,25 @@ def test_linear(device, act):
 
 
 @pytest.mark.parametrize("device", DEVICES)
+def test_linear_with_an_input_width_that_is_not_a_multiple_of_8(device):
+    """ViT patch embedding: 3 * 14 * 14 = 588 input features (padded to 592 inside the GEMMs)."""
+    dtype, tol = _cfg(device)
+    x = _rand(2, 30, 588, device=device, dtype=dtype, scale=0.5)
+    w = _rand(64, 588, device=device, dtype=dtype, seed=1, scale=0.1)
+    b = _rand(64, device=device, dtype=torch.float32, seed=2)
+    y = ops.linear(x, w, b)
+    gy = _rand(2, 30, 64, device=device, dtype=dtype, seed=5, grad=False)
+    y.backward(gy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.linear(xr, wr, br)
+    yr.backward(gy.float())
+    _check(y, yr, tol)
+    _check(x.grad, xr.grad, tol * 2)
+    _check(w.grad, wr.grad, tol * 4)
+    _check(b.grad, br.grad, tol * 4)
+
+
+@pytest.mark.parametrize("device", DEVICES)
 def test_mlp(device):
     dtype, tol = _cfg(device)
     x = _rand(2, 50, 64, device=device, dtype=dtype, scale=0.5)
