@@ -199,10 +199,12 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* 
   }
 }
 
-// Forward for rows of up to 2048 16-bit elements: one warp per row, the row in registers,
-// shuffle reductions only (no CTA barrier), 8 rows per CTA.
+// Forward for rows of up to 2048 16-bit elements: one warp per row, shuffle reductions only (no
+// CTA barrier), 8 rows per CTA.  The row stays in registers in its packed 16-bit form and is
+// expanded once per pass (sum, squared deviations, output): a third of the registers of an fp32
+// copy, which lets enough CTAs share an SM to keep the loads of a whole wave in flight.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res,
                      const float* __restrict__ gamma, const float* __restrict__ beta,
                      T* __restrict__ y, T* __restrict__ h_out, float* __restrict__ mean_out,
@@ -212,31 +214,33 @@ norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res,
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
-  float v[NV][V];
-  float s = 0.f;
+  uint4 q[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int idx = lane + i * 32;
-    if (idx < nvec) {
-      uint4 q = reinterpret_cast<const uint4*>(x + row * N)[idx];
-      const T* e = reinterpret_cast<const T*>(&q);
-      if (res) {
-        uint4 qr = reinterpret_cast<const uint4*>(res + row * N)[idx];
+    if (idx < nvec) q[i] = reinterpret_cast<const uint4*>(x + row * N)[idx];
+  }
+  if (res) {      // h = x + residual, rounded to the storage type like the unfused sequence
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        const uint4 qr = reinterpret_cast<const uint4*>(res + row * N)[idx];
         const T* er = reinterpret_cast<const T*>(&qr);
-        uint4 qh;
-        T* eh = reinterpret_cast<T*>(&qh);
+        T* e = reinterpret_cast<T*>(&q[i]);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          eh[j] = from_f32<T>(to_f32<T>(e[j]) + to_f32<T>(er[j]));
-          v[i][j] = to_f32<T>(eh[j]);
-        }
-        if (h_out) reinterpret_cast<uint4*>(h_out + row * N)[idx] = qh;
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j) v[i][j] = to_f32<T>(e[j]);
+        for (int j = 0; j < V; ++j) e[j] = from_f32<T>(to_f32<T>(e[j]) + to_f32<T>(er[j]));
+        if (h_out) reinterpret_cast<uint4*>(h_out + row * N)[idx] = q[i];
       }
+    }
+  }
+  float s = 0.f;
 #pragma unroll
-      for (int j = 0; j < V; ++j) s += v[i][j];
+  for (int i = 0; i < NV; ++i) {
+    if (lane + i * 32 < nvec) {
+      const T* e = reinterpret_cast<const T*>(&q[i]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += to_f32<T>(e[j]);
     }
   }
   const float mean = rms ? 0.f : warp_sum(s) / N;
@@ -244,8 +248,9 @@ norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res,
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (lane + i * 32 < nvec) {
+      const T* e = reinterpret_cast<const T*>(&q[i]);
 #pragma unroll
-      for (int j = 0; j < V; ++j) { const float d = v[i][j] - mean; sq += d * d; }
+      for (int j = 0; j < V; ++j) { const float d = to_f32<T>(e[j]) - mean; sq = fmaf(d, d, sq); }
     }
   }
   const float rstd = rsqrtf(warp_sum(sq) / N + eps);
@@ -267,11 +272,13 @@ norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res,
         b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
         b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
       }
-      uint4 q;
-      T* e = reinterpret_cast<T*>(&q);
+      const T* ei = reinterpret_cast<const T*>(&q[i]);
+      uint4 o;
+      T* e = reinterpret_cast<T*>(&o);
 #pragma unroll
-      for (int j = 0; j < V; ++j) e[j] = from_f32<T>((v[i][j] - mean) * rstd * g[j] + b[j]);
-      reinterpret_cast<uint4*>(y + row * N)[idx] = q;
+      for (int j = 0; j < V; ++j)
+        e[j] = from_f32<T>((to_f32<T>(ei[j]) - mean) * rstd * g[j] + b[j]);
+      reinterpret_cast<uint4*>(y + row * N)[idx] = o;
     }
   }
 }
