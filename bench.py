@@ -200,13 +200,12 @@ def _planned_mesh(args, wl, world, rank, cpu):
 def run_native(args) -> int:
     import torch
     import torch.distributed as dist
-    import torch.nn.functional as F
 
     from pfeife_b200 import PartialRunner, PipeOption, initialize_pfeife, partial_compiler
     from pfeife_b200.bench.workloads import get_workload
     from pfeife_b200.ops import _lib
     from pfeife_b200.runtime.partial import worker_loop
-    from pfeife_b200.utils import get_logger, set_logger_level
+    from pfeife_b200.utils import set_logger_level
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -7,7 +7,7 @@ A workload only describes; ``bench.py`` drives it through the public API.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, Optional, Tuple
 
 import torch
 

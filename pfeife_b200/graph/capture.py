@@ -12,8 +12,8 @@ nodes).
 from __future__ import annotations
 
 import re
-from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Any, List, Optional, Sequence
 
 import torch
 import torch.fx as fx

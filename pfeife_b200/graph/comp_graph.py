@@ -19,12 +19,12 @@ from __future__ import annotations
 import operator
 import pickle
 from dataclasses import dataclass, field
-from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Set, Tuple
 
 import torch
 import torch.fx as fx
 
-from .capture import CapturedGraph, GraphInput
+from .capture import CapturedGraph
 
 GRAPH_FETCH_MEM_CAP = 0.6
 WEIGHT_MULTIPLIER = 4  # weights + gradients + two optimizer moments

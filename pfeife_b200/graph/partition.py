@@ -21,7 +21,6 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 import torch.fx as fx
 
-from .capture import CapturedGraph, GraphInput
 from .comp_graph import CompGraph, ShapeMeta, _tensor_leaves
 
 OUTSIDE = -1  # producer id of user inputs, consumer id of model outputs

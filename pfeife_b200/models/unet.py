@@ -13,7 +13,7 @@ LayerNorm, cross-attention over the 77x2048 text states, LayerNorm, GEGLU feed-f
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Tuple
 
 import torch

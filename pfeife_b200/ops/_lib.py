@@ -8,7 +8,6 @@ implementations, which is what the CPU/gloo tests run.
 from __future__ import annotations
 
 import ctypes
-import os
 import threading
 from pathlib import Path
 from typing import Optional

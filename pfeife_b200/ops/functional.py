@@ -19,13 +19,12 @@ from __future__ import annotations
 import math
 import threading
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from . import _lib
 from . import kernels as kx
 
 ACT_NONE, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3

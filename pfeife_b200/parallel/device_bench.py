@@ -18,7 +18,7 @@ from __future__ import annotations
 import os
 import pickle
 import time
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch

@@ -12,7 +12,6 @@ even if the user's script seeded them differently.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -18,7 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
-from .schedule import PipeSchedParams, Work
+from .schedule import PipeSchedParams
 
 RESERVE_MEM_RATIO = 0.85
 

@@ -19,7 +19,6 @@ host library is built; the Python simulation in pipe_graph.py is the oracle.
 """
 from __future__ import annotations
 
-import ctypes
 import itertools
 import math
 import random
@@ -29,7 +28,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 from ..graph.comp_graph import CompGraph
 from ..utils import fmem, get_logger
-from .device_bench import MB, DeviceBench
+from .device_bench import DeviceBench
 from .pipe_graph import RESERVE_MEM_RATIO, PipeEdge, PipeGraph, PipeNode, Simulation
 from .schedule import PipeSchedParams, PipeSchedSet
 

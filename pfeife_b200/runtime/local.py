@@ -12,13 +12,11 @@ from __future__ import annotations
 
 import queue
 import threading
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Tuple
 
 import torch
 
-from ..option import PipeOption
 from ..parallel.device_bench import DeviceBench
-from ..utils import get_logger
 from .partial import PartialRunner
 from .transport import LocalTransport, _LocalHub
 from .worker import LoopFlag, StageWorker

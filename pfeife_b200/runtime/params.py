@@ -17,7 +17,7 @@ pfeife/mp/worker.py:265-275).  Adam, AdamW and SGD run on the native kernels; an
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch

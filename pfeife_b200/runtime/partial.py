@@ -24,11 +24,8 @@ from __future__ import annotations
 import atexit
 import copy
 import os
-import pickle
 import queue
-import tempfile
 import threading
-import uuid
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -36,7 +33,7 @@ import torch.distributed as dist
 
 from ..graph.capture import CapturedGraph, classify_inputs
 from ..graph.comp_graph import CompGraph
-from ..graph.partition import OUTSIDE, PartitionGraph, partition_module
+from ..graph.partition import PartitionGraph, partition_module
 from ..graph.profiler import gen_comp_graph_cpu, gen_local_comp_graph
 from ..option import PipeOption
 from ..parallel.device_bench import DeviceBench, NCCLDeviceBench

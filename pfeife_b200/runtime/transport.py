@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import queue
 import threading
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

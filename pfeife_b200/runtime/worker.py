@@ -21,14 +21,11 @@ from __future__ import annotations
 
 import contextlib
 import enum
-import queue
 import threading
-import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
-import torch.distributed as dist
 
 from ..graph.partition import OUTSIDE, PartitionGraph, StageSpec
 from ..graph.profiler import gen_amp_context
