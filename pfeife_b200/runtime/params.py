@@ -118,6 +118,7 @@ class RankParams:
         self.opt_state: Dict[str, torch.Tensor] = {}
         self.found_inf = torch.zeros(1, dtype=torch.float32, device=device)
         self._torch_opt = None
+        self._pending_opt_state = None
 
         with torch.no_grad():
             for s in self.slots.values():
@@ -252,6 +253,9 @@ class RankParams:
                                                   "differentiable")}
                 pg.append({"params": groups[g], **h})
             self._torch_opt = cls(pg)
+            if self._pending_opt_state is not None:     # a checkpoint loaded before the first step
+                self._apply_torch_state(self._pending_opt_state)
+                self._pending_opt_state = None
         for i, g in enumerate(self._torch_opt.param_groups):
             h = self.hyper[min(i, len(self.hyper) - 1)]
             for k in _HYPER_KEYS:
@@ -283,13 +287,47 @@ class RankParams:
         """qualified name -> {state name -> tensor}, keyed like torch's per-parameter state."""
         out: Dict[str, Dict[str, torch.Tensor]] = {}
         for s in self.packed_slots():
-            st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
-                  for k, v in self.opt_state.items()}
+            if self._torch_opt is not None:
+                # reference path: the torch optimizer owns the per-parameter state
+                src = self._torch_opt.state.get(getattr(s, "_opt_param", None), {})
+                st = {k: v.detach().clone().view(s.entry.tensor.shape)
+                      for k, v in src.items() if torch.is_tensor(v) and v.numel() == s.numel
+                      and k != "step"}
+            else:
+                st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
+                      for k, v in self.opt_state.items()}
             st["step"] = torch.tensor(float(self.step_count))
             out[s.entry.qualname] = st
         return out
 
+    def _uses_torch_optimizer(self) -> bool:
+        return not (self.optimizer_type in ("adam", "adamw", "sgd") and self.native)
+
+    def _apply_torch_state(self, state: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        for s in self.packed_slots():
+            st = state.get(s.entry.qualname)
+            p = getattr(s, "_opt_param", None)
+            if not st or p is None:
+                continue
+            dst = self._torch_opt.state[p]
+            for k, v in st.items():
+                if k == "step":
+                    continue
+                dst[k] = v.detach().to(device=p.device, dtype=p.dtype).reshape(p.shape).clone()
+            if "exp_avg" in st:     # Adam family: its own step counter drives the bias correction
+                dst["step"] = torch.tensor(float(st.get("step", self.step_count)))
+
     def load_optimizer_state(self, state: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        if self._uses_torch_optimizer():
+            for st in state.values():
+                if st and "step" in st:
+                    self.step_count = int(float(st["step"]))
+                    break
+            if self._torch_opt is not None:
+                self._apply_torch_state(state)
+            else:
+                self._pending_opt_state = state
+            return
         for s in self.packed_slots():
             st = state.get(s.entry.qualname)
             if not st:

@@ -75,10 +75,20 @@ def main():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--check_eval", action="store_true")
     ap.add_argument("--resume_check", action="store_true")
+    ap.add_argument("--fail_rank", type=int, default=-1,
+                    help="this global rank raises an exception on the host before its first step "
+                         "(failure-detection test; no device work is in flight)")
     PipeOption.add_arguments(ap)
     args = ap.parse_args()
 
     state = initialize_pfeife()
+    if args.fail_rank == state.rank:
+        raise RuntimeError(f"injected host-side failure on rank {state.rank}")
+    if not state.is_main_rank:
+        # only under ``mp_launch.py --all_main`` (the launcher runs worker ranks itself otherwise)
+        from pfeife_b200.runtime.partial import worker_loop
+        worker_loop()
+        return
     option = PipeOption.from_args(args)
     set_seed(0)
     model, make_batch, loss_fn = build(args.model)
@@ -129,6 +139,20 @@ def main():
             want = model.cpu()(x)
         result["eval_diff"] = float((torch.cat(got) - want).abs().max())
         model.to(dev)
+    if args.resume_check:
+        # checkpoint, train two more steps, restore the checkpoint, repeat the same two steps:
+        # parameters, optimizer moments and step count all have to come back
+        saved_opt = runner.gather_params(with_optimizer=True)
+        saved = {k: v.detach().clone() for k, v in model.state_dict().items()}
+        g2 = torch.Generator().manual_seed(777 + state.dp_rank)
+        batches = [make_batch(n, g2) for _ in range(2)]
+
+        def two_steps():
+            return [[float(l) for l in runner.step(*[t.to(dev) for t in b])] for b in batches]
+
+        result["resume_first"] = two_steps()
+        runner.load_params(saved, saved_opt)
+        result["resume_second"] = two_steps()
     opt_state = runner.gather_params(with_optimizer=True)
     diff = 0.0
     if state.dp_size == 1:

@@ -85,3 +85,41 @@ def test_unet_long_skip_edges_and_many_inputs(tmp_path):
     res, _ = launch(tmp_path, 2, ["--model", "unet_tiny", "--device_cnt", "2", "--batch_size", "2",
                                   "--batch_cnt", "4", "--steps", "2"])
     assert_equal_training(res, tol=1e-5)
+
+
+def test_checkpoint_resume_repeats_the_same_steps(tmp_path):
+    """gather_params(with_optimizer=True) -> load_params restores parameters, Adam moments and
+    the step count on every rank: the two steps after the checkpoint give the same losses when
+    they are repeated after the restore."""
+    res, _ = launch(tmp_path, 2, ["--model", "mlp", "--device_cnt", "2", "--batch_size", "4",
+                                  "--batch_cnt", "2", "--steps", "2", "--optimizer", "adam",
+                                  "--lr", "0.01", "--resume_check"])
+    assert len(res["resume_first"]) == 2
+    for a, b in zip(res["resume_first"], res["resume_second"]):
+        assert a == pytest.approx(b, abs=1e-6, rel=1e-6)
+    # and training did move between the two steps (the check is not vacuous)
+    assert res["resume_first"][0] != pytest.approx(res["resume_first"][1], abs=1e-9)
+
+
+@pytest.mark.parametrize("fail_rank", [0, 1])
+def test_a_rank_that_raises_takes_the_job_down(tmp_path, fail_rank):
+    """Failure detection on the host: one rank raises before its first step; the launcher notices
+    the dead child, ends the others and reports a non-zero exit instead of hanging."""
+    import time
+    out = str(tmp_path / "result.json")
+    _port[0] += 1
+    # --all_main: every rank runs the script, so the failing rank can be a pipeline worker
+    # (rank 0) as well as the pipeline's main rank (rank 1)
+    cmd = [sys.executable, os.path.join(ROOT, "mp_launch.py"), "--cpu", "--world_size", "2",
+           "--all_main", "--master_port", str(_port[0]),
+           os.path.join(ROOT, "tests", "scripts", "train_check.py"), "--cpu",
+           "--no_bench_optimizer", "--ctrl_timeout", "30", "--out", out, "--model", "mlp",
+           "--device_cnt", "2", "--batch_size", "4", "--batch_cnt", "2", "--steps", "2",
+           "--fail_rank", str(fail_rank)]
+    t0 = time.time()
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=240, cwd=ROOT)
+    assert r.returncode != 0
+    assert "injected host-side failure" in r.stdout
+    assert time.time() - t0 < 200
+    assert not os.path.exists(out)
