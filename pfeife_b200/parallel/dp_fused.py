@@ -175,6 +175,7 @@ class FusedDP(NcclDP):
         ln = max(self.shard[1] - self.shard[0], 4)
         self.m = torch.zeros(ln, dtype=torch.float32, device=self.device)
         self.v = torch.zeros(ln, dtype=torch.float32, device=self.device)
+        params.dp_state = self      # checkpoints read / restore the sharded moments through us
         self.flags = torch.zeros(2 * DP_MAX, dtype=torch.int32, device=self.device)
         self.local_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
@@ -236,3 +237,12 @@ class FusedDP(NcclDP):
             dist.all_reduce(full, group=self.group)
             out[name] = full
         return out
+
+    def load_optimizer_state(self, flats: Dict[str, torch.Tensor]) -> None:
+        """Inverse of ``gather_optimizer_state``: keeps this rank's shard of full-length moments
+        (resume from a checkpoint)."""
+        lo, hi = self.shard
+        for name, local in (("exp_avg", self.m), ("exp_avg_sq", self.v)):
+            full = flats.get(name)
+            if full is not None and hi > lo:
+                local[:hi - lo].copy_(full[lo:hi].to(local.device))

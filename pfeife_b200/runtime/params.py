@@ -119,6 +119,7 @@ class RankParams:
         self.found_inf = torch.zeros(1, dtype=torch.float32, device=device)
         self._torch_opt = None
         self._pending_opt_state = None
+        self.dp_state = None     # fused data-parallel layer that owns sharded optimizer moments
 
         with torch.no_grad():
             for s in self.slots.values():
@@ -286,8 +287,15 @@ class RankParams:
     def optimizer_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
         """qualified name -> {state name -> tensor}, keyed like torch's per-parameter state."""
         out: Dict[str, Dict[str, torch.Tensor]] = {}
+        # fused data parallelism keeps each moment only on the rank that owns the shard: assemble
+        # full-length copies (a collective over the replicas, which all take checkpoints together)
+        flats = self.dp_state.gather_optimizer_state() \
+            if (self.dp_state is not None and getattr(self.dp_state, "fused", False)) else None
         for s in self.packed_slots():
-            if self._torch_opt is not None:
+            if flats is not None:
+                st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
+                      for k, v in flats.items()}
+            elif self._torch_opt is not None:
                 # reference path: the torch optimizer owns the per-parameter state
                 src = self._torch_opt.state.get(getattr(s, "_opt_param", None), {})
                 st = {k: v.detach().clone().view(s.entry.tensor.shape)
@@ -318,6 +326,21 @@ class RankParams:
                 dst["step"] = torch.tensor(float(st.get("step", self.step_count)))
 
     def load_optimizer_state(self, state: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        if self.dp_state is not None and getattr(self.dp_state, "fused", False):
+            flats: Dict[str, torch.Tensor] = {}
+            for s in self.packed_slots():
+                st = state.get(s.entry.qualname)
+                if not st:
+                    continue
+                for k, v in st.items():
+                    if k == "step":
+                        self.step_count = int(float(v))
+                        continue
+                    if k not in flats:
+                        flats[k] = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+                    flats[k][s.offset:s.offset + s.numel].copy_(v.reshape(-1))
+            self.dp_state.load_optimizer_state(flats)
+            return
         if self._uses_torch_optimizer():
             for st in state.values():
                 if st and "step" in st:

@@ -70,6 +70,22 @@ def test_row_sharded_weights_match_replicated_weights(tmp_path, graphs):
         assert a == pytest.approx(b, rel=1e-3, abs=1e-3)
 
 
+def test_checkpoint_resume_under_fused_dp(tmp_path):
+    """The fused data-parallel step keeps Adam moments only on the rank that owns each shard;
+    a checkpoint assembles them and a restore hands every rank its shard back: the two steps
+    after the checkpoint repeat exactly after the restore, on both replicas."""
+    res, out = launch(tmp_path, 2, ["--model", "vit_small", "--device_cnt", "1", "--batch_size",
+                                    "4", "--batch_cnt", "2", "--steps", "2", "--optimizer",
+                                    "adamw", "--lr", "0.001", "--mixed_precision", "bf16",
+                                    "--resume_check"], dp_mesh="-2,1", tag="resume")
+    with open(out + ".dp0") as f:
+        other = json.load(f)
+    for r in (res, other):
+        for a, b in zip(r["resume_first"], r["resume_second"]):
+            assert a == pytest.approx(b, abs=1e-5, rel=1e-5)
+        assert r["resume_first"][0] != pytest.approx(r["resume_first"][1], abs=1e-9)
+
+
 def test_allgather_fused_into_gemm(tmp_path):
     out = str(tmp_path / "ag.json")
     _port[0] += 1
