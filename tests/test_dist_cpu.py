@@ -123,3 +123,22 @@ def test_a_rank_that_raises_takes_the_job_down(tmp_path, fail_rank):
     assert "injected host-side failure" in r.stdout
     assert time.time() - t0 < 200
     assert not os.path.exists(out)
+
+
+def test_manager_front_end_owns_loss_and_optimizer(tmp_path):
+    """``PipeManager(model, loss_fn, option).run(target, *inputs)`` over a 2-rank pipeline:
+    training, eval and gather_params against a plain loop."""
+    out = str(tmp_path / "mgr.json")
+    _port[0] += 1
+    cmd = [sys.executable, os.path.join(ROOT, "mp_launch.py"), "--cpu", "--world_size", "2",
+           "--master_port", str(_port[0]),
+           os.path.join(ROOT, "tests", "scripts", "manager_check.py"), "--cpu",
+           "--no_bench_optimizer", "--ctrl_timeout", "120", "--out", out, "--device_cnt", "2",
+           "--batch_size", "4", "--batch_cnt", "2"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=420, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-4000:]
+    with open(out) as f:
+        res = json.load(f)
+    assert_equal_training(res)
+    assert res["eval_diff"] <= 1e-5
