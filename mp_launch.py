@@ -57,8 +57,9 @@ def base_env(args) -> Dict[str, str]:
 
 
 def child_argv(args) -> List[str]:
-    out = [os.path.abspath(__file__), "--run_proc", "--world_size", str(args.world_size),
-           "--nnodes", str(args.nnodes), "--node_rank", str(args.node_rank)]
+    out = [os.path.abspath(__file__), "--run_proc", "--launcher", args.launcher,
+           "--world_size", str(args.world_size), "--nnodes", str(args.nnodes),
+           "--node_rank", str(args.node_rank)]
     if args.all_main:
         out.append("--all_main")
     if args.dp_mesh:
@@ -75,10 +76,11 @@ def get_python_env(args, local_rank: int) -> Dict[str, str]:
     return env
 
 
-def get_slurm_env(args) -> Dict[str, str]:
-    """Under ``srun`` every task derives its rank from SLURM's variables."""
+def get_slurm_env(args, e=None) -> Dict[str, str]:
+    """Under ``srun`` every task derives its rank from SLURM's variables (read in the task
+    itself: the launching process only has the batch step's own values)."""
     env = base_env(args)
-    e = os.environ
+    e = os.environ if e is None else e
     if "SLURM_PROCID" in e:
         env.update(RANK=e["SLURM_PROCID"], LOCAL_RANK=e.get("SLURM_LOCALID", "0"),
                    WORLD_SIZE=e.get("SLURM_NTASKS", str(args.world_size)),
@@ -98,7 +100,10 @@ def init_main(args) -> int:
                                       start_new_session=True))
     elif args.launcher == "slurm":
         cmd = ["srun", sys.executable] + child_argv(args)
-        procs.append(subprocess.Popen(cmd, env=get_slurm_env(args), start_new_session=True))
+        env = base_env(args)
+        for k in ("RANK", "LOCAL_RANK"):      # every task sets its own from SLURM_PROCID
+            env.pop(k, None)
+        procs.append(subprocess.Popen(cmd, env=env, start_new_session=True))
     else:
         for lr in range(per_node):
             procs.append(subprocess.Popen([sys.executable] + child_argv(args),
@@ -152,7 +157,7 @@ def run_worker() -> None:
 
 def run_proc(args) -> None:
     from pfeife_b200.topology import check_main_rank
-    if args.launcher == "slurm" and "SLURM_PROCID" in os.environ and "RANK" not in os.environ:
+    if args.launcher == "slurm" and "SLURM_PROCID" in os.environ:
         os.environ.update(get_slurm_env(args))
     if args.dp_mesh:
         os.environ["DP_MESH"] = args.dp_mesh
