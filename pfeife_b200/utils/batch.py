@@ -44,8 +44,10 @@ def split_args_kwargs(args: Tuple[Any, ...], kwargs: Dict[str, Any], batch_split
                       ) -> Tuple[List[Tuple[Any, ...]], List[Dict[str, Any]]]:
     """-> (list of per-micro-batch args tuples, list of per-micro-batch kwargs dicts)."""
     kwargs = kwargs or {}
-    a = shard_dict_of_args(dict(enumerate(args)), batch_split)
     k = shard_dict_of_args(kwargs, batch_split)
+    if args is None:      # as in the reference: a call without positional arguments
+        return [(None,) for _ in range(batch_split)], k
+    a = shard_dict_of_args(dict(enumerate(args)), batch_split)
     args_split = [tuple(chunk[i] for i in range(len(args))) for chunk in a]
     return args_split, k
 
