@@ -8,8 +8,10 @@ import torch.nn.functional as F
 
 
 class LossWrapper(nn.Module):
-    def forward(self, input, target, model=None):
-        raise NotImplementedError
+    """Base of the wrappers; on its own it sums the output, like the reference's base class."""
+
+    def forward(self, input, target=None, model=None):
+        return _first_tensor(input).float().sum()
 
 
 def _first_tensor(out):
@@ -32,10 +34,16 @@ class SumLoss(LossWrapper):
 
 
 class MaskedLMOutputLoss(LossWrapper):
-    """Uses the ``loss`` field a HuggingFace head already computed."""
+    """Uses the ``loss`` field a HuggingFace head already computed; a head that was given no
+    labels leaves it ``None``, and the sum of the logits stands in."""
 
     def forward(self, input, target=None, model=None):
-        return input.loss if hasattr(input, "loss") else input[0]
+        loss = getattr(input, "loss", None)
+        if loss is None and isinstance(input, dict):
+            loss = input.get("loss")
+        if loss is not None:
+            return loss
+        return _first_tensor(input).float().sum()
 
 
 class RescaleLoss(LossWrapper):
@@ -48,14 +56,22 @@ class RescaleLoss(LossWrapper):
 
 
 class NormalizeLoss(LossWrapper):
-    """Divides the wrapped loss by the number of elements of the output."""
+    """Scales the wrapped loss by the power of two that brings its magnitude into (0.5, 1]; a
+    zero loss passes through.  The reference finds the factor with ``.item()`` in two host loops
+    (doubling while below 1, halving while above 1); here the exponent is read off the value on
+    the device with ``frexp``, so the step needs no host sync and can sit inside a CUDA graph."""
 
     def __init__(self, loss_fn):
         super().__init__()
         self.loss_fn = loss_fn
 
     def forward(self, input, target, model=None):
-        return self.loss_fn(input, target, model) / max(1, _first_tensor(input).numel())
+        loss = self.loss_fn(input, target, model)
+        mant, exp = torch.frexp(loss.detach().float())
+        # |loss| = mant * 2^exp with mant in [0.5, 1): dividing by 2^exp lands in [0.5, 1); an exact
+        # power of two (mant == 0.5) ends the reference's loops at 1, one doubling further
+        exp = exp - (mant.abs() == 0.5).to(exp.dtype)
+        return loss * torch.ldexp(torch.ones_like(mant), -exp).to(loss.dtype)
 
 
 class CrossEntropyLoss(LossWrapper):
