@@ -301,6 +301,11 @@ class RankParams:
                 st = {k: v.detach().clone().view(s.entry.tensor.shape)
                       for k, v in src.items() if torch.is_tensor(v) and v.numel() == s.numel
                       and k != "step"}
+                if "step" in src:
+                    # the optimizer's own count: steps skipped on an overflow are not in it
+                    st["step"] = torch.tensor(float(src["step"]))
+                    out[s.entry.qualname] = st
+                    continue
             else:
                 st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
                       for k, v in self.opt_state.items()}
@@ -401,6 +406,18 @@ class LossScaler:
 
     def get_scale(self) -> float:
         return float(self.state[0])
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        """Scale and growth tracker, for checkpoints: a resumed fp16 run continues at the scale
+        the job had settled on instead of overflowing its way down from the initial one."""
+        st = self.state.detach().cpu()
+        return {"scale": st[0].clone(), "growth_tracker": st[1].clone()}
+
+    def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        if not self.enabled or not sd:
+            return
+        self.state[0] = float(sd["scale"])
+        self.state[1] = float(sd.get("growth_tracker", 0.0))
 
     def update(self, found_inf: torch.Tensor) -> None:
         if not self.enabled:

@@ -52,6 +52,10 @@ _current_runner: Optional["PartialRunner"] = None
 
 
 # ------------------------------------------------------------------------------ control plane
+# entry of the optimizer-state dictionary that carries the job's loss scale (not a parameter name)
+SCALER_KEY = "__loss_scaler__"
+
+
 class ControlPlane:
     """Small host-side messages between the ranks of one pipeline (gloo)."""
 
@@ -162,6 +166,7 @@ def worker_loop(option: Optional[PipeOption] = None) -> None:
             worker.params.load_named(msg["named"])
             if msg.get("opt"):
                 worker.params.load_optimizer_state(msg["opt"])
+                worker.scaler.load_state_dict(msg["opt"].get(SCALER_KEY))
         elif flag == LoopFlag.LOG_MEMORY_USAGE:
             worker.log_memory_usage()
 
@@ -345,6 +350,7 @@ class PartialRunner:
             self._threads.append(t)
         self._closed = False
         self._compiled = False
+        self._pending_load = None
         atexit.register(self.close)
 
     # ---- user API
@@ -370,6 +376,10 @@ class PartialRunner:
             for m in pipelined:
                 m._compile(self.optimizer)
             self._compiled = True
+            if self._pending_load is not None:     # a checkpoint handed over before the first step
+                named, opt = self._pending_load
+                self._pending_load = None
+                self.load_params(named, opt)
         return self._run(a_split, k_split, training=True)
 
     def eval_step(self, *args, **kwargs) -> List[Any]:
@@ -482,6 +492,8 @@ class PartialRunner:
             all_opt.update(item[1])
         all_named.update(named)
         all_opt.update(opt)
+        if with_optimizer and self.worker.scaler.enabled:
+            all_opt[SCALER_KEY] = self.worker.scaler.state_dict()   # one scale for the whole job
         with torch.no_grad():
             for m in self.modules:
                 if not m.should_pp:
@@ -494,12 +506,17 @@ class PartialRunner:
     def load_params(self, named: Dict[str, torch.Tensor],
                     opt: Optional[Dict[str, Dict[str, torch.Tensor]]] = None) -> None:
         """Resume: pushes a ``state_dict`` of the original module (and optimizer state) to the
-        ranks that own each parameter."""
+        ranks that own each parameter.  Before the first step no rank owns anything yet: the
+        checkpoint is kept and applied as soon as the stages exist, before that step computes."""
         named = {k: v.detach().cpu() for k, v in named.items()}
+        if not self._compiled:
+            self._pending_load = (named, opt)
+            return
         self.ctrl.bcast({"flag": LoopFlag.LOAD_PARAMS, "named": named, "opt": opt})
         self.worker.params.load_named(named)
         if opt:
             self.worker.params.load_optimizer_state(opt)
+            self.worker.scaler.load_state_dict(opt.get(SCALER_KEY))
 
     def log_memory_usage(self) -> None:
         self.ctrl.bcast({"flag": LoopFlag.LOG_MEMORY_USAGE})
@@ -516,3 +533,6 @@ class PartialRunner:
             pass
         for q in self._train_queues:
             q.put(None)
+        for t in self._threads:         # daemon threads, but none may outlive the runtime
+            if t is not threading.current_thread():
+                t.join(timeout=5.0)

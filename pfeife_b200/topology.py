@@ -14,6 +14,7 @@ plane (pickled objects, flags) so that nothing small ever goes through NCCL.
 """
 from __future__ import annotations
 
+import atexit
 import datetime
 import os
 from dataclasses import dataclass
@@ -192,6 +193,10 @@ class PfeifeState:
             dist.init_process_group(self.backend, rank=self.rank, world_size=self.world_size,
                                     timeout=timeout, **kwargs)
             self._owns_pg = True
+            if self.cpu:
+                # gloo's worker threads must be gone before the interpreter tears its modules
+                # down, or a rank can abort in its last moments, after all its work was done
+                atexit.register(self.destroy)
 
         # Data-plane groups.  Every rank must create every group, in the same order.
         self.pp_group = None
