@@ -15,6 +15,7 @@ graph inputs here, so nothing is cloned or re-targeted.
 from __future__ import annotations
 
 import copy
+import operator
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -155,6 +156,62 @@ def _const_of(node: fx.Node):
     return False, None
 
 
+_INPLACE_OPERATORS = {operator.iadd, operator.isub, operator.imul, operator.itruediv,
+                      operator.ifloordiv, operator.imod, operator.ipow, operator.iand,
+                      operator.ior, operator.ixor}
+_VIEW_METHODS = {"view", "reshape", "transpose", "permute", "flatten", "unflatten", "squeeze",
+                 "unsqueeze", "t", "view_as", "expand", "narrow", "select", "unbind", "chunk",
+                 "split", "contiguous", "detach", "__getitem__"}
+
+
+def _writes_in_place(n: fx.Node) -> bool:
+    """True for a node that overwrites its first argument: a method or function whose name ends
+    in one underscore (``relu_``, ``add_``), an augmented assignment, ``inplace=True``."""
+    if n.kwargs.get("inplace") is True:
+        return True
+    if n.op == "call_method":
+        return n.target.endswith("_") and not n.target.endswith("__")
+    if n.op == "call_function":
+        if n.target in _INPLACE_OPERATORS:
+            return True
+        name = getattr(n.target, "__name__", "")
+        return name.endswith("_") and not name.endswith("__")
+    return False
+
+
+def _is_view(n: fx.Node) -> bool:
+    if n.op == "call_method":
+        return n.target in _VIEW_METHODS
+    return n.op == "call_function" and n.target is operator.getitem
+
+
+def _protect_overwritten_inputs(g: fx.Graph, first_compute: Optional[fx.Node],
+                                placeholders: Sequence[fx.Node]) -> None:
+    """A value that crosses a stage boundary enters the consuming stage as a leaf tensor that
+    requires grad, and autograd refuses to overwrite a leaf.  Where the stage does overwrite one
+    (directly, or through a view of it) the stage works on a copy instead; everywhere else the
+    received buffer is consumed as it is."""
+    if first_compute is None:
+        return
+    for ph in placeholders:
+        seen, todo, hit = set(), [ph], False
+        while todo and not hit:
+            cur = todo.pop()
+            for u in cur.users:
+                if u in seen:
+                    continue
+                seen.add(u)
+                if _writes_in_place(u) and u.args and u.args[0] is cur:
+                    hit = True
+                    break
+                if _is_view(u):
+                    todo.append(u)
+        if hit:
+            with g.inserting_before(first_compute):
+                copy_node = g.call_method("clone", (ph,))
+            ph.replace_all_uses_with(copy_node, delete_user_cb=lambda u: u is not copy_node)
+
+
 def partition_module(cg: CompGraph, split_points: Sequence[int], device_cnt: int
                      ) -> PartitionGraph:
     captured = cg.captured
@@ -278,6 +335,9 @@ def partition_module(cg: CompGraph, split_points: Sequence[int], device_cnt: int
 
     by_name = [{n.name: n for n in g.nodes} for g in graphs]
     for s in range(n_stage):
+        edge_phs = [envs[s][i.name] for i in specs[s].inputs
+                    if i.kind == "edge" and i.name in envs[s]]
+        _protect_overwritten_inputs(graphs[s], first_compute[s], edge_phs)
         outs = tuple(envs[s][o.value] for o in specs[s].outputs)
         graphs[s].output(outs)
         graphs[s].lint()

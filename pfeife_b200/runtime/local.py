@@ -17,7 +17,7 @@ from typing import Any, Dict, List, Tuple
 import torch
 
 from ..parallel.device_bench import DeviceBench
-from .partial import PartialRunner
+from .partial import SCALER_KEY, PartialRunner
 from .transport import LocalTransport, _LocalHub
 from .worker import LoopFlag, StageWorker
 
@@ -149,20 +149,29 @@ class LocalRunner(PartialRunner):
                     raise res
 
     def _dispatch(self, msg: Dict[str, Any]) -> None:
-        self._wait_idle()
         flag = msg["flag"]
+        if flag == LoopFlag.STOP_LOOP:
+            try:
+                self._wait_idle()
+            except BaseException:       # a failed step was reported when it happened
+                pass
+            for q in self._jobs:
+                q.put(None)
+            return
+        if self.hub.aborted is not None:
+            raise RuntimeError("this pipeline stopped after a failed step; build a new runner") \
+                from self.hub.aborted
+        self._wait_idle()
         if flag in (LoopFlag.CONTINUE_LOOP, LoopFlag.EVAL_LOOP):
             for i, q in enumerate(self._jobs):
                 q.put(msg)
                 self._busy[i] = True
-        elif flag == LoopFlag.STOP_LOOP:
-            for q in self._jobs:
-                q.put(None)
         elif flag == LoopFlag.LOAD_PARAMS:
             for w in self.workers[:-1]:
                 w.params.load_named(msg["named"])
                 if msg.get("opt"):
                     w.params.load_optimizer_state(msg["opt"])
+                    w.scaler.load_state_dict(msg["opt"].get(SCALER_KEY))
         elif flag == LoopFlag.LOG_MEMORY_USAGE:
             for w in self.workers[:-1]:
                 w.log_memory_usage()
@@ -183,8 +192,20 @@ class LocalRunner(PartialRunner):
                 self._done[idx].put(e)
 
     def _run(self, a_split, k_split, training: bool):
-        out = super()._run(a_split, k_split, training)
-        self._wait_idle()
+        try:
+            out = super()._run(a_split, k_split, training)
+            self._wait_idle()
+        except BaseException as e:
+            # one stage failed: the others are waiting for tensors that will never arrive
+            self.hub.aborted = e
+            for i in range(len(self._jobs)):
+                if self._busy[i]:
+                    try:
+                        self._done[i].get(timeout=self.option.ctrl_timeout)
+                    except queue.Empty:
+                        pass
+                    self._busy[i] = False
+            raise
         return out
 
     def record_times(self) -> Dict[int, Tuple[float, float]]:

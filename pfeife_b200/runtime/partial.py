@@ -210,6 +210,11 @@ class PartialModule(torch.nn.Module):
                 len(self.captured.params) > 0
             self.pipe_idx = len(self.runner.modules)
             self.runner.modules.append(self)
+            # buffers that a forward pass updates (BatchNorm statistics and the like): the
+            # profiling passes below run the graph several times on the real tensors, and
+            # training must start from the values the user handed over, not from those
+            self._buffers_at_capture = {gi.index: gi.tensor.detach().clone()
+                                        for gi in self.captured.buffers} if self.should_pp else {}
 
     # -- first call: profile on the main rank, return a real output so exec_fn can continue
     def _probe_forward(self, args: Sequence[Any]) -> Any:
@@ -230,6 +235,12 @@ class PartialModule(torch.nn.Module):
         """Plan, partition and distribute (pfeife/mp/partial/module.py:290-371)."""
         r = self.runner
         opt, state = r.option, r.state
+        with torch.no_grad():
+            for gi in self.captured.buffers:
+                saved = self._buffers_at_capture.get(gi.index)
+                if saved is not None:
+                    gi.tensor.copy_(saved)
+        self._buffers_at_capture = {}
         pp = state.pp_size
         opt_pp = copy.copy(opt)
         opt_pp.device_cnt = pp

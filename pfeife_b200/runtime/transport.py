@@ -21,7 +21,8 @@ from __future__ import annotations
 
 import queue
 import threading
-from typing import Dict, List, Sequence, Tuple
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -108,6 +109,20 @@ class _LocalHub:
     def __init__(self):
         self.queues: Dict[Tuple[int, int], "queue.Queue"] = {}
         self.lock = threading.Lock()
+        # set when a device thread failed: receivers stop waiting for data that will never come
+        self.aborted: Optional[BaseException] = None
+
+    def get(self, src: int, dst: int, timeout: float):
+        q = self.q(src, dst)
+        deadline = time.monotonic() + timeout
+        while True:
+            if self.aborted is not None:
+                raise RuntimeError(f"pipeline aborted: another stage failed ({self.aborted!r})")
+            try:
+                return q.get(timeout=min(0.2, max(0.0, deadline - time.monotonic())))
+            except queue.Empty:
+                if time.monotonic() >= deadline:
+                    raise
 
     def q(self, src: int, dst: int) -> "queue.Queue":
         with self.lock:
@@ -129,7 +144,7 @@ class _LocalRecv(Handle):
         pend = t.pending[self.src]
         while not self.done:
             head = pend[0]
-            tensor, event = t.hub.q(head.src, t.rank).get(timeout=t.timeout)
+            tensor, event = t.hub.get(head.src, t.rank, t.timeout)
             if head.buf.is_cuda:
                 stream = t.copy_stream(head.src)
                 if event is not None:
