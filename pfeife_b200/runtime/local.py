@@ -73,6 +73,10 @@ class _LocalControl:
         return obj
 
     def scatter(self, objs: List[Any]) -> Any:
+        if objs and isinstance(objs[0], dict) and objs[0].get("abort"):
+            for q in self.runner._jobs:      # the first step failed: end the device threads
+                q.put(None)
+            return objs[-1]
         for w, payload in zip(self.runner.workers[:-1], objs[:-1]):
             self.runner._install(w, payload)
         return objs[-1]

@@ -146,6 +146,8 @@ def worker_loop(option: Optional[PipeOption] = None) -> None:
     worker = _make_worker(state, option)
     _run_device_bench(state, option)
     payload = ctrl.scatter(None)
+    if payload.get("abort"):        # the main rank failed before it had a plan
+        return
     _install_plan(worker, state, payload)
     ctrl.barrier()
     while True:
@@ -206,7 +208,11 @@ class PartialModule(torch.nn.Module):
             pp = self.runner.state.pp_size
             n_nodes = self.captured.compute_node_count()
             already = any(m.should_pp for m in self.runner.modules)
-            self.should_pp = (not already) and n_nodes >= max(2 * pp, 1) and \
+            # the reference's rule (pfeife/mp/partial/module.py:205-216): at least 2*pp graph
+            # nodes, of which at least pp compute; parameters are placeholders here and do not
+            # count as graph nodes
+            n_graph = n_nodes + len(self.captured.user_inputs) + 1
+            self.should_pp = (not already) and n_graph >= 2 * pp and n_nodes >= pp and \
                 len(self.captured.params) > 0
             self.pipe_idx = len(self.runner.modules)
             self.runner.modules.append(self)
@@ -378,20 +384,39 @@ class PartialRunner:
             raise RuntimeError("call set_exec_fn() before step()")
         a_split, k_split = split_args_kwargs(args, kwargs, self.batch_cnt)
         if not self._compiled:
-            self._probe_forward(a_split[0], k_split[0])
-            pipelined = [m for m in self.modules if m.should_pp and m.probed]
-            if not pipelined:
-                raise RuntimeError("no captured graph is eligible for pipelining: the model "
-                                   "call must happen inside exec_fn and the graph needs at "
-                                   f"least {2 * self.state.pp_size} compute nodes")
-            for m in pipelined:
-                m._compile(self.optimizer)
+            try:
+                self._probe_forward(a_split[0], k_split[0])
+                pipelined = [m for m in self.modules if m.should_pp and m.probed]
+                if not pipelined:
+                    raise RuntimeError("no captured graph is eligible for pipelining: the model "
+                                       "call must happen inside exec_fn and the graph needs at "
+                                       f"least {self.state.pp_size} compute nodes")
+                for m in pipelined:
+                    m._compile(self.optimizer)
+            except BaseException:
+                self._release_workers()
+                raise
             self._compiled = True
             if self._pending_load is not None:     # a checkpoint handed over before the first step
                 named, opt = self._pending_load
                 self._pending_load = None
                 self.load_params(named, opt)
         return self._run(a_split, k_split, training=True)
+
+    def _release_workers(self) -> None:
+        """The first step failed before the plan went out: the other ranks of the pipeline are
+        still waiting for it.  They get an empty plan, which ends their loop, and this runner is
+        closed, so that the error surfaces instead of a stalled job."""
+        if self._closed:
+            return
+        self._closed = True
+        if not any(m.compiled for m in self.modules):
+            try:
+                self.ctrl.scatter([{"abort": True}] * self.state.pp_size)
+            except Exception:
+                pass
+        for q in self._train_queues:
+            q.put(None)
 
     def eval_step(self, *args, **kwargs) -> List[Any]:
         """Forward-only pass through the pipeline; exec_fn must not call backward."""
