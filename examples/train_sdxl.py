@@ -82,7 +82,8 @@ def main():
 
     def item(g):
         r = lambda *s: torch.randn(*s, generator=g)
-        size = torch.tensor([args.resolution, args.resolution, 0, 0], dtype=torch.float32)
+        # integers: the loader casts floating tensors to the compute dtype, and bf16 would round sizes
+        size = torch.tensor([args.resolution, args.resolution, 0, 0], dtype=torch.int64)
         return (r(cfg.in_channels, side, side) * 0.18, r(77, cfg.cross_dim), r(cfg.pooled_dim), size)
 
     dataset = TensorFileDataset(args.data_file, 4) if args.data_file else \
