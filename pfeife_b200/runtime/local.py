@@ -61,6 +61,10 @@ class LocalReducer:
             self.slots.pop(me, None)
 
 
+class PipelineStopped(RuntimeError):
+    """Raised by a runner whose pipeline was torn down by an earlier failure."""
+
+
 class _LocalControl:
     """Control plane of the in-process pipeline: plain calls into the worker threads."""
 
@@ -163,8 +167,8 @@ class LocalRunner(PartialRunner):
                 q.put(None)
             return
         if self.hub.aborted is not None:
-            raise RuntimeError("this pipeline stopped after a failed step; build a new runner") \
-                from self.hub.aborted
+            raise PipelineStopped("this pipeline stopped after a failed step; build a new "
+                                  "runner") from self.hub.aborted
         self._wait_idle()
         if flag in (LoopFlag.CONTINUE_LOOP, LoopFlag.EVAL_LOOP):
             for i, q in enumerate(self._jobs):
@@ -193,15 +197,20 @@ class LocalRunner(PartialRunner):
                 worker.run(training=(msg["flag"] == LoopFlag.CONTINUE_LOOP))
                 self._done[idx].put(True)
             except BaseException as e:
+                if self.hub.aborted is None:
+                    self.hub.aborted = e       # stages waiting for this one's tensors give up
                 self._done[idx].put(e)
 
     def _run(self, a_split, k_split, training: bool):
         try:
             out = super()._run(a_split, k_split, training)
             self._wait_idle()
+        except PipelineStopped:
+            raise
         except BaseException as e:
             # one stage failed: the others are waiting for tensors that will never arrive
-            self.hub.aborted = e
+            if self.hub.aborted is None:
+                self.hub.aborted = e
             for i in range(len(self._jobs)):
                 if self._busy[i]:
                     try:
@@ -209,6 +218,8 @@ class LocalRunner(PartialRunner):
                     except queue.Empty:
                         pass
                     self._busy[i] = False
+            if self.hub.aborted is not e:
+                raise self.hub.aborted      # the failure that started it, not its echo
             raise
         return out
 

@@ -46,3 +46,36 @@ def test_local_pipeline_matches_plain_training(model_fn, dim, devices):
         assert len(mgr.runner.workers) == devices
     finally:
         mgr.close()
+
+
+@pytest.mark.timeout(120)
+def test_a_failing_stage_stops_the_whole_pipeline_at_once():
+    """Whichever device thread fails, the step raises that error within moments (the other
+    stages stop waiting for its tensors) and the runner refuses further steps."""
+    import time
+
+    import torch
+
+    from pfeife_b200 import PipeOption
+    from pfeife_b200.loss import SumLoss
+    from pfeife_b200.runtime.manager import LocalPipeManager
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(*[torch.nn.Linear(8, 8) for _ in range(6)])
+    option = PipeOption(device_cnt=2, batch_size=2, batch_cnt=2, cpu_test=True,
+                        no_bench_optimizer=True, ctrl_timeout=60)
+    mgr = LocalPipeManager(model, SumLoss(), option)
+    x = torch.randn(4, 8)
+    mgr.run(None, x)
+
+    def boom(*a, **k):
+        raise ValueError("stage 0 broke")
+
+    mgr.runner.workers[0].forward = boom
+    t0 = time.time()
+    with pytest.raises(ValueError, match="stage 0 broke"):
+        mgr.run(None, x)
+    assert time.time() - t0 < 20
+    with pytest.raises(RuntimeError, match="stopped after a failed step"):
+        mgr.run(None, x)
+    mgr.close()
