@@ -273,7 +273,11 @@ class CompGraph:
 
     def load_graph_data(self, path: str) -> None:
         with open(path, "rb") as f:
-            data = pickle.load(f)
+            self.apply_graph_data(pickle.load(f))
+
+    def apply_graph_data(self, data: Any) -> None:
+        """Copies profiled statistics (``graph_data()`` of the same model, or a reference-written
+        profile) positionally onto this graph."""
         if isinstance(data, dict) and data.get("format") == FORMAT:
             nodes, edges, fb = data["nodes"], data["edges"], data["fb_ratio"]
             get = lambda o, k: o[k]

@@ -228,6 +228,16 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
     return graph, output
 
 
+def run_unprofiled(captured: CapturedGraph, args: Sequence[Any], device: torch.device, option
+                   ) -> Tuple[CompGraph, Any]:
+    """The segmented graph and the output of one forward, without measuring anything: for a
+    rank that receives the statistics from the rank that profiled."""
+    graph = CompGraph(captured)
+    with gen_amp_context(device, option.mixed_precision):
+        output = SegmentExecutor(graph).run(args)
+    return graph, output
+
+
 def gen_comp_graph_cpu(captured: CapturedGraph, args: Sequence[Any], option
                        ) -> Tuple[CompGraph, Any]:
     """Unit-time profile for CPU tests: every segment costs 1 ms forward, ``fb_ratio`` 2

@@ -365,6 +365,19 @@ class PipeGraphGenerator:
             self.log.info("%s", best.pipe_graph.describe())
         return best
 
+    def plan_from(self, split_points: Sequence[int], sched_key: Sequence[int],
+                  max_mem: Optional[Sequence[float]] = None) -> Plan:
+        """The plan for given split points and schedule parameters
+        (``PipeSchedParams.key()``), without any search: what a data-parallel replica installs
+        after the first replica has planned."""
+        sched = PipeSchedParams(*[int(v) for v in sched_key])
+        pts = [int(p) for p in split_points]
+        v, ok, pg = self._valuate_points(pts, sched, max_mem)
+        plan = Plan(pts, sched, pg, v, pg.get_peak_memory(sched))
+        plan._ok = ok
+        self._refine_dep_graph(plan)
+        return plan
+
     def _refine_dep_graph(self, plan: Plan) -> None:
         dg = DependencyGraph(plan.pipe_graph, plan.sched)
         dg.calc_schedule()

@@ -34,7 +34,7 @@ import torch.distributed as dist
 from ..graph.capture import CapturedGraph, classify_inputs
 from ..graph.comp_graph import CompGraph
 from ..graph.partition import PartitionGraph, partition_module
-from ..graph.profiler import gen_comp_graph_cpu, gen_local_comp_graph
+from ..graph.profiler import gen_comp_graph_cpu, gen_local_comp_graph, run_unprofiled
 from ..option import PipeOption
 from ..parallel.device_bench import DeviceBench, NCCLDeviceBench
 from ..parallel.planner import Plan, get_pipe_class
@@ -90,6 +90,16 @@ class ControlPlane:
     def barrier(self) -> None:
         if self.state.pp_size > 1:
             dist.barrier(group=self.group)
+
+    def share_with_replicas(self, obj: Any = None) -> Any:
+        """Main ranks only: the object of the first replica's main rank, on every replica's main
+        rank.  The main ranks of all pipelines hold the same pipeline rank, so together they are
+        one data-parallel group."""
+        if self.state.dp_size == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.state.dp_group_ranks[0], group=self.state.ctrl_dp)
+        return box[0]
 
 
 class _DistReducer:
@@ -224,15 +234,23 @@ class PartialModule(torch.nn.Module):
 
     # -- first call: profile on the main rank, return a real output so exec_fn can continue
     def _probe_forward(self, args: Sequence[Any]) -> Any:
+        """One profile per job.  With data parallelism every replica's main rank captures the
+        same graph, but only the first replica measures it; its per-segment statistics go to the
+        other replicas, which run the graph once for the output their ``exec_fn`` continues
+        with.  Replicas that profiled on their own would see different timings, could choose
+        different split points and would then disagree on buffer layouts and group creation
+        (the reference shares one profile file, pfeife/mp/partial/module.py:263-272)."""
         r = self.runner
-        opt = r.option
-        if r.state.cpu:
-            cg, out = gen_comp_graph_cpu(self.captured, args, opt)
+        opt, state = r.option, r.state
+        if state.dp_size == 1 or state.dp_rank == 0:
+            if state.cpu:
+                cg, out = gen_comp_graph_cpu(self.captured, args, opt)
+            else:
+                cg, out = gen_local_comp_graph(self.captured, args, state.device, opt)
+            r.ctrl.share_with_replicas(cg.graph_data())
         else:
-            o = copy.copy(opt)
-            if r.state.dp_size > 1 and not o.graph_bench:
-                o.graph_bench = None
-            cg, out = gen_local_comp_graph(self.captured, args, r.state.device, o)
+            cg, out = run_unprofiled(self.captured, args, state.device, opt)
+            cg.apply_graph_data(r.ctrl.share_with_replicas(None))
         self.comp_graph = cg
         self.probed = True
         return out
@@ -257,7 +275,14 @@ class PartialModule(torch.nn.Module):
             total = torch.cuda.get_device_properties(state.device).total_memory
             max_mem = [float(total)] * pp
         gen = get_pipe_class(opt.partitioner)(self.comp_graph, r.device_bench, opt_pp)
-        plan = gen.gen_graph(opt.batch_cnt, max_mem, opt.split_points)
+        # one search per job: the first replica's split points and schedule parameters are
+        # installed by every replica (their link measurements differ, their plans must not)
+        if state.dp_size == 1 or state.dp_rank == 0:
+            plan = gen.gen_graph(opt.batch_cnt, max_mem, opt.split_points)
+            r.ctrl.share_with_replicas((list(plan.split_points), plan.sched.key()))
+        else:
+            points, sched_key = r.ctrl.share_with_replicas(None)
+            plan = gen.plan_from(points, sched_key, max_mem)
         self.plan = plan
         part = partition_module(self.comp_graph, plan.split_points, pp)
         self.part = part

@@ -78,6 +78,9 @@ def main():
     ap.add_argument("--fail_rank", type=int, default=-1,
                     help="this global rank raises an exception on the host before its first step "
                          "(failure-detection test; no device work is in flight)")
+    ap.add_argument("--skew_profile", action="store_true",
+                    help="every rank that profiles gets segment times of its own (seeded by its "
+                         "rank), as timing noise on real devices would give it")
     PipeOption.add_arguments(ap)
     args = ap.parse_args()
 
@@ -90,6 +93,19 @@ def main():
         worker_loop()
         return
     option = PipeOption.from_args(args)
+    if args.skew_profile:
+        import random
+
+        from pfeife_b200.runtime import partial as _partial
+        plain = _partial.gen_comp_graph_cpu
+
+        def skewed(captured, call_args, opt):
+            cg, out = plain(captured, call_args, opt)
+            rng = random.Random(1234 + state.rank)
+            for node in cg.nodes:
+                node.comp_time = rng.uniform(0.2, 5.0)
+            return cg, out
+        _partial.gen_comp_graph_cpu = skewed
     set_seed(0)
     model, make_batch, loss_fn = build(args.model)
     ref = copy.deepcopy(model)
@@ -160,6 +176,8 @@ def main():
             diff = max(diff, float((p.detach().cpu() - q.detach()).abs().max()))
     result["param_diff"] = diff
     result["opt_state_keys"] = sorted(opt_state.keys())[:3] if opt_state else []
+    result["split_points"] = [list(m.plan.split_points) for m in runner.modules
+                              if m.plan is not None]
     result["state_dict_keys"] = len(model.state_dict())
     if state.dp_size > 1:
         # replicas must hold identical parameters after training

@@ -75,6 +75,18 @@ def test_dp2_x_pp2_replicas_stay_identical(tmp_path):
     assert res["losses"] != other["losses"]      # replicas saw different data
 
 
+def test_replicas_install_one_plan_whatever_they_would_measure(tmp_path):
+    """Two replicas whose own profiles would differ (every profiling rank gets different segment
+    times) still install the same split points: only the first replica profiles and plans."""
+    res, out = launch(tmp_path, 4, ["--model", "mlp", "--device_cnt", "2", "--batch_size", "2",
+                                    "--batch_cnt", "2", "--steps", "2", "--skew_profile"],
+                      dp_mesh="-2,2")
+    with open(out + ".dp0") as f:
+        other = json.load(f)
+    assert res["split_points"] and res["split_points"] == other["split_points"]
+    assert res["param_checksum"] == pytest.approx(other["param_checksum"], rel=1e-9)
+
+
 def test_llama_tied_embeddings_looped(tmp_path):
     res, _ = launch(tmp_path, 2, ["--model", "llama_tiny", "--device_cnt", "2", "--batch_size", "2",
                                   "--batch_cnt", "4", "--steps", "2"])
