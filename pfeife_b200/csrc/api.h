@@ -52,8 +52,10 @@ PF_DECL int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const 
 PF_DECL int pf_nonfinite(const void* g, long long n, void* found_inf, int sm_count, void* stream);
 PF_DECL int pf_adamw(void* p, void* g, void* m, void* v, void* lp, long long n,
                      const void* found_inf, const void* loss_scale, float lr, float beta1,
-                     float beta2, float eps, float weight_decay, int step, float grad_scale,
-                     int adamw, int zero_grad, int lp_dtype, int sm_count, void* stream);
+                     float beta2, float eps, float weight_decay, int step,
+                     const void* applied_steps, float grad_scale, int adamw, int zero_grad,
+                     int lp_dtype, int sm_count, void* stream);
+PF_DECL int pf_step_advance(void* applied_steps, const void* found_inf, void* stream);
 PF_DECL int pf_sgd(void* p, void* g, void* mom, void* lp, long long n, const void* found_inf,
                    const void* loss_scale, float lr, float momentum, float dampening,
                    float weight_decay, int nesterov, int first_step, float grad_scale,
@@ -96,11 +98,12 @@ PF_DECL int pf_attn_bwd(const void* dout, const void* q, const void* k, const vo
 PF_DECL int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                              void* const* lp, void* const* flags, void* m, void* v,
                              void* local_sync, long long shard_lo, long long shard_hi,
-                             long long local_below, long long zero_lo, long long zero_hi,
-                             float lr, float beta1, float beta2,
-                             float eps, float weight_decay, int step, float grad_scale, int adamw,
-                             int lp_dtype, int check_inf, const void* loss_scale, void* found_inf,
-                             int epoch, int calls_before, int* status, int sm_count, void* stream);
+                             long long total, int ngroups, const long long* groups,
+                             const float* hyper, const void* applied_steps, int host_step,
+                             float grad_scale, int lp_dtype, int check_inf, int found_given,
+                             const void* loss_scale, void* found_inf, int epoch,
+                             int arrivals_before, int* barriers_out, int* grid_out, int* status,
+                             int sm_count, void* stream);
 PF_DECL int pf_gather_rows(void* dst, void* const* copies, const int* row_end, int world, int rank,
                            int rows, long long row_bytes, int sm_count, void* stream);
 PF_DECL int pf_ipc_get_handle(void* ptr, void* handle_out_64);

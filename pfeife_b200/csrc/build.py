@@ -28,10 +28,14 @@ HOST_LIB = PKG / "libpfeife_b200_host.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",
+    "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
 ]
+# Approximate division / square root / transcendentals are fine for activations and softmax,
+# not for the optimizer update: those two files are bandwidth-bound and keep IEEE arithmetic.
+FAST_MATH = ["--use_fast_math"]
+PRECISE_SOURCES = {"optim.cu", "dp_fused.cu"}
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread"]
 
 
@@ -71,7 +75,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         obj = BUILD / (src.stem + ".cu.o")
         objs_cu.append(obj)
         if force or _stale(obj, [src] + headers):
-            flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+            flags = list(NVCC_FLAGS) + ([] if src.name in PRECISE_SOURCES else FAST_MATH) + \
+                (["-Xptxas", "-v"] if ptxas_info else [])
             jobs.append([nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
     for src in cpp:
         obj = BUILD / (src.stem + ".cpp.o")

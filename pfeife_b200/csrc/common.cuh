@@ -29,8 +29,22 @@ enum Status : int {
 #define PF_WAIT_CYCLES (2000000000ll)
 #endif
 
+// The status buffer handed to a kernel is int[PF_STATUS_WORDS]:
+//   [0] first error code (0 = none), [1] wait limit in units of 1024 cycles (0 = PF_WAIT_CYCLES).
+// The limit is a run-time value so that a caller (or a test that lets a wait run out on
+// purpose) can shorten it without rebuilding the library.
+constexpr int PF_STATUS_WORDS = 4;
+
 __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ long long wait_limit(const int* status) {
+  if (status) {
+    const int k = *reinterpret_cast<const volatile int*>(status + 1);
+    if (k > 0) return static_cast<long long>(k) << 10;
+  }
+  return PF_WAIT_CYCLES;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -76,9 +90,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (after recording `code`) when the limit runs out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = clock64(), limit = wait_limit(status);
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > PF_WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       report(status, code);
       return false;
     }
@@ -222,9 +236,9 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* status,
                                                   int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = clock64(), limit = wait_limit(status);
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if (clock64() - t0 > PF_WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       report(status, code);
       return false;
     }

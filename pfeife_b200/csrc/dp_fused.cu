@@ -1,22 +1,29 @@
 // Fused data-parallel step over NVLink peer memory: gradient reduce-scatter + unscale +
-// non-finite agreement + partitioned AdamW + all-gather of the updated weights, in ONE kernel
-// per rank (one process per GPU; every rank launches the same kernel on its own stream).
+// non-finite agreement + partitioned AdamW + all-gather of the updated 16-bit weights, in ONE
+// kernel per rank (one process per GPU; every rank launches the same kernel on its own stream).
 //
 // Every rank owns a contiguous shard of the flat parameter space.  Its kernel
 //   1. waits until every rank has finished its backward (flag barrier over peer memory),
-//   2. reads its shard of the fp32 gradient bucket from EVERY rank with plain P2P vector loads,
-//      sums, stores the sum into its own bucket and zeroes the peers' copies (ready for the
-//      next step's accumulation), noting whether anything was non-finite,
-//   3. publishes its non-finite flag to all ranks and barriers, so that all ranks take the same
-//      skip decision (dynamic loss scaling),
-//   4. applies AdamW on the shard with moments that exist only on the owner (ZeRO-1 memory),
-//      and writes the new fp32 master weights and their 16-bit shadow into EVERY rank's
-//      buffers with P2P vector stores,
-//   5. barriers again so nobody starts the next forward on half-written weights.
+//   2. reads its shard of the fp32 gradient bucket from EVERY rank with plain P2P vector loads
+//      (the loads of all peers are issued before any is consumed), sums them into its own
+//      bucket and notes whether anything was non-finite,
+//   3. (dynamic loss scaling only) publishes its non-finite flag to all ranks and barriers, so
+//      that all ranks take the same skip decision; a decision agreed outside the kernel, over
+//      a whole PPxDP job, is passed in instead and costs no barrier,
+//   4. applies Adam/AdamW on the shard, all optimizer groups in one launch, with moments that
+//      exist only on the owner (ZeRO-1 memory), and writes the new 16-bit weights into EVERY
+//      rank's shadow buffer with P2P vector stores.  The fp32 masters stay with the owner; only
+//      the tail of each group that some op reads in fp32 (biases, norm weights: `master_from`)
+//      is pushed to the peers' master buffers,
+//   5. barriers again so nobody starts the next forward on half-written weights, and clears the
+//      part of its own gradient bucket that other ranks own (they have all read it by then).
+// Bytes over NVLink per parameter: 4 read + 2 written, times (world-1)/world.
 // No NCCL call, no TMA and no multicast load is involved; all remote traffic is ld/st.global on
 // IPC-mapped peer pointers.  Barriers are epoch counters written with st.release.sys and
-// polled with ld.acquire.sys; every poll is bounded and reports PF_ERR_TIMEOUT_PEER_FLAG
-// instead of spinning forever when a peer is gone.
+// polled with ld.acquire.sys.  Every poll is bounded by the run-time wait limit of the status
+// buffer; a wait that runs out is STICKY for the call: the kernel records
+// PF_ERR_TIMEOUT_PEER_FLAG, marks the step as skipped, touches no weight, no moment and no peer
+// memory afterwards, and returns.  The host reads the status word once per step.
 #include <cstring>
 #include "common.cuh"
 #include "api.h"
@@ -24,11 +31,21 @@
 namespace pf {
 
 constexpr int DP_MAX = 8;
-// Ranks reach the first barrier of a step with the skew of a whole training step between
-// them (first-step compilation, graph capture), so that wait is allowed ~20 s; the later
-// barriers only cover the kernel's own phases.
-constexpr long long DP_ENTRY_WAIT = 20 * PF_WAIT_CYCLES;
+constexpr int DP_MAX_GROUPS = 8;
 constexpr int DP_THREADS = 512;
+// Ranks reach the first barrier of a step with the skew of a whole training step between them
+// (first-step compilation, graph capture), so that wait gets this multiple of the limit; the
+// later barriers only cover the kernel's own phases.
+constexpr int DP_ENTRY_WAIT_FACTOR = 10;
+
+struct DpGroup {
+  long long lo, hi;            // range of the flat buffer this optimizer group covers
+  long long local_below;       // 16-bit weights below this index are written locally only: their
+                               // first consumer gathers the rows other ranks own
+  long long master_from;       // fp32 masters at or above this index also go to every peer
+  float lr, beta1, beta2, eps, weight_decay;
+  int adamw;
+};
 
 struct DpArgs {
   int rank, world;
@@ -38,18 +55,21 @@ struct DpArgs {
   int* flags[DP_MAX];          // per rank: int[DP_MAX] barrier slots + int[DP_MAX] found slots
   float* m;                    // local moments, indexed from shard_lo
   float* v;
-  int* local_sync;             // local: [0] arrival counter, [1] release word
+  int* local_sync;             // local: [0] arrival counter, [1] release word, [2] failed epoch
   long long shard_lo, shard_hi;
-  long long local_below;       // 16-bit weights at flat indices below this are written locally
-                               // only: their first consumer gathers the rows other ranks own
-                               // (fused all-gather GEMM); fp32 masters always go to every rank
-  long long zero_lo, zero_hi;  // range of the local gradient bucket this call clears
-  float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
-  int adamw, lp_dtype, check_inf;
+  long long total;             // length of the flat buffers
+  int ngroups;
+  DpGroup group[DP_MAX_GROUPS];
+  float grad_scale;
+  int lp_dtype;
+  int check_inf;               // 1: agree on non-finite gradients inside the kernel
+  int found_given;             // 1: *found_inf already holds the job-wide decision
   const float* loss_scale;     // local device scalar (identical on every rank) or null
-  float* found_inf;            // local: set to 1 when the step was skipped
-  int epoch;                   // barrier epoch base of this call (strictly increasing)
-  int sync_base;               // arrivals expected before this call
+  float* found_inf;            // local: 1 when the step was skipped
+  const int* applied_steps;    // device counter of optimizer steps that were applied so far
+  int host_step;               // used when applied_steps is null
+  int epoch;                   // epoch of this call's first barrier (same on every rank)
+  int sync_base;               // arrivals at local_sync[0] before this call
   int* status;
 };
 
@@ -66,119 +86,135 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// counters wrap: "a has reached b" in modular arithmetic
+__device__ __forceinline__ bool reached(int a, int b) { return (int)((unsigned)a - (unsigned)b) >= 0; }
 
 // All CTAs of this GPU and all ranks meet here.  `k` = ordinal of the barrier within the call.
-__device__ void job_barrier(const DpArgs& a, int k) {
+// Returns false on every thread of every CTA of this GPU when any wait of this call ran out.
+__device__ bool job_barrier(const DpArgs& a, int k) {
+  __shared__ int s_failed;
   __threadfence_system();
   __syncthreads();
   const int epoch = a.epoch + k;
   if (threadIdx.x == 0) {
-    const int target = a.sync_base + (k + 1) * gridDim.x;
+    const long long limit = wait_limit(a.status) * (k == 0 ? DP_ENTRY_WAIT_FACTOR : 1);
+    const int target = a.sync_base + (k + 1) * (int)gridDim.x;
     atomicAdd(&a.local_sync[0], 1);
+    bool ok = true;
     if (blockIdx.x == 0) {
       long long t0 = clock64();
-      bool ok = true;
-      while (ld_acquire_gpu(&a.local_sync[0]) < target) {
-        if (clock64() - t0 > PF_WAIT_CYCLES) { report(a.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+      while (!reached(ld_acquire_gpu(&a.local_sync[0]), target)) {
+        if (clock64() - t0 > limit) { ok = false; break; }
       }
-      __threadfence_system();
-      for (int p = 0; p < a.world; ++p) st_release_sys(&a.flags[p][a.rank], epoch);
-      const long long limit = (k == 0) ? DP_ENTRY_WAIT : PF_WAIT_CYCLES;
-      for (int r = 0; r < a.world && ok; ++r) {
-        t0 = clock64();
-        while (ld_acquire_sys(&a.flags[a.rank][r]) < epoch) {
-          if (clock64() - t0 > limit) { report(a.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+      if (ok) {
+        __threadfence_system();
+        for (int p = 0; p < a.world; ++p) st_release_sys(&a.flags[p][a.rank], epoch);
+        for (int r = 0; r < a.world && ok; ++r) {
+          t0 = clock64();
+          while (!reached(ld_acquire_sys(&a.flags[a.rank][r]), epoch)) {
+            if (clock64() - t0 > limit) { ok = false; break; }
+          }
         }
       }
+      if (!ok) {
+        report(a.status, PF_ERR_TIMEOUT_PEER_FLAG);
+        atomicExch(&a.local_sync[2], a.epoch);      // sticky for this call
+      }
       __threadfence_system();
-      atomicExch(&a.local_sync[1], epoch);
+      atomicExch(&a.local_sync[1], epoch);          // release the other CTAs either way
     } else {
-      long long t0 = clock64();
-      while (ld_acquire_gpu(&a.local_sync[1]) < epoch) {
-        if (clock64() - t0 > ((k == 0) ? DP_ENTRY_WAIT : PF_WAIT_CYCLES) * (a.world + 1)) { report(a.status, PF_ERR_TIMEOUT_PEER_FLAG); break; }
+      const long long t0 = clock64();
+      while (!reached(ld_acquire_gpu(&a.local_sync[1]), epoch)) {
+        if (clock64() - t0 > 2 * limit + limit * a.world) {
+          report(a.status, PF_ERR_TIMEOUT_PEER_FLAG);
+          atomicExch(&a.local_sync[2], a.epoch);
+          break;
+        }
       }
     }
+    s_failed = ld_acquire_gpu(&a.local_sync[2]) == a.epoch;
   }
   __syncthreads();
+  return !s_failed;
 }
 
+template <int WORLD>
 __global__ void __launch_bounds__(DP_THREADS, 2)
 dp_fused_kernel(const DpArgs a) {
   const long long lo = a.shard_lo, hi = a.shard_hi;
   const long long nvec = (hi - lo) / 4;        // shards are multiples of 4 elements
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  int kbar = 0;
 
-  job_barrier(a, 0);                            // every rank's gradients are complete
+  bool ok = job_barrier(a, kbar++);            // every rank's gradients are complete
+  if (!ok) { if (tid == 0 && a.found_inf) *a.found_inf = 1.f; return; }
 
-  // ---- reduce-scatter into the local bucket, zero the peers' copies.  Four 16-byte vectors
-  //      per thread and peer are requested before any is consumed, so enough bytes are in
-  //      flight to cover the NVLink latency.
+  // ---- reduce-scatter into the local bucket.  One or two 16-byte vectors per thread from each
+  //      of the WORLD buckets (128 bytes per thread in all) are requested before any is consumed.
   bool bad = false;
-  constexpr int U = 4;
+  constexpr int U = WORLD <= 4 ? 2 : 1;
   for (long long i0 = tid; i0 < nvec; i0 += stride * U) {
-    float4 s[U];
+    float4 g[WORLD][U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < a.world; ++p) {
-      float4 g[U];
+    for (int p = 0; p < WORLD; ++p)
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
-        g[u] = i < nvec ? *reinterpret_cast<const float4*>(a.grad[p] + lo + i * 4)
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        g[p][u] = i < nvec ? __ldcs(reinterpret_cast<const float4*>(a.grad[p] + lo + i * 4))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long i = i0 + u * stride;
-        s[u].x += g[u].x; s[u].y += g[u].y; s[u].z += g[u].z; s[u].w += g[u].w;
-      }
-    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i = i0 + u * stride;
+      float4 s = g[0][u];
+#pragma unroll
+      for (int p = 1; p < WORLD; ++p) {
+        s.x += g[p][u].x; s.y += g[p][u].y; s.z += g[p][u].z; s.w += g[p][u].w;
+      }
       if (i < nvec) {
-        *reinterpret_cast<float4*>(a.grad[a.rank] + lo + i * 4) = s[u];
+        if (WORLD > 1) *reinterpret_cast<float4*>(a.grad[a.rank] + lo + i * 4) = s;
         if (a.check_inf)
-          bad |= !(isfinite(s[u].x) && isfinite(s[u].y) && isfinite(s[u].z) && isfinite(s[u].w));
+          bad |= !(isfinite(s.x) && isfinite(s.y) && isfinite(s.z) && isfinite(s.w));
       }
     }
-  }
-  if (a.check_inf) {
-    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0)
-      for (int p = 0; p < a.world; ++p) st_release_sys(&a.flags[p][DP_MAX + a.rank], a.epoch);
-  }
-
-  job_barrier(a, 1);                            // everybody's non-finite flag is published
-
-  // ---- every rank has read what it needed of this bucket: clear the part of it that other
-  //      ranks own (local stores; the own shard is cleared by the update loop below)
-  {
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const long long n_before = (lo - a.zero_lo) / 4, n_after = (a.zero_hi - hi) / 4;
-    for (long long i = tid; i < n_before; i += stride)
-      *reinterpret_cast<float4*>(a.grad[a.rank] + a.zero_lo + i * 4) = z4;
-    for (long long i = tid; i < n_after; i += stride)
-      *reinterpret_cast<float4*>(a.grad[a.rank] + hi + i * 4) = z4;
   }
 
   bool skip = false;
   if (a.check_inf) {
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0)
+      for (int p = 0; p < a.world; ++p) st_release_sys(&a.flags[p][DP_MAX + a.rank], a.epoch);
+    ok = job_barrier(a, kbar++);               // everybody's non-finite flag is published
+    if (!ok) { if (tid == 0 && a.found_inf) *a.found_inf = 1.f; return; }
     for (int r = 0; r < a.world; ++r)
       skip |= ld_acquire_sys(&a.flags[a.rank][DP_MAX + r]) == a.epoch;
     if (tid == 0) *a.found_inf = skip ? 1.f : 0.f;
+  } else if (a.found_given) {
+    skip = *reinterpret_cast<const volatile float*>(a.found_inf) != 0.f;
   }
   float gs = a.grad_scale;
   if (a.loss_scale) gs /= *a.loss_scale;
-  const float inv_bc1 = 1.f / a.bc1;
-  const float inv_sqrt_bc2 = rsqrtf(a.bc2);
+  const float step = (float)(a.applied_steps ? *a.applied_steps + 1 : a.host_step);
 
-  // ---- partitioned AdamW, all-gather of master weights and 16-bit shadow by P2P stores
+  // ---- partitioned Adam/AdamW; new 16-bit weights go to every rank by P2P stores
+  int gi = 0;
+  float lr = 0.f, b1 = 0.f, b2 = 0.f, eps = 0.f, wd = 0.f, inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
+  bool adamw = true;
+  long long g_lo = 0, g_hi = -1, local_below = 0, master_from = 0;
   for (long long i = tid; i < nvec; i += stride) {
     const long long e = lo + i * 4;
     float4 g4 = *reinterpret_cast<const float4*>(a.grad[a.rank] + e);
     *reinterpret_cast<float4*>(a.grad[a.rank] + e) = make_float4(0.f, 0.f, 0.f, 0.f);
     if (skip) continue;
+    if (e < g_lo || e >= g_hi) {               // entered another optimizer group
+      for (gi = 0; gi < a.ngroups - 1 && !(e >= a.group[gi].lo && e < a.group[gi].hi); ++gi) {}
+      const DpGroup& G = a.group[gi];
+      g_lo = G.lo; g_hi = G.hi; local_below = G.local_below; master_from = G.master_from;
+      lr = G.lr; b1 = G.beta1; b2 = G.beta2; eps = G.eps; wd = G.weight_decay;
+      adamw = G.adamw != 0;
+      inv_bc1 = 1.f / (1.f - powf(b1, step));
+      inv_sqrt_bc2 = rsqrtf(1.f - powf(b2, step));
+    }
     float4 w4 = *reinterpret_cast<const float4*>(a.master[a.rank] + e);
     float4 m4 = *reinterpret_cast<const float4*>(a.m + i * 4);
     float4 v4 = *reinterpret_cast<const float4*>(a.v + i * 4);
@@ -187,15 +223,16 @@ dp_fused_kernel(const DpArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float gr = g[j] * gs;
-      if (a.adamw) w[j] *= (1.f - a.lr * a.weight_decay);
-      else gr += a.weight_decay * w[j];
-      m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gr;
-      v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gr * gr;
-      w[j] -= a.lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + a.eps);
+      if (adamw) w[j] *= (1.f - lr * wd);
+      else gr += wd * w[j];
+      m[j] = b1 * m[j] + (1.f - b1) * gr;
+      v[j] = b2 * v[j] + (1.f - b2) * gr * gr;
+      w[j] -= lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + eps);
     }
     *reinterpret_cast<float4*>(a.m + i * 4) = make_float4(m[0], m[1], m[2], m[3]);
     *reinterpret_cast<float4*>(a.v + i * 4) = make_float4(v[0], v[1], v[2], v[3]);
     const float4 nw = make_float4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<float4*>(a.master[a.rank] + e) = nw;
     uint2 q = make_uint2(0, 0);
     if (a.lp[a.rank]) {
       if (a.lp_dtype == PF_BF16) {
@@ -205,16 +242,31 @@ dp_fused_kernel(const DpArgs a) {
         __half2 x = __floats2half2_rn(w[0], w[1]), y = __floats2half2_rn(w[2], w[3]);
         q = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&y));
       }
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q;
     }
-    const bool push_lp = e >= a.local_below;
-    for (int p = 0; p < a.world; ++p) {
-      *reinterpret_cast<float4*>(a.master[p] + e) = nw;
-      if (a.lp[p] && (push_lp || p == a.rank))
+    const bool push_lp = e >= local_below, push_master = e >= master_from;
+#pragma unroll
+    for (int p = 0; p < WORLD; ++p) {
+      if (p == a.rank) continue;
+      if (push_master) *reinterpret_cast<float4*>(a.master[p] + e) = nw;
+      if (a.lp[p] && push_lp)
         *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q;
     }
   }
 
-  job_barrier(a, 2);                            // all weights have landed everywhere
+  ok = job_barrier(a, kbar++);                  // all weights have landed everywhere
+  if (!ok) return;
+
+  // ---- every rank has read what it needed of this bucket: clear the part of it that other
+  //      ranks own (local stores; the own shard was cleared by the update loop)
+  {
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long n_before = lo / 4, n_after = (a.total - hi) / 4;
+    for (long long i = tid; i < n_before; i += stride)
+      *reinterpret_cast<float4*>(a.grad[a.rank] + i * 4) = z4;
+    for (long long i = tid; i < n_after; i += stride)
+      *reinterpret_cast<float4*>(a.grad[a.rank] + hi + i * 4) = z4;
+  }
 }
 
 }  // namespace pf
@@ -222,21 +274,27 @@ dp_fused_kernel(const DpArgs a) {
 using namespace pf;
 
 // Pointer tables are arrays of `world` device pointers (entry `rank` is the local buffer).
-// [shard_lo, shard_hi) is the part of this call's range [zero_lo, zero_hi) that this rank owns:
-// it reduces and updates its shard and clears the whole range of its own gradient bucket.
-// `epoch` must grow by at least 3 per call and be identical on every rank; `sync_base` is
-// (number of earlier calls) * 3 * grid.  Returns the grid size used through *grid_out.
+// [shard_lo, shard_hi) is the part of the flat buffers [0, total) that this rank owns: it
+// reduces and updates its shard and clears the whole of its own gradient bucket.
+// `groups` holds `ngroups` records of 4 long long (lo, hi, local_below, master_from) and
+// `hyper` `ngroups` records of 6 floats (lr, beta1, beta2, eps, weight_decay, adamw != 0).
+// `epoch` is the value of this call's first barrier: it must be identical on every rank and
+// grow by the number of barriers a call uses (2, or 3 with check_inf), which the call returns
+// through *barriers_out; `arrivals_before` is the sum over earlier calls of barriers * grid
+// (*grid_out).  `applied_steps` (device int, may be null) counts the optimizer steps that were
+// not skipped; the bias correction uses it, so a step skipped on an overflow does not count.
 PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                             void* const* lp, void* const* flags, void* m, void* v,
                             void* local_sync, long long shard_lo, long long shard_hi,
-                            long long local_below, long long zero_lo, long long zero_hi,
-                            float lr,
-                            float beta1, float beta2, float eps, float weight_decay, int step,
-                            float grad_scale, int adamw, int lp_dtype, int check_inf,
-                            const void* loss_scale, void* found_inf, int epoch, int calls_before,
-                            int* status, int sm_count, void* stream) {
-  if (world < 1 || world > DP_MAX) return -3;
-  if ((shard_lo % 4) || (shard_hi % 4)) return -2;
+                            long long total, int ngroups, const long long* groups,
+                            const float* hyper, const void* applied_steps, int host_step,
+                            float grad_scale, int lp_dtype, int check_inf, int found_given,
+                            const void* loss_scale, void* found_inf, int epoch,
+                            int arrivals_before, int* barriers_out, int* grid_out, int* status,
+                            int sm_count, void* stream) {
+  if (world < 1 || world > DP_MAX || ngroups < 1 || ngroups > DP_MAX_GROUPS) return -3;
+  if ((shard_lo % 4) || (shard_hi % 4) || (total % 4)) return -2;
+  if (shard_lo < 0 || shard_hi < shard_lo || shard_hi > total) return -2;
   DpArgs a = {};
   a.rank = rank; a.world = world;
   for (int p = 0; p < world; ++p) {
@@ -246,20 +304,38 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
     a.flags[p] = (int*)flags[p];
   }
   a.m = (float*)m; a.v = (float*)v; a.local_sync = (int*)local_sync;
-  a.shard_lo = shard_lo; a.shard_hi = shard_hi;
-  if (zero_lo > shard_lo || zero_hi < shard_hi || (zero_lo % 4) || (zero_hi % 4)) return -2;
-  a.local_below = local_below;
-  a.zero_lo = zero_lo; a.zero_hi = zero_hi;
-  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
-  a.bc1 = 1.f - powf(beta1, (float)step);
-  a.bc2 = 1.f - powf(beta2, (float)step);
-  a.grad_scale = grad_scale; a.adamw = adamw; a.lp_dtype = lp_dtype; a.check_inf = check_inf;
+  a.shard_lo = shard_lo; a.shard_hi = shard_hi; a.total = total;
+  a.ngroups = ngroups;
+  for (int g = 0; g < ngroups; ++g) {
+    DpGroup& G = a.group[g];
+    G.lo = groups[4 * g]; G.hi = groups[4 * g + 1];
+    G.local_below = groups[4 * g + 2]; G.master_from = groups[4 * g + 3];
+    if ((G.lo % 4) || (G.hi % 4)) return -2;
+    G.lr = hyper[6 * g]; G.beta1 = hyper[6 * g + 1]; G.beta2 = hyper[6 * g + 2];
+    G.eps = hyper[6 * g + 3]; G.weight_decay = hyper[6 * g + 4]; G.adamw = hyper[6 * g + 5] != 0.f;
+  }
+  a.grad_scale = grad_scale; a.lp_dtype = lp_dtype;
+  a.check_inf = check_inf; a.found_given = check_inf ? 0 : found_given;
   a.loss_scale = (const float*)loss_scale; a.found_inf = (float*)found_inf;
+  a.applied_steps = (const int*)applied_steps; a.host_step = host_step;
   a.epoch = epoch; a.status = status;
-  // two 512-thread CTAs per SM: all CTAs are co-resident (the barriers rely on it)
+  // two 512-thread CTAs per SM: all CTAs are co-resident (the barriers rely on it; a CTA that
+  // has to wait for an SM delays the barrier, within the wait limit)
   const int grid = 2 * (sm_count > 0 ? sm_count : 148);
-  a.sync_base = calls_before * 3 * grid;
-  dp_fused_kernel<<<grid, DP_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  a.sync_base = arrivals_before;
+  if (barriers_out) *barriers_out = check_inf ? 3 : 2;
+  if (grid_out) *grid_out = grid;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (world) {
+    case 1: dp_fused_kernel<1><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 2: dp_fused_kernel<2><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 3: dp_fused_kernel<3><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 4: dp_fused_kernel<4><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 5: dp_fused_kernel<5><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 6: dp_fused_kernel<6><<<grid, DP_THREADS, 0, st>>>(a); break;
+    case 7: dp_fused_kernel<7><<<grid, DP_THREADS, 0, st>>>(a); break;
+    default: dp_fused_kernel<8><<<grid, DP_THREADS, 0, st>>>(a); break;
+  }
   PF_CHECK_LAUNCH();
   return 0;
 }

@@ -261,9 +261,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int n1 = min(p.N, n0 + BNT);
           const int expect = (n1 - n0) - max(0, min(n1, own1) - max(n0, own0));
           if (expect > 0) {
-            long long t0 = clock64();
+            const long long t0 = clock64(), limit = wait_limit(p.status);
             while (*reinterpret_cast<volatile int*>(p.gather_ready + nt) < expect) {
-              if (clock64() - t0 > PF_WAIT_CYCLES) { report(p.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
+              if (clock64() - t0 > limit) { report(p.status, PF_ERR_TIMEOUT_PEER_FLAG); ok = false; break; }
             }
             // once every remote row is in place no later tile needs to look again
             const int remote_rows = p.N - max(0, min(p.N, own1) - own0);

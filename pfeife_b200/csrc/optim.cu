@@ -25,7 +25,7 @@ nonfinite_kernel(const float* __restrict__ g, long long n, float* __restrict__ f
 
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay;
-  float bc1, bc2;      // 1 - beta^t
+  int step;            // 1-based step number, used when no device counter is given
   float grad_scale;    // multiplies the gradient (1 / loss_scale / accumulation count)
   int adamw;           // decoupled decay (AdamW) or L2 (Adam)
   int zero_grad;
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
              float* __restrict__ v, void* __restrict__ lp, long long n,
              const float* __restrict__ found_inf, const float* __restrict__ loss_scale,
-             AdamArgs a) {
+             const int* __restrict__ applied_steps, AdamArgs a) {
   if (loss_scale) a.grad_scale /= *loss_scale;
   if (found_inf && *found_inf != 0.f) {
     if (a.zero_grad) {
@@ -50,8 +50,11 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m
   }
   const long long nvec = n / 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  const float inv_bc1 = 1.f / a.bc1;
-  const float inv_sqrt_bc2 = rsqrtf(a.bc2);
+  // bias correction from the number of steps that were really applied: a step skipped on a
+  // gradient overflow does not advance it (the counter moves after all groups were updated)
+  const float t = (float)(applied_steps ? *applied_steps + 1 : a.step);
+  const float inv_bc1 = 1.f / (1.f - powf(a.beta1, t));
+  const float inv_sqrt_bc2 = rsqrtf(1.f - powf(a.beta2, t));
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
     float4 pg = reinterpret_cast<float4*>(g)[i];
     float4 pp = reinterpret_cast<float4*>(p)[i];
@@ -135,6 +138,11 @@ sgd_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ mom
   }
 }
 
+// applied-step counter of the Adam family: advances unless the step was skipped
+__global__ void step_advance_kernel(int* applied_steps, const float* found_inf) {
+  if (threadIdx.x == 0 && blockIdx.x == 0 && !(found_inf && *found_inf != 0.f)) *applied_steps += 1;
+}
+
 // scale update of dynamic loss scaling, entirely on the device:
 //   state = {scale, growth_tracker}; found_inf is reset afterwards
 __global__ void loss_scale_update_kernel(float* state, float* found_inf, float growth,
@@ -176,17 +184,23 @@ PF_API int pf_nonfinite(const void* g, long long n, void* found_inf, int sm_coun
 
 PF_API int pf_adamw(void* p, void* g, void* m, void* v, void* lp, long long n,
                     const void* found_inf, const void* loss_scale, float lr, float beta1, float beta2, float eps,
-                    float weight_decay, int step, float grad_scale, int adamw, int zero_grad,
-                    int lp_dtype, int sm_count, void* stream) {
+                    float weight_decay, int step, const void* applied_steps, float grad_scale,
+                    int adamw, int zero_grad, int lp_dtype, int sm_count, void* stream) {
   if (n <= 0) return 0;
   AdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
-  a.bc1 = 1.f - powf(beta1, (float)step);
-  a.bc2 = 1.f - powf(beta2, (float)step);
+  a.step = step;
   a.grad_scale = grad_scale; a.adamw = adamw; a.zero_grad = zero_grad; a.lp_dtype = lp_dtype;
   adamw_kernel<<<opt_grid(n, sm_count), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (float*)p, (float*)g, (float*)m, (float*)v, lp, n, (const float*)found_inf,
-      (const float*)loss_scale, a);
+      (const float*)loss_scale, (const int*)applied_steps, a);
+  PF_CHECK_LAUNCH();
+  return 0;
+}
+
+PF_API int pf_step_advance(void* applied_steps, const void* found_inf, void* stream) {
+  step_advance_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (int*)applied_steps, (const float*)found_inf);
   PF_CHECK_LAUNCH();
   return 0;
 }

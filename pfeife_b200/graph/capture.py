@@ -70,9 +70,45 @@ class CapturedGraph:
         return sum(1 for n in self.gm.graph.nodes if n.op in ("call_function", "call_method",
                                                                 "call_module"))
 
+    def shadow_only_inputs(self) -> set:
+        """Indices of the state placeholders that are read ONLY as the weight operand of the
+        native GEMM-like ops (linear, fused MLP, convolution, embedding).  Under mixed precision
+        those ops read the 16-bit shadow of the weight, never its fp32 master, so a
+        data-parallel rank that does not own such a parameter needs no current master copy of
+        it.  Anything else (biases, norm weights, position embeddings, a weight that an ATen op
+        touches) is read in fp32."""
+        out = set()
+        by_name = {n.name: n for n in self.gm.graph.nodes}
+        for gi in self.inputs:
+            if not gi.is_state:
+                continue
+            node = by_name.get(gi.node_name)
+            users = list(node.users) if node is not None else []
+            if users and all(_reads_shadow(u, node) for u in users):
+                out.add(gi.index)
+        return out
+
     def split_call_args(self, args: Sequence[Any]) -> List[Any]:
         """Runtime call arguments (in placeholder order) -> just the user inputs."""
         return [args[i.index] for i in self.inputs if i.kind == "input"]
+
+
+# op name -> positions of the weight operands that the op reads through the 16-bit shadow
+_SHADOW_OPERANDS = {"linear_fwd": (1,), "mlp_fwd": (1, 3), "conv2d_fwd": (1,), "embed_fwd": (1,)}
+
+
+def _reads_shadow(user: fx.Node, value: fx.Node) -> bool:
+    if user.op != "call_function":
+        return False
+    name = str(user.target)
+    if "pfeife" not in name:
+        return False
+    for op, positions in _SHADOW_OPERANDS.items():
+        if f"pfeife.{op}" in name or f"pfeife::{op}" in name:
+            uses = [i for i, a in enumerate(user.args) if a is value]
+            return bool(uses) and all(i in positions for i in uses) and \
+                value not in user.kwargs.values()
+    return False
 
 
 def _source_name(node: fx.Node) -> Optional[str]:

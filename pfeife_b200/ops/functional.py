@@ -728,7 +728,10 @@ def mse_loss(a: Tensor, b: Tensor) -> Tensor:
 def embed_fwd(ids: Tensor, table: Tensor, out_dtype: torch.dtype) -> Tensor:
     if table.is_cuda:
         t = table
-        if t.dtype != out_dtype and t.dtype != torch.float32:
+        s = _slot(table)
+        if s is not None and s.lp is not None and s.lp.dtype == out_dtype:
+            t = _weight_as(table, out_dtype)     # the 16-bit shadow: half the bytes, same values
+        elif t.dtype != out_dtype and t.dtype != torch.float32:
             t = t.float()
         return kx.embed_fwd(t, ids, out_dtype)
     return F.embedding(ids, table).to(out_dtype)

@@ -21,22 +21,68 @@ EW_DGELU, EW_DGELU_TANH, EW_DSILU = 10, 11, 12
 EW_ADD, EW_MUL, EW_SILU_MUL, EW_GELU_MUL = 20, 21, 30, 31
 
 _status = {}
+_status_host = {}
+STATUS_WORDS = 4     # [0] first error code, [1] wait limit in 1024-cycle units (0 = built-in)
+_STATUS_NAMES = {1: "TIMEOUT_FULL", 2: "TIMEOUT_EMPTY", 3: "TIMEOUT_TMEM_FULL",
+                 4: "TIMEOUT_TMEM_EMPTY", 5: "TIMEOUT_PEER_FLAG", 6: "BAD_ARG"}
+PF_ERR_TIMEOUT_PEER_FLAG = 5
 
 
 def status_word(device=None) -> torch.Tensor:
-    """int32[1] per device; kernels record the first bounded-wait failure here (0 = ok)."""
+    """int32[STATUS_WORDS] per device.  Kernels record the first bounded-wait failure in word 0
+    (0 = ok) and read their wait limit from word 1 (``set_wait_limit``); the environment
+    variable PF_WAIT_CYCLES presets that limit."""
     idx = torch.cuda.current_device() if device is None else torch.device(device).index
     if idx not in _status:
-        _status[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        t = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=f"cuda:{idx}")
+        import os
+        env = os.environ.get("PF_WAIT_CYCLES")
+        if env:
+            t[1] = max(1, int(float(env)) >> 10)
+        _status[idx] = t
     return _status[idx]
+
+
+def set_wait_limit(cycles: Optional[int], device=None) -> None:
+    """Bounds every in-kernel wait (mbarrier, peer flag) to about `cycles` SM clock cycles;
+    None restores the built-in limit (about a second)."""
+    status_word(device)[1] = 0 if not cycles else max(1, int(cycles) >> 10)
+
+
+def _raise_status(code: int) -> None:
+    raise _lib.KernelError(f"a kernel reported status {code} "
+                           f"({_STATUS_NAMES.get(code, '?')}: a bounded wait ran out)")
 
 
 def check_status(device=None) -> None:
     """Synchronising read of the status word; raises if any kernel gave up on a wait."""
-    code = int(status_word(device).item())
+    code = int(status_word(device)[0].item())
     if code != 0:
-        status_word(device).zero_()
-        raise _lib.KernelError(f"a kernel reported status {code} (bounded wait ran out)")
+        status_word(device)[0] = 0
+        _raise_status(code)
+
+
+def poll_status(device=None) -> None:
+    """The same check without stalling the host: every call raises if the copy started by the
+    PREVIOUS call shows a failure, then starts a new asynchronous copy of the status word to
+    pinned memory on the current stream.  Called once per training step, it reports a kernel
+    that gave up on a wait one step later."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    ent = _status_host.get(idx)
+    if ent is None:
+        ent = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+        _status_host[idx] = ent
+    if ent["event"] is not None:
+        ent["event"].synchronize()       # recorded a whole step ago: long since complete
+        code = int(ent["host"][0])
+        if code != 0:
+            ent["event"] = None
+            status_word(idx)[0] = 0
+            _raise_status(code)
+    ent["host"].copy_(status_word(idx)[:1], non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(idx))
+    ent["event"] = ev
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
@@ -222,15 +268,25 @@ def adamw(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *,
           beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
           grad_scale: float = 1.0, decoupled: bool = True, zero_grad: bool = True,
           lp: Optional[torch.Tensor] = None, found_inf: Optional[torch.Tensor] = None,
-          loss_scale: Optional[torch.Tensor] = None) -> None:
+          loss_scale: Optional[torch.Tensor] = None,
+          applied_steps: Optional[torch.Tensor] = None) -> None:
+    """`applied_steps` (int32 device scalar): when given, the bias correction uses its value + 1
+    instead of `step`; advance it with ``step_advance`` after every group was updated."""
     L = _lib.lib()
     for t in (p, g, m, v):
         assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == p.numel()
     check(L.pf_adamw(ptr(p), ptr(g), ptr(m), ptr(v), ptr(lp), c_ll(p.numel()), ptr(found_inf),
                      ptr(loss_scale), c_f(lr), c_f(beta1), c_f(beta2), c_f(eps),
-                     c_f(weight_decay), int(step), c_f(grad_scale), int(decoupled),
+                     c_f(weight_decay), int(step), ptr(applied_steps), c_f(grad_scale),
+                     int(decoupled),
                      int(zero_grad), dt(lp.dtype) if lp is not None else 0, sm_count(p.device),
                      stream()), "pf_adamw")
+
+
+def step_advance(applied_steps: torch.Tensor, found_inf: Optional[torch.Tensor]) -> None:
+    """applied_steps += 1 unless `found_inf` is set (the step was skipped)."""
+    L = _lib.lib()
+    check(L.pf_step_advance(ptr(applied_steps), ptr(found_inf), stream()), "pf_step_advance")
 
 
 def sgd(p: torch.Tensor, g: torch.Tensor, mom: Optional[torch.Tensor], *, lr: float,

@@ -5,7 +5,8 @@ rank that reads and writes the other ranks' buffers directly over NVLink (csrc/d
 Host side: the flat gradient / master / shadow buffers of ``RankParams`` are ordinary device
 allocations whose CUDA IPC handles are exchanged once over the control group; every rank maps
 its peers' buffers and keeps a table of peer pointers.  Optimizer moments exist only for the
-rank's own shard (ZeRO-1).  The kernel's cross-GPU barriers are epoch counters in a small
+rank's own shard (ZeRO-1), and so do current fp32 masters of the weights that are only ever read
+through their 16-bit shadow (``gather_master`` completes them for checkpoints).  The kernel's cross-GPU barriers are epoch counters in a small
 peer-visible flag buffer.
 
 Optimizers other than Adam / AdamW fall back to the NCCL path.
@@ -24,6 +25,7 @@ from ..ops._lib import c_f, c_ll, check, dt, ptr, sm_count, stream
 from .dp import NcclDP
 
 DP_MAX = 8
+DP_MAX_GROUPS = 8
 ALIGN = 128
 
 
@@ -147,6 +149,37 @@ def row_ends(offset: int, cols: int, rows: int, bounds: Sequence[int]) -> List[i
     return ends
 
 
+def launch_fused_step(rank: int, world: int, t_grad, t_master, t_lp, t_flags, m: torch.Tensor,
+                      v: torch.Tensor, local_sync: torch.Tensor, shard: Tuple[int, int],
+                      total: int, groups: Sequence[Tuple[int, int, int, int]],
+                      hyper: Sequence[Tuple[float, float, float, float, float, bool]],
+                      applied_steps: Optional[torch.Tensor], host_step: int, grad_scale: float,
+                      lp_dtype: Optional[torch.dtype], check_inf: bool, found_given: bool,
+                      loss_scale: Optional[torch.Tensor], found_inf: torch.Tensor, epoch: int,
+                      arrivals: int, device) -> Tuple[int, int]:
+    """One launch of the fused kernel on the current stream.  `t_*` are pointer tables
+    (``_table``) with one entry per rank; `groups` holds (lo, hi, local_below, master_from) and
+    `hyper` (lr, beta1, beta2, eps, weight_decay, adamw) per optimizer group.  Returns
+    (barriers used, grid size): the caller adds them to its running epoch / arrival counts,
+    which must be the same on every rank."""
+    L = _lib.lib()
+    flat_g = [int(x) for g in groups for x in g]
+    flat_h = [float(x) for h in hyper for x in h]
+    c_groups = (ctypes.c_longlong * len(flat_g))(*flat_g)
+    c_hyper = (ctypes.c_float * len(flat_h))(*flat_h)
+    nbar, grid = ctypes.c_int(0), ctypes.c_int(0)
+    code = L.pf_dp_fused_step(
+        int(rank), int(world), t_grad, t_master, t_lp, t_flags, ptr(m), ptr(v), ptr(local_sync),
+        c_ll(shard[0]), c_ll(shard[1]), c_ll(total), len(groups), c_groups, c_hyper,
+        ptr(applied_steps), int(host_step), c_f(grad_scale),
+        dt(lp_dtype) if lp_dtype is not None else 0, int(check_inf), int(found_given),
+        ptr(loss_scale), ptr(found_inf), int(epoch) & 0x7FFFFFFF, int(arrivals) & 0x7FFFFFFF,
+        ctypes.byref(nbar), ctypes.byref(grid), ptr(kx.status_word(device)), sm_count(device),
+        stream())
+    check(code, "pf_dp_fused_step")
+    return nbar.value, grid.value
+
+
 class FusedDP(NcclDP):
     fused = True
 
@@ -163,7 +196,8 @@ class FusedDP(NcclDP):
     def attach(self, params) -> None:
         super().attach(params)          # replicas start from dp rank 0's values
         self.params = params
-        if params.optimizer_type not in ("adam", "adamw") or not params.numel:
+        if params.optimizer_type not in ("adam", "adamw") or not params.numel or \
+                not params.native or len(params.group_ranges) > DP_MAX_GROUPS:
             self.fused = False
             return
         n = params.numel
@@ -175,9 +209,15 @@ class FusedDP(NcclDP):
         ln = max(self.shard[1] - self.shard[0], 4)
         self.m = torch.zeros(ln, dtype=torch.float32, device=self.device)
         self.v = torch.zeros(ln, dtype=torch.float32, device=self.device)
-        params.dp_state = self      # checkpoints read / restore the sharded moments through us
+        params.dp_state = self      # checkpoints read / restore the sharded state through us
         self.flags = torch.zeros(2 * DP_MAX, dtype=torch.int32, device=self.device)
-        self.local_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.local_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # barrier bookkeeping, identical on every rank: epoch of the next call's first barrier
+        # and the arrivals counted so far (both wrap; the kernel compares modulo 2^32)
+        self.epoch, self.arrivals = 1, 0
+        # fp32 masters are pushed to the peers only where some op reads them in fp32; without a
+        # 16-bit shadow everything is read in fp32
+        self.master_from = dict(params.master_from) if params.lp is not None else {}
         torch.cuda.synchronize(self.device)
         self.t_grad = _table(self.peers.share(params.grad))
         self.t_master = _table(self.peers.share(params.master))
@@ -197,34 +237,46 @@ class FusedDP(NcclDP):
                 Fn.set_gather(s.master, Fn.GatherInfo(copies, ends, self.size, self.rank, ready))
         dist.barrier(group=self.state.ctrl_dp)
 
-    def reduce_and_step(self, params, scaler, fp16: bool) -> None:
-        L = _lib.lib()
+    def reduce_and_step(self, params, scaler, fp16: bool, found_agreed: bool = False) -> None:
+        """One launch for the whole bucket (every optimizer group).  With ``found_agreed`` the
+        non-finite decision in ``params.found_inf`` was already agreed over the whole job and
+        the kernel only reads it; otherwise, under fp16, the replicas agree inside the kernel
+        (enough for a job that is one pipeline stage wide)."""
         params.step_count += 1
-        lo_s, hi_s = self.shard
+        adamw = params.optimizer_type == "adamw"
+        groups, hyper = [], []
         for g, lo, hi in params.group_ranges:
             h = params.hyper[min(g, len(params.hyper) - 1)]
-            a, b = max(lo, lo_s), min(hi, hi_s)
-            if b < a:
-                a = b = lo       # nothing of this group is owned here: only clear its gradients
             b1, b2 = h.get("betas", (0.9, 0.999))
-            adamw = params.optimizer_type == "adamw"
-            off = max(a - lo_s, 0)
-            m = self.m[off:] if off < self.m.numel() else self.m
-            v = self.v[off:] if off < self.v.numel() else self.v
-            code = L.pf_dp_fused_step(
-                self.rank, self.size, self.t_grad, self.t_master, self.t_lp, self.t_flags,
-                ptr(m), ptr(v), ptr(self.local_sync), c_ll(a), c_ll(b),
-                c_ll(self.deferred_below.get(g, 0)), c_ll(lo), c_ll(hi), c_f(h.get("lr", 1e-3)),
-                c_f(b1), c_f(b2), c_f(h.get("eps", 1e-8)),
-                c_f(h.get("weight_decay", 0.01 if adamw else 0.0)), int(params.step_count),
-                c_f(1.0 / self.size), int(adamw),
-                dt(params.lp.dtype) if params.lp is not None else 0, int(fp16),
-                ptr(scaler.scale_tensor), ptr(params.found_inf), 3 * self.calls + 1, self.calls,
-                ptr(kx.status_word(self.device)), sm_count(self.device), stream())
-            check(code, "pf_dp_fused_step")
-            self.calls += 1
+            groups.append((lo, hi, self.deferred_below.get(g, lo), self.master_from.get(g, lo)))
+            hyper.append((h.get("lr", 1e-3), b1, b2, h.get("eps", 1e-8),
+                          h.get("weight_decay", 0.01 if adamw else 0.0), adamw))
+        nbar, grid = launch_fused_step(
+            self.rank, self.size, self.t_grad, self.t_master, self.t_lp, self.t_flags, self.m,
+            self.v, self.local_sync, self.shard, params.numel, groups, hyper,
+            params.applied_steps, params.step_count, 1.0 / self.size,
+            params.lp.dtype if params.lp is not None else None,
+            check_inf=bool(fp16 and not found_agreed), found_given=bool(fp16 and found_agreed),
+            loss_scale=scaler.scale_tensor, found_inf=params.found_inf, epoch=self.epoch,
+            arrivals=self.arrivals, device=self.device)
+        self.epoch += nbar
+        self.arrivals += nbar * grid
+        self.calls += 1
+        kx.step_advance(params.applied_steps, params.found_inf if fp16 else None)
         if fp16:
             scaler.update(params.found_inf)
+
+    def gather_master(self) -> None:
+        """Makes every replica's fp32 master buffer complete (for checkpoints): between steps a
+        rank holds current masters only for its own shard, plus the small fp32-read tail of each
+        group that the step pushes everywhere."""
+        p = self.params
+        if p is None or not self.fused or not p.numel:
+            return
+        for r in range(self.size):
+            lo, hi = self.bounds[r], self.bounds[r + 1]
+            if hi > lo:
+                dist.broadcast(p.master[lo:hi], self.state.dp_group_ranks[r], group=self.group)
 
     def gather_optimizer_state(self) -> Dict[str, torch.Tensor]:
         """Full-length moments assembled from every rank's shard (for checkpoints)."""

@@ -96,6 +96,9 @@ class _LocalControl:
     def barrier(self) -> None:
         return
 
+    def share_with_replicas(self, obj: Any = None) -> Any:
+        return obj       # one pipeline, no replicas
+
 
 class LocalRunner(PartialRunner):
     """``PartialRunner`` over devices of this process (``option.device_map``, or CPU threads

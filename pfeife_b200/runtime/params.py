@@ -56,6 +56,9 @@ class StateEntry:
     tensor: torch.Tensor      # initial value (any device)
     requires_grad: bool
     group: int = 0            # index into the user's optimizer.param_groups
+    # True: every op that reads this parameter reads its 16-bit shadow (a weight of linear /
+    # conv / embedding); False: some op reads the fp32 value; None: not analysed
+    lp_only: Optional[bool] = None
 
 
 @dataclass
@@ -85,17 +88,30 @@ class RankParams:
         self.optimizer_type = optimizer_type.lower()
         self.hyper = [dict(h) for h in hyper] or [{}]
         self.native = (device.type == "cuda") if native is None else native
+        if any(h.get("amsgrad") or h.get("maximize") for h in self.hyper):
+            self.native = False      # variants the native kernels do not implement
         self.step_count = 0
+        # optimizer steps that were applied (not skipped on an overflow): drives Adam's bias
+        # correction on the device
+        self.applied_steps = torch.zeros(1, dtype=torch.int32, device=device) \
+            if device.type == "cuda" else None
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
 
         packed = [e for e in entries if e.kind == "param" and e.requires_grad
                   and e.tensor.dtype.is_floating_point]
         defer = bool(defer_gather and lp_dtype is not None and self.native)
-        deferrable = (lambda e: defer and gather_deferrable(e.tensor))
-        packed.sort(key=lambda e: (e.group, not deferrable(e), e.ph_index))
+        deferrable = (lambda e: defer and gather_deferrable(e.tensor) and e.lp_only is not False)
+        # Within a group: first the matrices whose all-gather is deferred, then the other weights
+        # that are only read through their shadow, then what some op reads in fp32.  The fused
+        # data-parallel step pushes fp32 masters to the replicas only from `master_from` on; a
+        # group with a parameter that was not analysed is pushed as a whole.
+        shadow_only = (lambda e: e.lp_only is True and lp_dtype is not None)
+        packed.sort(key=lambda e: (e.group, not deferrable(e), not shadow_only(e), e.ph_index))
         self.slots: Dict[int, _Slot] = {}
         self.group_ranges: List[Tuple[int, int, int]] = []   # (group, lo, hi)
         self.deferred_below: Dict[int, int] = {}             # group -> end of its deferred region
+        self.master_from: Dict[int, int] = {}                # group -> start of its fp32-read tail
+        unknown = {e.group for e in packed if e.lp_only is None}
         off = 0
         cur_group, group_lo = None, 0
         for e in packed:
@@ -104,11 +120,14 @@ class RankParams:
                     self.group_ranges.append((cur_group, group_lo, off))
                 cur_group, group_lo = e.group, off
                 self.deferred_below[e.group] = off
+                self.master_from[e.group] = off
             n = e.tensor.numel()
             self.slots[e.ph_index] = _Slot(e, off, n, deferred=deferrable(e))
             off += (n + ALIGN - 1) // ALIGN * ALIGN
             if deferrable(e):
                 self.deferred_below[e.group] = off
+            if shadow_only(e) and e.group not in unknown:
+                self.master_from[e.group] = off
         if cur_group is not None:
             self.group_ranges.append((cur_group, group_lo, off))
         self.numel = off
@@ -215,6 +234,11 @@ class RankParams:
 
     def _step_native(self, kind, grad_scale, loss_scale, use_found_inf, shard) -> None:
         found = self.found_inf if use_found_inf else None
+        self._step_groups(kind, grad_scale, loss_scale, found, shard)
+        if kind in ("adam", "adamw"):
+            kx.step_advance(self.applied_steps, found)
+
+    def _step_groups(self, kind, grad_scale, loss_scale, found, shard) -> None:
         for g, lo, hi in self._ranges(shard):
             h = self.hyper[min(g, len(self.hyper) - 1)]
             p, gr = self.master[lo:hi], self.grad[lo:hi]
@@ -226,7 +250,7 @@ class RankParams:
                          weight_decay=h.get("weight_decay", 0.01 if kind == "adamw" else 0.0),
                          step=self.step_count, grad_scale=grad_scale,
                          decoupled=(kind == "adamw"), zero_grad=True, lp=lp, found_inf=found,
-                         loss_scale=loss_scale)
+                         loss_scale=loss_scale, applied_steps=self.applied_steps)
             else:
                 mom = h.get("momentum", 0.0)
                 kx.sgd(p, gr, self._state("momentum")[lo:hi] if mom else None,
@@ -248,6 +272,8 @@ class RankParams:
                 groups.setdefault(s.entry.group, []).append(p)
             cls = get_optimizer_cls(self.optimizer_type)
             pg = []
+            # this rank may hold only some of the user's groups: remember which
+            self._torch_group_ids = sorted(groups)
             for g in sorted(groups):
                 h = {k: v for k, v in self.hyper[min(g, len(self.hyper) - 1)].items()
                      if k in _HYPER_KEYS or k in ("foreach", "fused", "capturable",
@@ -258,7 +284,7 @@ class RankParams:
                 self._apply_torch_state(self._pending_opt_state)
                 self._pending_opt_state = None
         for i, g in enumerate(self._torch_opt.param_groups):
-            h = self.hyper[min(i, len(self.hyper) - 1)]
+            h = self.hyper[min(self._torch_group_ids[i], len(self.hyper) - 1)]
             for k in _HYPER_KEYS:
                 if k in h and k in g:
                     g[k] = h[k]
@@ -279,10 +305,25 @@ class RankParams:
     # ------------------------------------------------------------------ checkpoint
     def named_tensors(self) -> Dict[str, torch.Tensor]:
         """qualified name -> current full-precision value (for gather_params / state_dict)."""
+        if self.dp_state is not None and getattr(self.dp_state, "fused", False):
+            self.dp_state.gather_master()    # a collective: all replicas checkpoint together
         out = {}
         for s in self.slots.values():
             out[s.entry.qualname] = (s.master if s.offset >= 0 else s.view).detach()
         return out
+
+    def optimizer_steps(self) -> int:
+        """Steps that count for Adam's bias correction: on the native path the device counter
+        (skipped steps excluded), else the host's count."""
+        if self.applied_steps is not None and self.native and \
+                self.optimizer_type in ("adam", "adamw"):
+            return int(self.applied_steps.item())
+        return self.step_count
+
+    def _set_optimizer_steps(self, n: int) -> None:
+        self.step_count = int(n)
+        if self.applied_steps is not None:
+            self.applied_steps.fill_(int(n))
 
     def optimizer_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
         """qualified name -> {state name -> tensor}, keyed like torch's per-parameter state."""
@@ -291,6 +332,7 @@ class RankParams:
         # full-length copies (a collective over the replicas, which all take checkpoints together)
         flats = self.dp_state.gather_optimizer_state() \
             if (self.dp_state is not None and getattr(self.dp_state, "fused", False)) else None
+        steps = self.optimizer_steps()
         for s in self.packed_slots():
             if flats is not None:
                 st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
@@ -309,7 +351,7 @@ class RankParams:
             else:
                 st = {k: v[s.offset:s.offset + s.numel].view(s.entry.tensor.shape).detach().clone()
                       for k, v in self.opt_state.items()}
-            st["step"] = torch.tensor(float(self.step_count))
+            st["step"] = torch.tensor(float(steps))
             out[s.entry.qualname] = st
         return out
 
@@ -339,7 +381,7 @@ class RankParams:
                     continue
                 for k, v in st.items():
                     if k == "step":
-                        self.step_count = int(float(v))
+                        self._set_optimizer_steps(int(float(v)))
                         continue
                     if k not in flats:
                         flats[k] = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
@@ -362,7 +404,7 @@ class RankParams:
                 continue
             for k, v in st.items():
                 if k == "step":
-                    self.step_count = int(float(v))
+                    self._set_optimizer_steps(int(float(v)))
                     continue
                 self._state(k)[s.offset:s.offset + s.numel].copy_(v.reshape(-1))
 

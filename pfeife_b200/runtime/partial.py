@@ -173,6 +173,8 @@ def worker_loop(option: Optional[PipeOption] = None) -> None:
             named = {k: v.cpu() for k, v in worker.params.named_tensors().items()}
             opt = {k: {kk: vv.cpu() for kk, vv in st.items()}
                    for k, st in worker.params.optimizer_state().items()} if msg.get("opt") else {}
+            if msg.get("opt") and worker.scaler.enabled:
+                opt[SCALER_KEY] = worker.scaler.state_dict()
             ctrl.gather((named, opt))
         elif flag == LoopFlag.LOAD_PARAMS:
             worker.params.load_named(msg["named"])
@@ -300,6 +302,7 @@ class PartialModule(torch.nn.Module):
         hyper = snapshot_hyper(optimizer) if optimizer is not None else \
             [dict(opt.optimizer_kwargs)]
         opt_type = type(optimizer).__name__ if optimizer is not None else opt.optimizer_type
+        shadow_only = self.captured.shadow_only_inputs()
         payloads = []
         for rank in range(pp):
             entries = []
@@ -309,7 +312,7 @@ class PartialModule(torch.nn.Module):
                 entries.append(StateEntry(ph, gi.qualname, gi.kind,
                                           t.detach() if rank == state.pp_rank else t.detach().cpu(),
                                           bool(gi.kind == "param" and t.requires_grad),
-                                          group_of.get(id(t), 0)))
+                                          group_of.get(id(t), 0), lp_only=(ph in shadow_only)))
             payloads.append({"part": part.for_rank(rank), "entries": entries,
                              "optimizer_type": opt_type, "hyper": hyper, "steps": steps,
                              "eval_steps": eval_steps, "batch_cnt": opt.batch_cnt})
@@ -546,15 +549,22 @@ class PartialRunner:
         gathered = self.ctrl.gather((named, opt)) if self.state.pp_size > 1 else [(named, opt)]
         all_named: Dict[str, torch.Tensor] = {}
         all_opt: Dict[str, Dict[str, torch.Tensor]] = {}
+        mine = self.worker.scaler.state_dict() if self.worker.scaler.enabled else None
         for item in gathered:
             if item is None:
                 continue
             all_named.update(item[0])
+            theirs = item[1].pop(SCALER_KEY, None) if isinstance(item[1], dict) else None
+            if theirs is not None and mine is not None and \
+                    float(theirs["scale"]) != float(mine["scale"]):
+                raise RuntimeError(
+                    f"the loss scale differs between pipeline ranks ({float(theirs['scale'])} vs "
+                    f"{float(mine['scale'])}): a rank skipped a step that another applied")
             all_opt.update(item[1])
         all_named.update(named)
         all_opt.update(opt)
-        if with_optimizer and self.worker.scaler.enabled:
-            all_opt[SCALER_KEY] = self.worker.scaler.state_dict()   # one scale for the whole job
+        if with_optimizer and mine is not None:
+            all_opt[SCALER_KEY] = mine      # one scale for the whole job
         with torch.no_grad():
             for m in self.modules:
                 if not m.should_pp:

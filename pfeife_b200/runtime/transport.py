@@ -138,6 +138,9 @@ class _LocalRecv(Handle):
 
     def wait(self) -> None:
         if self.done:
+            # completed while another handle of the channel was being waited for: the copy is
+            # queued on the side stream, and the consumer's stream still has to wait for it
+            self._join_stream()
             return
         t = self.t
         # receives on a channel complete in posting order
@@ -159,8 +162,12 @@ class _LocalRecv(Handle):
                 head.event = None
             head.done = True
             pend.pop(0)
-        if getattr(self, "event", None) is not None:
-            torch.cuda.current_stream(self.buf.device).wait_event(self.event)
+        self._join_stream()
+
+    def _join_stream(self) -> None:
+        ev = getattr(self, "event", None)
+        if ev is not None:
+            torch.cuda.current_stream(self.buf.device).wait_event(ev)
 
 
 class LocalTransport(Transport):

@@ -126,12 +126,14 @@ class CommPlan:
                         if rank_of(inp.src_stage) == rank:
                             self.need_at.setdefault((int(StepWork.RECV_GRAD), inp.src_stage,
                                                      st.batch_id), []).append(m)
+        self.recv_pos: Dict[int, Dict[MsgKey, int]] = {}   # src rank -> message key -> position
         for (a, b), msgs in fifo.items():
             self.channels.append((a, b))
             if a == rank:
                 self.channel_send[b] = msgs
             if b == rank:
                 self.channel_recv[a] = msgs
+                self.recv_pos[a] = {m.key: i for i, m in enumerate(msgs)}
 
 
 def _lib_add(n: int) -> None:
@@ -212,6 +214,8 @@ class StageWorker:
         self.graph_key: Dict[Tuple[int, int], Tuple[int, int, int]] = {}
         # stages whose row-sharded weights were completed since the last optimizer step
         self.gathered_stages: set = set()
+        # True when the job has more ranks than this stage's replicas (set by the front-end)
+        self.inf_sync_job_wide = pp_size > 1
         self.train_steps_done = 0
         self._reset_step_state()
 
@@ -252,6 +256,7 @@ class StageWorker:
             self.eval_comm = CommPlan(self.part, eval_steps_by_rank, self.batch_cnt,
                                       self.pp_rank, self.main_rank, training=False)
         self.recv_bufs: Dict[MsgKey, torch.Tensor] = {}
+        self.zero_bufs: Dict[MsgKey, torch.Tensor] = {}
         self.slot_of, _ = inflight_slots(self.steps)
         if self.transport is not None:
             g = self.global_ranks
@@ -286,12 +291,7 @@ class StageWorker:
         """Posts the receives of channel src->me in FIFO order up to `msg` plus look-ahead."""
         fifo = comm.channel_recv[src]
         cur = self.recv_cursor.get(src, 0)
-        # position of msg in the FIFO (search forward from the cursor; it is rarely far)
-        want = None
-        for i in range(len(fifo)):
-            if fifo[i].key == msg.key:
-                want = i
-                break
+        want = comm.recv_pos[src].get(msg.key)
         assert want is not None, f"message {msg.key} not on channel {src}->{self.pp_rank}"
         upto = min(len(fifo), max(cur, want + 1 + self.recv_lookahead))
         g = self.global_ranks
@@ -504,10 +504,20 @@ class StageWorker:
         sp = self.part.stages[stage]
         outs = self.fw_outputs.pop((stage, mb))
         grads_by_out: Dict[int, torch.Tensor] = {}
+        owned: set = set()      # outputs whose running sum lives in one of our receive buffers
         for m in comm.need_at.get((int(StepWork.RECV_GRAD), stage, mb), []):
             g = self._take(m)
             j = m.key[2]
-            grads_by_out[j] = g if j not in grads_by_out else grads_by_out[j] + g
+            if j not in grads_by_out:
+                grads_by_out[j] = g
+                if m.src_rank != m.dst_rank:
+                    owned.add(j)
+            elif j in owned and grads_by_out[j].dtype == g.dtype:
+                # an output with several consumers: sum in place in the first receive buffer
+                # (it is ours until the next step's receive overwrites it)
+                grads_by_out[j].add_(g)
+            else:
+                grads_by_out[j] = grads_by_out[j] + g
         if any(c[0] == OUTSIDE for o in sp.outputs for c in o.consumers):
             ev = self.bw_events.get(mb)
             if ev is not None:
@@ -550,8 +560,11 @@ class StageWorker:
         for m in comm.send_at.get((int(StepWork.SEND_GRAD), stage, mb), []):
             t = ins[m.key[4]]
             g = t.grad if torch.is_tensor(t) else None
-            if g is None:
-                g = torch.zeros(m.meta.size, dtype=m.meta.dtype, device=self.device)
+            if g is None:      # the stage did not use this input: its gradient is zero
+                g = self.zero_bufs.get(m.key)
+                if g is None:
+                    g = torch.zeros(m.meta.size, dtype=m.meta.dtype, device=self.device)
+                    self.zero_bufs[m.key] = g
             self._send(m, g)
 
     # ------------------------------------------------------------------ optimizer step
@@ -593,7 +606,15 @@ class StageWorker:
         grad_scale = 1.0
         fp16 = self.scaler.enabled
         if self.dp is not None and self.dp.fused:
-            self.dp.reduce_and_step(self.params, self.scaler, fp16)
+            agreed = False
+            if fp16 and self.inf_sync_job_wide:
+                # a pipeline of several ranks: the skip decision must be the same on every rank
+                # of the job, not only among the replicas of this stage.  A non-finite term
+                # makes the reduced sum non-finite, so the local buckets decide.
+                self.params.check_finite()
+                self.sync_found_inf()
+                agreed = True
+            self.dp.reduce_and_step(self.params, self.scaler, fp16, found_agreed=agreed)
             self.gathered_stages.clear()    # 16-bit weight matrices are row-sharded again
             return
         if self.dp is not None:
@@ -639,6 +660,11 @@ class StageWorker:
                 elif w == StepWork.OPTIMIZER_STEP and training:
                     self.optimizer_step()
                     self.train_steps_done += 1
+                    if nvtx and self.params is not None and self.params.native:
+                        # a kernel that gave up on a bounded wait (a replica that is late or
+                        # gone) ends the job here, one step later, without a host sync per step
+                        from ..ops import kernels as kx
+                        kx.poll_status(self.device)
                 if nvtx:
                     torch.cuda.nvtx.range_pop()
         if not training:

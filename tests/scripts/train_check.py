@@ -78,6 +78,11 @@ def main():
     ap.add_argument("--fail_rank", type=int, default=-1,
                     help="this global rank raises an exception on the host before its first step "
                          "(failure-detection test; no device work is in flight)")
+    ap.add_argument("--inject_inf", type=int, default=-1,
+                    help="at this step the first replica's inputs are infinite, so its "
+                         "gradients overflow (dynamic loss scaling must skip the step everywhere)")
+    ap.add_argument("--two_groups", action="store_true",
+                    help="matrices and vectors in two optimizer groups")
     ap.add_argument("--skew_profile", action="store_true",
                     help="every rank that profiles gets segment times of its own (seeded by its "
                          "rank), as timing noise on real devices would give it")
@@ -111,9 +116,16 @@ def main():
     ref = copy.deepcopy(model)
     dev = state.device
     model.to(dev)
-    mk = lambda m: (torch.optim.SGD(m.parameters(), lr=args.lr) if args.optimizer == "sgd" else
-                    torch.optim.AdamW(m.parameters(), lr=args.lr, weight_decay=0.01)
-                    if args.optimizer == "adamw" else torch.optim.Adam(m.parameters(), lr=args.lr))
+    def param_sets(m):
+        if not args.two_groups:
+            return m.parameters()
+        ps = list(m.parameters())
+        return [{"params": [p for p in ps if p.dim() >= 2]},
+                {"params": [p for p in ps if p.dim() < 2], "weight_decay": 0.0}]
+
+    mk = lambda m: (torch.optim.SGD(param_sets(m), lr=args.lr) if args.optimizer == "sgd" else
+                    torch.optim.AdamW(param_sets(m), lr=args.lr, weight_decay=0.01)
+                    if args.optimizer == "adamw" else torch.optim.Adam(param_sets(m), lr=args.lr))
     opt, ropt = mk(model), mk(ref)
     sched = torch.optim.lr_scheduler.StepLR(opt, 1, gamma=0.5)
     rsched = torch.optim.lr_scheduler.StepLR(ropt, 1, gamma=0.5)
@@ -123,7 +135,7 @@ def main():
 
     def exec_fn(*batch):
         loss = loss_fn(cm, *batch)
-        loss.backward()
+        runner.scaler.scale(loss).backward()
         return loss.detach().cpu()
 
     runner.set_exec_fn(exec_fn)
@@ -132,6 +144,8 @@ def main():
     losses, ref_losses = [], []
     for step in range(args.steps):
         batch = make_batch(n, g)
+        if step == args.inject_inf and state.dp_rank == 0:
+            batch = tuple(t * float("inf") if t.is_floating_point() else t for t in batch)
         out = runner.step(*[t.to(dev) for t in batch])
         losses.append([float(l) for l in out])
         sched.step()
@@ -176,6 +190,11 @@ def main():
             diff = max(diff, float((p.detach().cpu() - q.detach()).abs().max()))
     result["param_diff"] = diff
     result["opt_state_keys"] = sorted(opt_state.keys())[:3] if opt_state else []
+    if opt_state:
+        result["opt_steps"] = sorted({int(float(st["step"])) for k, st in opt_state.items()
+                                      if isinstance(st, dict) and "step" in st})
+        sc = opt_state.get("__loss_scaler__")
+        result["loss_scale"] = float(sc["scale"]) if sc else None
     result["split_points"] = [list(m.plan.split_points) for m in runner.modules
                               if m.plan is not None]
     result["state_dict_keys"] = len(model.state_dict())

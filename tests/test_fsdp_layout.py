@@ -56,6 +56,52 @@ def test_deferrable_matrices_are_packed_first_within_a_group():
     assert q.slots[0].offset == 0 and not q.slots[1].deferred
 
 
+def test_weights_read_through_their_shadow_precede_the_fp32_read_tail():
+    """The fused data-parallel step pushes fp32 masters to the replicas only from
+    ``master_from`` on: weights that every op reads through the 16-bit shadow are packed before
+    what some op reads in fp32; a group with a parameter nobody analysed is pushed whole."""
+    big = torch.zeros(512, 512)
+    mk = lambda lp: [StateEntry(0, "bias", "param", torch.zeros(512), True, 0, lp_only=False),
+                     StateEntry(1, "w1", "param", big.clone(), True, 0, lp_only=True),
+                     StateEntry(2, "pos", "param", torch.zeros(1, 4, 512), True, 0, lp_only=False),
+                     StateEntry(3, "conv", "param", torch.zeros(8, 4, 3, 3), True, 0, lp_only=True),
+                     StateEntry(4, "w2", "param", big.clone(), True, 1, lp_only=lp)]
+    p = RankParams(mk(True), torch.device("cpu"), torch.bfloat16, "adamw", [{}, {}], native=True)
+    order = sorted((s.offset, s.entry.qualname) for s in p.packed_slots())
+    assert [n for _, n in order] == ["w1", "conv", "bias", "pos", "w2"]
+    assert p.master_from[0] == p.slots[0].offset         # the tail starts at the first fp32 read
+    g1 = [(lo, hi) for g, lo, hi in p.group_ranges if g == 1][0]
+    assert p.master_from[1] == g1[1]                     # nothing of group 1 is read in fp32
+    q = RankParams(mk(None), torch.device("cpu"), torch.bfloat16, "adamw", [{}, {}], native=True)
+    g1 = [(lo, hi) for g, lo, hi in q.group_ranges if g == 1][0]
+    assert q.master_from[1] == g1[0]                     # not analysed: pushed as a whole
+    # deferral (row-sharded weights) never applies to a weight that some op reads in fp32
+    e = mk(True)
+    e[1].lp_only = False
+    r = RankParams(e, torch.device("cpu"), torch.bfloat16, "adamw", [{}, {}], native=True,
+                   defer_gather=True)
+    assert not r.slots[1].deferred and r.slots[4].deferred
+    # without a shadow every master is read directly
+    f = RankParams(mk(True), torch.device("cpu"), None, "adamw", [{}, {}], native=True)
+    assert f.master_from[0] == 0
+
+
+def test_torch_optimizer_groups_keep_their_own_hyper_parameters():
+    """A pipeline rank that holds only parameters of the user's SECOND group must step them
+    with that group's learning rate."""
+    entries = [StateEntry(0, "w", "param", torch.ones(4), True, 1)]
+    hyper = [{"lr": 1.0}, {"lr": 0.25}]
+    p = RankParams(entries, torch.device("cpu"), None, "sgd", hyper, native=False)
+    p.slots[0].grad.fill_(1.0)
+    p.step()
+    assert torch.allclose(p.slots[0].master, torch.full((4,), 0.75))
+    hyper[1]["lr"] = 0.5
+    p.set_hyper(hyper)
+    p.slots[0].grad.fill_(1.0)
+    p.step()
+    assert torch.allclose(p.slots[0].master, torch.full((4,), 0.25))
+
+
 def test_weights_are_gathered_once_per_gather_session():
     from pfeife_b200.ops import functional as Fn
     w = torch.zeros(256, 1024)

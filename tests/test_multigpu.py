@@ -70,6 +70,37 @@ def test_row_sharded_weights_match_replicated_weights(tmp_path, graphs):
         assert a == pytest.approx(b, rel=1e-3, abs=1e-3)
 
 
+def _overflow_run(tmp_path, world, mesh, device_cnt):
+    res, out = launch(tmp_path, world, ["--model", "vit_small", "--device_cnt", str(device_cnt),
+                                        "--batch_size", "4", "--batch_cnt", "2", "--steps", "3",
+                                        "--optimizer", "adamw", "--lr", "0.001",
+                                        "--mixed_precision", "fp16", "--two_groups",
+                                        "--inject_inf", "1"], dp_mesh=mesh, tag="ovf")
+    with open(out + ".dp0") as f:
+        other = json.load(f)
+    for r in (res, other):
+        # the overflowing step was skipped by every parameter of both groups on every rank
+        assert r["opt_steps"] == [2], r["opt_steps"]
+        assert r["loss_scale"] == 32768.0
+    assert res["param_checksum"] == pytest.approx(other["param_checksum"], rel=1e-7)
+
+
+def test_overflow_on_one_replica_skips_both_groups_on_both_replicas(tmp_path):
+    """fp16, two optimizer groups, fused data parallelism: one replica's gradients overflow in
+    step 1.  Both replicas skip that step for BOTH groups, halve the scale once and keep
+    identical weights; Adam's step count leaves the skipped step out."""
+    _overflow_run(tmp_path, 2, "-2,1", 1)
+
+
+def test_overflow_is_agreed_over_pipeline_and_replicas(tmp_path):
+    """The same with two pipeline stages per replica (PP2 x DP2): the stage that did not
+    overflow itself skips too, and every rank keeps the same scale."""
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 CUDA devices")
+    _overflow_run(tmp_path, 4, "-2,2", 2)
+
+
 def test_checkpoint_resume_under_fused_dp(tmp_path):
     """The fused data-parallel step keeps Adam moments only on the rank that owns each shard;
     a checkpoint assembles them and a restore hands every rank its shard back: the two steps
