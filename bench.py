@@ -143,40 +143,53 @@ def _to_compute(t, dtype):
 
 
 def _planned_mesh(args, wl, world, rank, cpu):
-    """The PP x DP mesh for `world` GPUs, chosen by the planner: rank 0 profiles one micro-batch
-    of the model on its GPU and evaluates every factorisation of the world size; the others read
-    its answer from a key-value store (the process groups do not exist yet -- they depend on
-    the answer).  Falls back to pure data parallelism if planning fails on rank 0."""
+    """The PP x DP mesh for `world` GPUs, chosen by the planner.  The job's default process
+    group is created first and two of its ranks measure the link (latency and bandwidth of
+    point-to-point transfers, the ``--device_bench`` measurement); rank 0 then profiles one
+    micro-batch of the model on its GPU, evaluates every factorisation of the world size with
+    the measured link and broadcasts its choice.  Falls back to pure data parallelism if
+    planning fails on rank 0."""
     import datetime
     import torch
     import torch.distributed as dist
-    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
-    port = int(os.environ.get("MASTER_PORT", "29500")) + 17
-    store = dist.TCPStore(host, port, world, is_master=(rank == 0),
-                          timeout=datetime.timedelta(seconds=1200))
+    from pfeife_b200.parallel.device_bench import NCCLDeviceBench
+    dev = torch.device("cpu") if cpu else torch.device(
+        "cuda", int(os.environ.get("LOCAL_RANK", "0")) % max(1, torch.cuda.device_count()))
+    if not cpu:
+        torch.cuda.set_device(dev)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "24446")
+        kw = {} if cpu else {"device_id": dev}
+        dist.init_process_group("gloo" if cpu else "nccl", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=1800), **kw)
+    link = None
+    if not cpu:
+        bench = NCCLDeviceBench(rank, list(range(world)), dev, dist.group.WORLD)
+        bench.run_bench(args.device_bench, uniform=True)
+        if bench.params:
+            link = tuple(float(v) for v in next(iter(bench.params.values())))
+    box = [None]
     if rank == 0:
-        mesh, table = f"-{world},1", None
+        mesh, table, pred = f"-{world},1", None, None
         try:
             from pfeife_b200 import PipeOption
-            from pfeife_b200.parallel.mesh_plan import plan_mesh
-            dev = torch.device("cpu") if cpu else torch.device(
-                "cuda", int(os.environ.get("LOCAL_RANK", "0")))
-            if not cpu:
-                torch.cuda.set_device(dev)
+            from pfeife_b200.parallel.mesh_plan import NVSWITCH_LINK, plan_mesh
             torch.manual_seed(0)
             model = wl.build_model().to(dev)
+            extra = {k: v for k, v in wl.option.items() if k in ("prefetch_fwd", "loop_batch")}
             opt = PipeOption(device_cnt=1, batch_size=wl.micro_batch, batch_cnt=wl.batch_cnt,
                              mixed_precision=None if cpu else wl.precision, cpu_test=cpu,
-                             no_bench_optimizer=True, verbosity="warning")
+                             no_bench_optimizer=True, verbosity="warning", **extra)
             cd = _compute_dtype(torch, None if cpu else wl.precision)
             mb = wl.make_batch(wl.micro_batch, torch.Generator().manual_seed(0))
             x = tuple(_to_compute(t, cd).to(dev) for t in mb[:wl.n_model_inputs])
-            choice = plan_mesh(model, x, opt, world, dev)
+            choice = plan_mesh(model, x, opt, world, dev, link=link or NVSWITCH_LINK)
             mesh = choice.dp_mesh
-            # the cost model is good to about 5 % (predicted vs measured step time); within
-            # that margin pure data parallelism wins the tie: no bubble, no stage hand-offs
+            # a pure data-parallel layout within 2 % of the best prediction wins the tie (no
+            # stage hand-offs, no bubble: fewer things that the cost model leaves out)
             dp_only = [row for row in choice.table if row[0] == 1 and row[4]]
-            if dp_only and dp_only[0][3] >= 0.95 * choice.samples_per_s:
+            if dp_only and dp_only[0][3] >= 0.98 * choice.samples_per_s:
                 mesh = f"-{world},1"
             table = [{"pp": a, "dp": b, "step_ms": round(c, 2), "samples_per_s": round(d, 1),
                       "fits": bool(e)} for a, b, c, d, e in choice.table]
@@ -186,15 +199,20 @@ def _planned_mesh(args, wl, world, rank, cpu):
         except Exception as exc:   # planning must never take the benchmark down
             print(f"[bench] mesh planning failed ({type(exc).__name__}: {exc}); "
                   f"using pure data parallelism", file=sys.stderr, flush=True)
-        store.set("mesh", json.dumps({"mesh": mesh, "table": table}))
-    got = json.loads(store.get("mesh").decode())
-    # every rank has read the answer before rank 0 (the store's server) moves on
-    store.add("mesh_read", 1)
-    if rank == 0:
-        deadline = time.time() + 600
-        while int(store.add("mesh_read", 0)) < world and time.time() < deadline:
-            time.sleep(0.05)
-    return got["mesh"], got["table"]
+        box = [{"mesh": mesh, "table": table}]
+    dist.broadcast_object_list(box, src=0)
+    got = box[0]
+    got["link"] = None if link is None else {
+        "latency_ms": round(link[0], 4), "gb_per_s": round((1 << 20) / 1e9 / (link[1] / 1e3), 1)
+        if link[1] > 0 else None}
+    return got["mesh"], got
+
+
+def _predicted_ms(table, pp, dp):
+    for row in table or []:
+        if row["pp"] == pp and row["dp"] == dp:
+            return row["step_ms"]
+    return None
 
 
 def run_native(args) -> int:
@@ -223,17 +241,24 @@ def run_native(args) -> int:
     dev = state.device
     mp = None if cpu else wl.precision
     extra_opt = dict(wl.option)
+    for k in ("loop_cnt", "loop_batch", "prefetch_fwd", "split_points", "scheduler"):
+        if getattr(args, k, None) is not None:
+            extra_opt[k] = getattr(args, k)
     if state.pp_size == 1:
-        extra_opt.pop("loop_cnt", None)
+        for k in ("loop_cnt", "loop_batch", "prefetch_fwd"):
+            extra_opt.pop(k, None)
     if args.use_fsdp:
         extra_opt["use_fsdp"] = True
     option = PipeOption(device_cnt=state.pp_size, batch_size=wl.micro_batch,
                         batch_cnt=wl.batch_cnt, mixed_precision=mp, cpu_test=cpu,
                         no_bench_optimizer=True, optimizer={"type": "adamw", "lr": 1e-4},
                         fused_dp=not args.nccl_dp, cuda_graphs=not args.no_graphs,
+                        device_bench=args.device_bench,
                         verbosity="info" if args.verbose else "warning", **extra_opt)
     if not state.is_main_rank:
         worker_loop()
+        if world > 1:
+            dist.barrier()      # the job ends together (the main ranks wait here after closing)
         return 0
 
     torch.manual_seed(0)
@@ -251,15 +276,26 @@ def run_native(args) -> int:
     n = wl.micro_batch * wl.batch_cnt
     g = torch.Generator(device="cpu").manual_seed(1 + state.dp_rank)
     cd = _compute_dtype(torch, mp)
-    host = [_to_compute(t, cd) for t in wl.make_batch(n, g)]
+    # the host holds what a data loader would hand over: fp32 tensors in pinned memory
+    host = list(wl.make_batch(n, g))
     if not cpu:
         host = [t.pin_memory() for t in host]
-    resident = [t.to(dev) for t in host]
+
+    def to_compute(t):
+        if not t.is_floating_point() or t.dtype == cd:
+            return t
+        if t.is_cuda and cd in (torch.float16, torch.bfloat16):
+            from pfeife_b200.ops import kernels as kx
+            return kx.cast(t, cd)
+        return t.to(cd)
+
+    resident = [to_compute(t.to(dev)) for t in host]
 
     # End-to-end steps read their inputs from pinned host memory and bring the loss back.  Like
     # a prefetching data loader, the copy of step i+1's inputs is issued on a side stream
     # before step i is launched, so it travels while step i computes; every step still makes
-    # its own host-to-device copy inside the timed region.
+    # its own host-to-device copy inside the timed region, followed by the cast to the compute
+    # dtype on the device.  The reference arm loads its inputs the same way.
     copy_stream = None if cpu else torch.cuda.Stream(device=dev)
     pending = []
 
@@ -282,14 +318,19 @@ def run_native(args) -> int:
             torch.cuda.current_stream(dev).wait_event(ev)
             for t in batch:
                 t.record_stream(torch.cuda.current_stream(dev))
-        losses = runner.step(*batch)
+        losses = runner.step(*[to_compute(t) for t in batch])
         return float(torch.stack([l.float() for l in losses]).sum().cpu())
 
     def sync():
+        """Every rank of the job is idle: the other ranks of this pipeline answer a control
+        round trip after synchronising their devices, and the pipelines' main ranks (one
+        data-parallel group) meet at a barrier."""
+        if state.pp_size > 1:
+            runner.time_report(reset=False)
         if not cpu:
             torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        if state.dp_size > 1:
+            dist.barrier(group=state.dp_group)
             if not cpu:
                 torch.cuda.synchronize()
 
@@ -305,23 +346,34 @@ def run_native(args) -> int:
             s.record()
             for i in range(args.steps):
                 one_step(e2e, last=(i == args.steps - 1))
+            if state.pp_size > 1:
+                # the earlier stages finish a step after the last one: the timed region ends
+                # when every rank of the pipeline has finished its work
+                runner.time_report(reset=False)
             e.record()
             sync()
             ms = s.elapsed_time(e) / args.steps
-        if world > 1:   # max over ranks
+        if world > 1:   # max over the ranks that time (the main rank of every pipeline)
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=state.dp_group) \
+                if state.dp_size > 1 else None
             ms = float(t)
         return ms
 
     for _ in range(max(args.warmup, 1)):
         one_step(False)
+    runner.time_report(reset=True)          # per-stage event records restart with the timed steps
     sampler = ClockSampler(dev.index or 0)
     if state.is_main_process and not cpu:
         sampler.start()
+    if not cpu:
+        torch.cuda.profiler.start()         # capture range for an external profiler
     l0 = _lib.launch_count()
     ms = timed(False)
     launches = _lib.launch_count() - l0
+    if not cpu:
+        torch.cuda.profiler.stop()
+    bubble = runner.bubble_report(ms)
     # the end-to-end path has first-use costs of its own (copy stream, staging buffers of the
     # allocator): warm it up as well
     for _ in range(min(max(args.warmup, 1), 2)):
@@ -331,22 +383,39 @@ def run_native(args) -> int:
     if not cpu:
         from pfeife_b200.ops import kernels as kx
         kx.check_status()
-    bubble = 0.0
+    sim_bubble, predicted = 0.0, None
     for m in runner.modules:
         if m.plan is not None and m.plan.sim is not None:
-            bubble = m.plan.sim.bubble_fraction
+            sim_bubble = m.plan.sim.bubble_fraction
+            predicted = m.plan.time
+    # every pipeline's main rank reports its own bubble; the line carries the worst pipeline
+    if state.dp_size > 1:
+        allb = [None] * state.dp_size
+        dist.all_gather_object(allb, bubble, group=state.ctrl_dp)
+        bubble = max(allb, key=lambda b: b["max_pct"])
     if state.is_main_process:
         samples = n * state.dp_size
+        table = (planned or {}).get("table")
+        pred_mesh = _predicted_ms(table, state.pp_size, state.dp_size)
         emit_result(args, impl="pfeife_b200", n_gpus=world, ms=ms, ms_e2e=ms_e2e, samples=samples,
                     clocks=clocks, launches=launches,
                     parallelism=f"pp{state.pp_size}xdp{state.dp_size}",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=4, workload=wl,
                     extra={"dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
                            if state.dp_size > 1 else None,
-                           "planner_mesh_table": planned,
+                           "planner_mesh_table": table,
+                           "planner_link": (planned or {}).get("link"),
+                           "planner_predicted_step_ms": pred_mesh if pred_mesh is not None
+                           else predicted,
+                           "planner_error_pct": None if not (pred_mesh or predicted) else round(
+                               100.0 * ((pred_mesh or predicted) - ms) / ms, 2),
                            "use_fsdp": bool(option.use_fsdp),
                            "optimizer_and_dp_exposed_ms": runner.worker.last_optimizer_ms(),
-                           "pipeline_bubble_pct": 100.0 * bubble})
+                           "pipeline_bubble_pct": bubble["max_pct"],
+                           "pipeline_bubble_mean_pct": bubble["mean_pct"],
+                           "pipeline_bubble_simulated_pct": 100.0 * sim_bubble,
+                           "per_rank": [{k: (round(v, 3) if isinstance(v, float) else v)
+                                         for k, v in r.items()} for r in bubble["per_rank"]]})
     runner.close()
     if world > 1:
         dist.barrier()
@@ -367,6 +436,12 @@ def main(argv=None) -> int:
     ap.add_argument("--use_fsdp", action="store_true",
                     help="keep weight matrices row-sharded between optimizer steps; the first "
                          "GEMM that reads one gathers the other ranks' rows (needs DP > 1)")
+    ap.add_argument("--loop_cnt", type=int, default=None, help="stages per pipeline rank")
+    ap.add_argument("--loop_batch", type=int, default=None)
+    ap.add_argument("--prefetch_fwd", type=int, default=None)
+    ap.add_argument("--scheduler", type=str, default=None)
+    ap.add_argument("--device_bench", type=str, default=None,
+                    help="link-model file (measured and written when it does not exist)")
     ap.add_argument("--cpu", action="store_true", help="plumbing check without a GPU")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--workload", default="vitg",

@@ -886,13 +886,6 @@ PF_API int pf_gemm(const void* A, const void* B, void* C, int M, int N, int K, l
   return -1;
 }
 
-// Diagnostic: result of encoding a 2-D 16-bit tensor map with the given geometry (0 = ok).
-PF_API int pf_tmap_probe(const void* base, long long inner, long long outer, long long ld,
-                         int box_inner, int box_outer) {
-  CUtensorMap m;
-  return make_tmap_2d_16bit(&m, base, 1, inner, outer, ld, box_inner, box_outer);
-}
-
 // C[M,N] = epi(A[M,K] . W[N,K]^T) where the rows of W are owned by `world` ranks: rank r owns
 // rows [row_end[r-1], row_end[r]) (row_end[world-1] == N) and `copies[r]` points at rank r's
 // full-size copy of W (pitch ldb, peer-mapped for r != rank) in which at least the rows it owns

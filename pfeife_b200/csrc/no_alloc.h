@@ -18,7 +18,13 @@
 //    Inputs and outputs are still the caller's buffers.
 //  * The first call on each device looks up the array's device address (one
 //    cudaGetSymbolAddress with that device current).  Make that first call before any stream
-//    capture is started on the device.
+//    capture is started on the device, and OUTSIDE the region in which you may not allocate:
+//    the CUDA runtime loads a library's device code lazily, so the first use of this
+//    translation unit on a device can make the runtime itself allocate memory for the module
+//    image (the 4 MiB array included).  From the second call on nothing is allocated.
+//  * The looked-up addresses sit in a small per-device table that is filled without a lock.
+//    Two host threads that make the first call for the same device at the same time both
+//    store the same value, which is harmless; no other state is shared between host threads.
 //  * All calls share the one array and it keeps the previous call's contents; the kernels
 //    overwrite every element they later read, so nothing has to be cleared, but two calls that
 //    overlap on the GPU (different streams, or graphs replayed concurrently) race on it.

@@ -4,6 +4,7 @@
 // The backward writes dx (optionally + the gradient that flows around the norm through the
 // residual branch) and per-CTA partial sums of dgamma / dbeta into a scratch buffer that a
 // second small kernel folds into the fp32 parameter gradients.
+#include "no_alloc.h"
 #include "common.cuh"
 #include "api.h"
 
@@ -661,7 +662,6 @@ PF_API int pf_norm_bwd(const void* dy, const void* h, const void* gamma, const v
 }
 
 // ------------------------------------------------------------------ allocation-free variant
-#include "no_alloc.h"
 
 // Partial dgamma / dbeta sums of pf_norm_bwd_static.  One copy per device that loads the
 // library; shared by every call on that device.

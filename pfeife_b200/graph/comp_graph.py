@@ -26,6 +26,7 @@ import torch.fx as fx
 
 from .capture import CapturedGraph
 
+# share of device memory above which the profiling pass moves what it keeps alive to the host
 GRAPH_FETCH_MEM_CAP = 0.6
 WEIGHT_MULTIPLIER = 4  # weights + gradients + two optimizer moments
 FORMAT = "pfeife_b200.graph_bench/1"
@@ -225,6 +226,101 @@ class CompGraph:
         for node in self.nodes:
             node.act_mem = node.out_bytes
             node.temp_mem = node.out_bytes
+
+    # ------------------------------------------------------------------ linearisation
+    def linear_order(self, mode: str) -> List[int]:
+        """A topological order of the segments for ``--linearizer`` (behaviour of
+        pfeife/graph/computation_graph.py:193-277).  Runnable segments are grown into chains
+        (a segment whose only unfinished producer is the chain's tail joins it); each round runs
+        one whole chain: the one with the fewest segments (``short_first``), the most
+        (``long_first``), or the one that leaves the least memory alive while it runs
+        (``save_mem``: activations of the other candidates + its own transient peak)."""
+        n = len(self.nodes)
+        if mode in (None, "none") or n < 2:
+            return list(range(n))
+        if mode not in ("save_mem", "short_first", "long_first"):
+            raise ValueError(f"unknown linearizer {mode!r}")
+        preds: List[Set[int]] = [set() for _ in range(n)]
+        succs: List[Set[int]] = [set() for _ in range(n)]
+        for e in self.edges:
+            if e.start != e.end:
+                preds[e.end].add(e.start)
+                succs[e.start].add(e.end)
+        done: Set[int] = set()
+        order: List[int] = []
+        while len(done) < n:
+            chains = []
+            for i in range(n):
+                if i in done or not preds[i] <= done:
+                    continue
+                chain, cur = [i], i
+                while len(succs[cur]) == 1:
+                    nxt = next(iter(succs[cur]))
+                    if nxt in done or any(p != cur and p not in done for p in preds[nxt]):
+                        break
+                    chain.append(nxt)
+                    cur = nxt
+                chains.append(chain)
+            chains.sort(key=len)
+            if mode == "short_first":
+                taken = chains[0]
+            elif mode == "long_first":
+                taken = chains[-1]
+            else:
+                cost = []
+                for c in chains:
+                    act, peak = 0, 0
+                    for i in c:
+                        peak = max(peak, self.nodes[i].temp_mem + act)
+                        act += self.nodes[i].act_mem
+                    cost.append((c, act, peak))
+                total = sum(a for _, a, _ in cost)
+                taken = min(cost, key=lambda t: total - t[1] + t[2])[0]
+            for i in taken:
+                if i not in done:
+                    done.add(i)
+                    order.append(i)
+        return order
+
+    def linearize(self, mode: str) -> bool:
+        """Re-orders the segments by ``linear_order(mode)`` and the FX graph with them (the
+        reference's ``traverse_linearize`` + ``redraw_graph``), keeping the statistics each
+        segment already carries.  Returns whether anything moved."""
+        order = self.linear_order(mode)
+        if order == list(range(len(self.nodes))):
+            return False
+        gm = self.captured.gm
+        by_name = {n.name: n for n in gm.graph.nodes}
+        placeholders = [n for n in gm.graph.nodes if n.op == "placeholder"]
+        anchor = placeholders[-1] if placeholders else None
+        stats = {}
+        for new_idx, old_idx in enumerate(order):
+            node = self.nodes[old_idx]
+            stats[new_idx] = (node.act_mem, node.temp_mem, node.comp_time, node.back_time,
+                              node.optim_time)
+            for name in node.fx_nodes:
+                fx_node = by_name[name]
+                if anchor is None:
+                    first = next(iter(gm.graph.nodes))
+                    if first is not fx_node:
+                        first.prepend(fx_node)
+                else:
+                    anchor.append(fx_node)
+                anchor = fx_node
+        gm.graph.lint()
+        gm.recompile()
+        fb = self.fb_ratio
+        self.nodes, self.edges, self.param_set = [], [], ParamSet()
+        self.seg_of, self.input_users = {}, {}
+        self.output_segments, self.placeholder_order = [], []
+        self._build()
+        if len(self.nodes) == len(order):
+            for idx, (act, temp, t, bt, ot) in stats.items():
+                nd = self.nodes[idx]
+                nd.act_mem, nd.temp_mem, nd.comp_time, nd.back_time, nd.optim_time = \
+                    act, temp, t, bt, ot
+        self.fb_ratio = fb
+        return True
 
     # ------------------------------------------------------------------ queries
     def __len__(self) -> int:

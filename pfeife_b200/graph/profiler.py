@@ -24,6 +24,7 @@ import torch.fx as fx
 
 from ..utils import get_logger
 from .capture import CapturedGraph
+from . import comp_graph as comp_graph_mod
 from .comp_graph import CompGraph, _tensor_leaves
 
 TIME_WARM_ITER = 2
@@ -150,10 +151,18 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
     amp = lambda: gen_amp_context(device, option.mixed_precision)
 
     cached = option.graph_bench and os.path.exists(option.graph_bench)
-    # ---- pass 1: one real forward with memory statistics
+    # ---- pass 1: one real forward with memory statistics.  It keeps every activation alive
+    #      (the caller's loss and backward continue from its output), so a model whose
+    #      activations outgrow the device is profiled with its saved tensors parked in pinned
+    #      host memory from the segment on at which reserved memory passes GRAPH_FETCH_MEM_CAP
+    #      of the device (pfeife/graph/computation_graph.py:926-963 offloads the same way);
+    #      the segments after that point keep their analytic activation sizes.
     mem_before: Dict[int, int] = {}
+    offload = contextlib.ExitStack()
+    offloaded_from = [None]
     if is_cuda:
         torch.cuda.synchronize(device)
+        total_mem = torch.cuda.get_device_properties(device).total_memory
 
         def on_start(seg):
             torch.cuda.reset_peak_memory_stats(device)
@@ -163,16 +172,29 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
             now = torch.cuda.memory_allocated(device)
             peak = torch.cuda.max_memory_allocated(device)
             node = graph.nodes[seg]
-            node.act_mem = max(0, now - mem_before[seg])
-            node.temp_mem = max(node.act_mem, peak - mem_before[seg])
+            if offloaded_from[0] is None:
+                node.act_mem = max(0, now - mem_before[seg])
+                node.temp_mem = max(node.act_mem, peak - mem_before[seg])
+                if torch.cuda.memory_reserved(device) > comp_graph_mod.GRAPH_FETCH_MEM_CAP * total_mem:
+                    offloaded_from[0] = seg + 1
+                    offload.enter_context(torch.autograd.graph.save_on_cpu(pin_memory=True))
+                    log.info("profiling pass: activations go to host memory from segment %d on",
+                             seg + 1)
+            else:
+                node.temp_mem = max(node.act_mem, peak - mem_before[seg])
     else:
         on_start = on_end = None
-    with amp():
+    with offload, amp():
         output = ex.run(args, None if cached else on_start, None if cached else on_end)
     if cached:
         graph.load_graph_data(option.graph_bench)
         log.info("loaded graph bench from %s: %s", option.graph_bench, graph.summary())
         return graph, output
+    # the segment order the planner cuts (--linearizer): chosen from the memory figures of pass
+    # 1, before the timing passes run in that order (pfeife/local/graph_bench.py:436-438)
+    if graph.linearize(getattr(option, "linearizer", "none")):
+        ex = SegmentExecutor(graph)
+        log.info("segments re-ordered by the %s linearizer", option.linearizer)
 
     # ---- pass 2: per-segment forward timing
     n_seg = len(graph.nodes)
@@ -245,6 +267,7 @@ def gen_comp_graph_cpu(captured: CapturedGraph, args: Sequence[Any], option
     graph = CompGraph(captured)
     with gen_amp_context(torch.device("cpu"), option.mixed_precision):
         output = SegmentExecutor(graph).run(args)
+    graph.linearize(getattr(option, "linearizer", "none"))
     for n in graph.nodes:
         n.comp_time = 1.0
     graph.fb_ratio = 2.0

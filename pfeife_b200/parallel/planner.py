@@ -485,25 +485,43 @@ def get_pipe_class(name: str):
 
 
 # ------------------------------------------------------------------------------ DP term + mesh
+# Measured copy bandwidth of one B200's HBM3e (bytes/s); only used to estimate the optimizer
+# step when the profile carries no measured optimizer time.
+HBM_BYTES_PER_S = 6.5e12
+# bytes the fused optimizer moves per parameter: gradient read + cleared, master, two moments
+# read + written, 16-bit weight written
+ADAM_BYTES_PER_PARAM = 34.0
+
+
 def dp_exposed_time(param_bytes_per_rank: float, dp_size: int, bench: Optional[DeviceBench],
                     grad_dtype_bytes: int = 4, overlap: float = 0.0) -> float:
     """Predicted exposed time (ms) of the data-parallel step of one rank beyond its local
     optimizer: every rank reads the other ranks' gradients of its shard (``(dp-1)/dp`` of the
-    gradient bytes cross the links towards it) and pushes its updated fp32 masters and 16-bit
-    weights to the others (the same share of 4 + 2 bytes per parameter leaves it); reads and
-    pushes follow each other inside one kernel, so their times add.  Measured on ViT-g/14
-    (1.01 B parameters): 8.8 ms at 2 ranks and 11.3 ms at 8 on top of the 6.5 ms local optimizer;
-    this model gives 6.6 and 11.5.  ``overlap`` is the fraction hidden behind the backward."""
+    gradient bytes cross the links towards it) and pushes its updated 16-bit weights to the
+    others (the same share of 2 bytes per parameter leaves it; fp32 masters stay with their
+    owner); reads and pushes follow each other inside one kernel, so their times add.  The
+    link model is the measured one when `bench` carries it.  ``overlap`` is the fraction
+    hidden behind the backward."""
     if dp_size <= 1:
         return 0.0
     n_el = param_bytes_per_rank / 4.0
     share = (dp_size - 1) / dp_size
-    moved = n_el * (grad_dtype_bytes + 4 + 2) * share
+    moved = n_el * (grad_dtype_bytes + 2) * share
     if bench is None or not bench.params:
         ms = moved / (770e9) * 1e3 + 0.05
     else:
         ms = bench.send_time(next(iter(bench.params)), moved)
     return ms * (1.0 - overlap)
+
+
+def optimizer_time(param_bytes_per_rank: float, dp_size: int, measured_ms: float = 0.0) -> float:
+    """Time (ms) of the optimizer update of one rank: the measured value when the profile has
+    one, else the bytes the fused update moves at HBM bandwidth.  Under data parallelism every
+    rank updates only its shard."""
+    if measured_ms > 0.0:
+        return measured_ms / max(1, dp_size)
+    n_el = param_bytes_per_rank / 4.0
+    return n_el * ADAM_BYTES_PER_PARAM / max(1, dp_size) / HBM_BYTES_PER_S * 1e3
 
 
 @dataclass
@@ -551,7 +569,12 @@ def choose_mesh(comp_graph: CompGraph, world_size: int, option, bench: Optional[
                        for r in range(pp))
         # ZeRO-style sharding divides the static optimizer footprint by dp
         ok = max(plan.peak_mem) < RESERVE_MEM_RATIO * device_mem
-        step = plan.time + dp_exposed_time(per_rank, dp, bench)
+        # the pipeline makespan contains the optimizer only when the profile measured it; the
+        # data-parallel shard of it is what remains exposed either way
+        measured_opt = max(sum(n.optim_time for n in plan.pipe_graph.nodes if n.rank == r)
+                           for r in range(pp))
+        step = plan.time - measured_opt + optimizer_time(per_rank, dp, measured_opt) + \
+            dp_exposed_time(per_rank, dp, bench)
         sps = bs * option.batch_cnt * dp / step * 1e3
         table.append((pp, dp, step, sps, ok))
         cand = MeshChoice(pp, dp, plan, step, sps)

@@ -159,6 +159,15 @@ class LocalRunner(PartialRunner):
                 if isinstance(res, BaseException):
                     raise res
 
+    def time_report(self, reset: bool = True) -> List[Dict[str, Any]]:
+        self._wait_idle()
+        reps = []
+        for w in self.workers:
+            rep = w.time_report(reset)
+            rep["memory"] = w.memory_usage()
+            reps.append(rep)
+        return reps
+
     def _dispatch(self, msg: Dict[str, Any]) -> None:
         flag = msg["flag"]
         if flag == LoopFlag.STOP_LOOP:

@@ -183,6 +183,10 @@ def worker_loop(option: Optional[PipeOption] = None) -> None:
                 worker.scaler.load_state_dict(msg["opt"].get(SCALER_KEY))
         elif flag == LoopFlag.LOG_MEMORY_USAGE:
             worker.log_memory_usage()
+        elif flag == LoopFlag.REPORT_TIMES:
+            rep = worker.time_report(msg.get("reset", True))
+            rep["memory"] = worker.memory_usage()
+            ctrl.gather(rep)
 
 
 def _run_device_bench(state: PfeifeState, option: PipeOption) -> DeviceBench:
@@ -592,6 +596,32 @@ class PartialRunner:
     def log_memory_usage(self) -> None:
         self.ctrl.bcast({"flag": LoopFlag.LOG_MEMORY_USAGE})
         self.worker.log_memory_usage()
+
+    def time_report(self, reset: bool = True) -> List[Dict[str, Any]]:
+        """Per pipeline rank of this pipeline: device time spent in stage forwards, backwards
+        and optimizer steps since the last report, the number of steps covered and the memory
+        figures (``StageWorker.time_report``).  ``bubble_report`` turns it into idle shares."""
+        self.ctrl.bcast({"flag": LoopFlag.REPORT_TIMES, "reset": reset})
+        mine = self.worker.time_report(reset)
+        mine["memory"] = self.worker.memory_usage()
+        reps = self.ctrl.gather(mine) if self.state.pp_size > 1 else [mine]
+        return [r for r in reps if r is not None]
+
+    def bubble_report(self, step_ms: float, reset: bool = True) -> Dict[str, Any]:
+        """Measured pipeline bubble of the steps since the last report, given their mean
+        device time: per rank ``1 - (forward + backward time) / (step time - optimizer time)``,
+        with the maximum and mean over the ranks of this pipeline (the reference records the
+        same per-stage events and never reads them back, pfeife/mp/worker.py:1484-1499)."""
+        per_rank = []
+        for r in sorted(self.time_report(reset), key=lambda r: r["pp_rank"]):
+            n = max(1, r["steps"])
+            busy = (r["fwd_ms"] + r["bwd_ms"]) / n
+            window = max(step_ms - r["opt_ms"] / n, 1e-9)
+            per_rank.append({"pp_rank": r["pp_rank"], "busy_ms": busy, "opt_ms": r["opt_ms"] / n,
+                             "bubble_pct": 100.0 * max(0.0, 1.0 - busy / window),
+                             "max_mem_bytes": r["memory"]["max"]})
+        b = [r["bubble_pct"] for r in per_rank]
+        return {"per_rank": per_rank, "max_pct": max(b), "mean_pct": sum(b) / len(b)}
 
     def close(self) -> None:
         if self._closed:

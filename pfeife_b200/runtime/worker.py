@@ -43,6 +43,7 @@ class LoopFlag(enum.IntEnum):
     LOG_MEMORY_USAGE = 3
     LOAD_PARAMS = 4
     EVAL_LOOP = 5
+    REPORT_TIMES = 6
 
 
 # message key: (is_grad, producer_stage, producer_output, consumer_stage, consumer_input, mb)
@@ -217,6 +218,7 @@ class StageWorker:
         # True when the job has more ranks than this stage's replicas (set by the front-end)
         self.inf_sync_job_wide = pp_size > 1
         self.train_steps_done = 0
+        self.opt_event_log: List[Tuple[Any, Any]] = []
         self._reset_step_state()
 
     # ------------------------------------------------------------------ plan installation
@@ -590,6 +592,29 @@ class StageWorker:
         ev0 = self.recorder.record_event(self.device)
         self._optimizer_step()
         self.opt_events = (ev0, self.recorder.record_event(self.device))
+        self.opt_event_log.append(self.opt_events)
+        if len(self.opt_event_log) > 4096:      # nobody is reading them: keep the tail
+            del self.opt_event_log[:2048]
+            self.recorder.reset()
+
+    def time_report(self, reset: bool = True) -> Dict[str, float]:
+        """Device time this rank spent in stage forwards, stage backwards and optimizer steps
+        since the last report (CUDA events on the compute stream; waits for incoming transfers
+        are enqueued before a stage's first event and so are not counted), and the number of
+        optimizer steps that covers.  The idle share of a step (pipeline bubble) follows from
+        these and the step time."""
+        fw, bw = self.recorder.get_event_logs()
+        if self.device.type == "cuda" and self.opt_event_log:
+            self.opt_event_log[-1][1].synchronize()
+        rep = {"pp_rank": self.pp_rank,
+               "fwd_ms": float(sum(sum(v) for v in fw.values())),
+               "bwd_ms": float(sum(sum(v) for v in bw.values())),
+               "opt_ms": float(sum(a.elapsed_time(b) for a, b in self.opt_event_log)),
+               "steps": len(self.opt_event_log)}
+        if reset:
+            self.recorder.reset()
+            self.opt_event_log.clear()
+        return rep
 
     def last_optimizer_ms(self) -> float:
         """Device time of the last optimizer step (data-parallel reduce + update + gather); it
