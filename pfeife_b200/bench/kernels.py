@@ -1,6 +1,7 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-    python -m pfeife_b200.bench.kernels [--which gemm,conv,norm,adamw] [--json out.jsonl]
+    python -m pfeife_b200.bench.kernels [--which gemm,conv,norm,adamw,attn,groupnorm,rope]
+                                        [--json out.jsonl]
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MiB buffer, median of `--iters`.  Fractions are against the measured
@@ -122,6 +123,81 @@ def bench_norm(timer, out):
              "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
 
 
+def bench_attn(timer, out):
+    """Flash attention forward / backward against ``F.scaled_dot_product_attention`` on the
+    shapes of the benchmark models: ViT-g/14 (d = 88), Llama-2-7B (causal, d = 128), the SDXL
+    UNet's self-attention at 64x64 and 32x32 latents and its cross-attention (77 text tokens)."""
+    import torch.nn.functional as F
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    shapes = [("vitg", 24, 16, 257, 257, 88, False), ("llama7b", 1, 32, 2048, 2048, 128, True),
+              ("unet_64x64", 4, 10, 4096, 4096, 64, False), ("unet_32x32", 4, 20, 1024, 1024, 64, False),
+              ("unet_cross_77", 4, 20, 1024, 77, 64, False)]
+    for name, B, H, Sq, Sk, D, causal in shapes:
+        dtype = torch.bfloat16
+        q = torch.randn(B, Sq, H, D, device="cuda").to(dtype)
+        k = torch.randn(B, Sk, H, D, device="cuda").to(dtype)
+        v = torch.randn(B, Sk, H, D, device="cuda").to(dtype)
+        do = torch.randn(B, Sq, H, D, device="cuda").to(dtype)
+        scale = D ** -0.5
+        ms_f = timer(lambda: kx.attn_fwd(q, k, v, causal, scale))
+        o, lse = kx.attn_fwd(q, k, v, causal, scale)
+        ms_b = timer(lambda: kx.attn_bwd(do, q, k, v, o, lse, causal, scale))
+        # SDPA wants [B, H, S, D]; the transposed views cost it nothing (strided inputs)
+        qt, kt, vt = (t.transpose(1, 2).detach().requires_grad_() for t in (q, k, v))
+        ms_rf = timer(lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal))
+        ot = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal)
+        dot = do.transpose(1, 2)
+        ms_rb = timer(lambda: torch.autograd.grad(ot, (qt, kt, vt), dot, retain_graph=True))
+        frac = 0.5 if causal else 1.0
+        fl = 4.0 * B * H * Sq * Sk * D * frac
+        out({"kernel": "flash_attention", "case": name, "B": B, "H": H, "Sq": Sq, "Sk": Sk, "D": D,
+             "causal": causal, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_tflops": fl / ms_f / 1e9,
+             "bwd_tflops": 2.5 * fl / ms_b / 1e9, "sdpa_fwd_ms": ms_rf, "sdpa_bwd_ms": ms_rb,
+             "fwd_vs_sdpa": ms_rf / ms_f, "bwd_vs_sdpa": ms_rb / ms_b, "peak_ref": tag})
+
+
+def bench_groupnorm(timer, out):
+    """GroupNorm(32) + SiLU on NHWC activations of the SDXL UNet, forward and backward, against
+    ``F.group_norm`` + ``F.silu`` on channels-last tensors."""
+    import torch.nn.functional as F
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    for name, B, HW, C in (("sdxl_320_128", 4, 128, 320), ("sdxl_640_64", 4, 64, 640),
+                           ("sdxl_1280_32", 4, 32, 1280), ("sdxl_1920_64", 4, 64, 1920)):
+        x = torch.randn(B, HW, HW, C, device="cuda").to(torch.bfloat16)
+        g = torch.ones(C, device="cuda")
+        b = torch.zeros(C, device="cuda")
+        dy = torch.randn_like(x)
+        ms_f = timer(lambda: kx.groupnorm_fwd(x, g, b, 32, 1e-5, True))
+        y, mean, rstd = kx.groupnorm_fwd(x, g, b, 32, 1e-5, True)
+        ms_b = timer(lambda: kx.groupnorm_bwd(dy, x, mean, rstd, g, b, 32, True))
+        xn = x.permute(0, 3, 1, 2).detach().requires_grad_()
+        ms_rf = timer(lambda: F.silu(F.group_norm(xn, 32, g, b, 1e-5)))
+        yr = F.silu(F.group_norm(xn, 32, g, b, 1e-5))
+        dyn = dy.permute(0, 3, 1, 2)
+        ms_rb = timer(lambda: torch.autograd.grad(yr, xn, dyn, retain_graph=True))
+        nb = x.numel() * 2
+        out({"kernel": "groupnorm_silu", "case": name, "fwd_ms": ms_f, "bwd_ms": ms_b,
+             "fwd_gbs": 2 * nb / ms_f / 1e6, "bwd_gbs": 3 * nb / ms_b / 1e6,
+             "fwd_frac_peak": 2 * nb / ms_f / 1e6 / hbm, "bwd_frac_peak": 3 * nb / ms_b / 1e6 / hbm,
+             "torch_fwd_ms": ms_rf, "torch_bwd_ms": ms_rb, "fwd_vs_torch": ms_rf / ms_f,
+             "bwd_vs_torch": ms_rb / ms_b, "peak_ref": tag})
+
+
+def bench_rope(timer, out):
+    from pfeife_b200.ops import functional as Fn
+    from pfeife_b200.ops import kernels as kx
+    hbm, tf, tag = peaks()
+    B, S, H, D = 16, 2048, 32, 128
+    x = torch.randn(B, S, H, D, device="cuda").to(torch.bfloat16)
+    cos, sin = Fn.rope_tables(S, D, device="cuda")
+    ms = timer(lambda: kx.rope(x, cos, sin))
+    gb = 2 * x.numel() * 2 / 1e9
+    out({"kernel": "rope", "shape": [B, S, H, D], "ms": ms, "gbs": gb / ms * 1e3,
+         "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
+
+
 def bench_adamw(timer, out):
     from pfeife_b200.ops import kernels as kx
     hbm, tf, tag = peaks()
@@ -150,7 +226,8 @@ def main(argv=None):
             sink.write(line + "\n")
 
     timer = Timer(a.iters)
-    table = {"gemm": bench_gemm, "conv": bench_conv, "norm": bench_norm, "adamw": bench_adamw}
+    table = {"gemm": bench_gemm, "conv": bench_conv, "norm": bench_norm, "adamw": bench_adamw,
+             "attn": bench_attn, "groupnorm": bench_groupnorm, "rope": bench_rope}
     for k in a.which.split(","):
         table[k](timer, out)
     from pfeife_b200.ops import kernels as kx

@@ -103,9 +103,15 @@ _FLAGS: List[_Flag] = [
     _Flag("mixed_precision", None, "--mixed_precision", dict(type=str, choices=["fp16", "bf16"])),
     _Flag("cpu_test", False, "--cpu", dict(action="store_true"),
           help="run on CPU (gloo), for tests"),
-    _Flag("no_side_effect", False, "--no_side_effect", dict(action="store_true")),
-    _Flag("no_io_cache", False, "--no_io_cache", dict(action="store_true")),
-    _Flag("single_comm_thread", False, "--single_comm_thread", dict(action="store_true")),
+    _Flag("no_side_effect", False, "--no_side_effect", dict(action="store_true"),
+          help="manager front-ends: the framework owns the loss and hands back only losses; "
+               "that is how PipeManager / LocalPipeManager always run here, so the flag "
+               "selects nothing further"),
+    _Flag("no_io_cache", False, "--no_io_cache", dict(action="store_true"),
+          help="allocate stage-boundary receive buffers per step instead of keeping them"),
+    _Flag("single_comm_thread", False, "--single_comm_thread", dict(action="store_true"),
+          help="accepted for compatibility: this runtime posts transfers from the stage "
+               "thread itself and has no sender threads to merge"),
     _Flag("no_bench_optimizer", False, "--no_bench_optimizer", dict(action="store_true")),
     # ---- additions of this framework
     _Flag("dp_mesh", None, "--dp_mesh_opt", dict(type=str),

@@ -287,6 +287,11 @@ class StageWorker:
         for h in self.sends:
             h.wait()
         self._reset_step_state()
+        if getattr(self.option, "no_io_cache", False) and hasattr(self, "recv_bufs"):
+            # --no_io_cache: receive buffers live for one step instead of being kept per
+            # (edge, micro-batch) for the whole run (pfeife/local/worker.py:403-420)
+            self.recv_bufs.clear()
+            self.zero_bufs.clear()
 
     # ------------------------------------------------------------------ receive machinery
     def _post_until(self, comm: CommPlan, src: int, msg: _Msg) -> None:

@@ -137,3 +137,68 @@ def test_graph_bench_cache_roundtrip(tmp_path):
     assert cg2.fb_ratio == cg.fb_ratio
     cgu, _ = gen_comp_graph_cpu(cap, args, opt)
     assert all(n.comp_time == 1.0 for n in cgu.nodes) and cgu.fb_ratio == 2.0
+
+
+class _Branchy(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        mk = lambda: torch.nn.Linear(8, 8)
+        self.a, self.b1, self.b2, self.c1, self.d = mk(), mk(), mk(), mk(), mk()
+
+    def forward(self, x):
+        h = self.a(x)
+        long = torch.relu(self.b2(torch.relu(self.b1(h))))
+        short = self.c1(h)
+        return self.d(long + short)
+
+
+@pytest.mark.parametrize("mode", ["save_mem", "short_first", "long_first"])
+def test_linearizers_keep_the_function_and_order_the_branches(mode):
+    """--linearizer: a topological re-ordering of the segments (and of the FX graph with them):
+    the short branch runs first under ``short_first``, the long one under ``long_first``, and
+    the graph computes the same function either way."""
+    torch.manual_seed(0)
+    model = _Branchy()
+    x = torch.randn(3, 8)
+    cap, args, ref = capture(model, x)
+    cg = CompGraph(cap)
+    n = len(cg.nodes)
+    order = cg.linear_order(mode)
+    assert sorted(order) == list(range(n))
+    pos = {seg: i for i, seg in enumerate(order)}
+    for e in cg.edges:                      # producers stay ahead of their consumers
+        assert pos[e.start] < pos[e.end]
+    names_before = [nd.fx_nodes[-1] for nd in cg.nodes]
+    moved = cg.linearize(mode)
+    names_after = [nd.fx_nodes[-1] for nd in cg.nodes]
+    assert sorted(names_before) == sorted(names_after)
+    if mode == "short_first":
+        assert moved and names_after.index("short") < names_after.index("long")
+    if mode == "long_first":
+        assert names_after.index("long") < names_after.index("short")
+    part = partition_module(cg, [n // 2], device_cnt=2)
+    out = check_partition(cg, part, args)
+    got = out[0] if isinstance(out, (tuple, list)) else out
+    assert torch.allclose(got, ref, atol=1e-6)
+
+
+def test_linearizer_option_reaches_the_profile():
+    cap, args, ref = capture(_Branchy(), torch.randn(3, 8))
+    opt = PipeOption(device_cnt=2, linearizer="short_first", no_bench_optimizer=True, cpu_test=True)
+    cg, out = gen_comp_graph_cpu(cap, args, opt)
+    names = [nd.fx_nodes[-1] for nd in cg.nodes]
+    assert names.index("short") < names.index("long")
+
+
+def test_compile_hook_wraps_a_stage_module():
+    """--backend: a stage module is compiled with the named dynamo backend on first use
+    (pfeife/compile.py:19-60); no backend leaves the module as it is."""
+    from pfeife_b200.compile import WrapperModule, compile_module
+    mod = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU())
+    assert compile_module(None, mod) is mod
+    wrapped = compile_module("eager", mod)
+    assert isinstance(wrapped, WrapperModule)
+    x = torch.randn(2, 4)
+    assert torch.allclose(wrapped(x), mod(x))
+    single = WrapperModule(lambda *a: (a[0] * 2,), unwrap_singleton_tuple=True)
+    assert torch.equal(single(x), x * 2)

@@ -131,3 +131,18 @@ def test_allgather_fused_into_gemm(tmp_path):
     with open(out) as f:
         res = json.load(f)
     assert res["gathered_ok"] and res["err"] < 0.15
+
+
+def test_thread_runtime_on_two_gpus_matches_the_plain_loop():
+    """The single-process runtime (one thread per device, activations moved by peer copies on
+    side streams) through ``benchmark_local.py --check_valid`` on two GPUs: pipelined training
+    tracks the un-pipelined loop step by step."""
+    import re
+    cmd = [sys.executable, os.path.join(ROOT, "benchmark_local.py"), "--model", "vit_tiny",
+           "--device_cnt", "2", "--batch_size", "2", "--batch_cnt", "4", "--check_valid",
+           "--valid_steps", "3"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=420, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-4000:]
+    d = [float(x) for x in re.findall(r"diff percentage: (-?[0-9.]+)%", r.stdout)]
+    assert len(d) == 3 and max(abs(x) for x in d) < 1.0, r.stdout[-2000:]
