@@ -87,6 +87,11 @@ def run(args) -> int:
                 pass
         env = dict(os.environ, PFEIFE_REF_CHILD="1", DP_MESH=mesh, PFEIFE_REF_OUT=out,
                    MASTER_PORT=str(base_port + 101 + i), PFEIFE_REF_LIMIT=str(share - 15))
+        # the children rendezvous on a port of their own, where no launcher agent serves a
+        # store: without these variables rank 0 of the child job creates it, as under the
+        # reference's own launcher
+        for k in [k for k in env if k.startswith("TORCHELASTIC_") or k.startswith("TORCH_NCCL_ASYNC")]:
+            env.pop(k, None)
         cmd = [sys.executable, os.path.join(root, "bench.py"), "--impl", "reference",
                "--gpus", str(world), "--steps", str(args.steps), "--warmup", str(args.warmup),
                "--layers", str(args.layers), "--hidden", str(args.hidden), "--heads",

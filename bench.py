@@ -411,6 +411,8 @@ def run_native(args) -> int:
                                100.0 * ((pred_mesh or predicted) - ms) / ms, 2),
                            "use_fsdp": bool(option.use_fsdp),
                            "optimizer_and_dp_exposed_ms": runner.worker.last_optimizer_ms(),
+                           "dp_phases_ms": runner.worker.dp.phase_ms()
+                           if getattr(runner.worker.dp, "fused", False) else None,
                            "pipeline_bubble_pct": bubble["max_pct"],
                            "pipeline_bubble_mean_pct": bubble["mean_pct"],
                            "pipeline_bubble_simulated_pct": 100.0 * sim_bubble,

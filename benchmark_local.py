@@ -37,6 +37,9 @@ def build(args, option):
     first = torch.device("cpu") if cpu else torch.device(option.device_map[0])
     last = torch.device("cpu") if cpu else torch.device(option.device_map[option.device_cnt - 1])
     cd = option.mixed_precision
+    # the graph is captured with the model's own tensors: they sit with the inputs (the first
+    # device) until the stages are cut and every device takes its share
+    model.to(first)
     return model, _to(vargs, first, cd), _to(kwargs, first, cd), loss_fn, _to(target, last, cd), last
 
 
@@ -47,7 +50,7 @@ def run_valid(args, option) -> int:
     loss_fn = RescaleLoss(loss_fn, 1 / 1000)
     opt_kwargs = dict(option.optimizer_kwargs or {})
     opt_kwargs.setdefault("lr", 1e-5)
-    local = copy.deepcopy(model)
+    local = copy.deepcopy(model).to("cpu")       # the plain loop runs on the host
     manager = LocalPipeManager(model, loss_fn, option,
                                optimizer=torch.optim.Adam(model.parameters(), **opt_kwargs))
     optim = torch.optim.Adam(local.parameters(), **opt_kwargs)

@@ -108,12 +108,16 @@ def get_workload(name: str, args=None) -> Workload:
     if name == "vitl":          # PP=4 x DP=2, prefetch_fwd 2
         return _vit("vitl", "ViT-L/16", "vit_large", 16, 8, mesh8="-2,4",
                     option={"prefetch_fwd": 2}, num_classes=1000)
+    # --layers / --batch_cnt shorten a run of the big configurations (plumbing checks on few GPUs)
+    over = {"num_layers": g("layers", None)} if g("layers", None) else {}
     if name == "llama7b":       # looped pipeline: 16 stages on 8 ranks
-        return _llama("llama7b", "llama2_7b", 1, 16, 2048, "8", {"loop_cnt": 2})
+        return _llama("llama7b", "llama2_7b", 1, g("batch_cnt", 16), 2048, "8", {"loop_cnt": 2},
+                      **over)
     if name == "llama7b_fsdp":  # PP=4 x DP=2, row-sharded weights between optimizer steps
-        return _llama("llama7b_fsdp", "llama2_7b", 1, 16, 2048, "-2,4", {"use_fsdp": True})
+        return _llama("llama7b_fsdp", "llama2_7b", 1, g("batch_cnt", 16), 2048, "-2,4",
+                      {"use_fsdp": True}, **over)
     if name == "sdxl":
-        return _unet("sdxl", "sdxl", 4, 8, 128, "2,-4")
+        return _unet("sdxl", "sdxl", 4, g("batch_cnt", 8), 128, "2,-4")
     # reduced shapes for plumbing checks (CPU / few GPUs)
     if name == "vit_tiny":
         return _vit("vit_tiny", "ViT-Tiny", "vit_tiny", g("batch_size", 4), g("batch_cnt", 4),

@@ -103,7 +103,7 @@ PF_DECL int pf_dp_fused_step(int rank, int world, void* const* grad, void* const
                              float grad_scale, int lp_dtype, int check_inf, int found_given,
                              const void* loss_scale, void* found_inf, int epoch,
                              int arrivals_before, int* barriers_out, int* grid_out, int* status,
-                             int sm_count, void* stream);
+                             void* trace, int sm_count, void* stream);
 PF_DECL int pf_gather_rows(void* dst, void* const* copies, const int* row_end, int world, int rank,
                            int rows, long long row_bytes, int sm_count, void* stream);
 PF_DECL int pf_ipc_get_handle(void* ptr, void* handle_out_64);

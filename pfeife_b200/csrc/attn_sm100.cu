@@ -27,6 +27,7 @@
 // ATT_TAIL_MAX rows are left over, the tensor-core tiles cover only the full multiples and a
 // small CUDA-core kernel computes the leftover query rows.  (The same split of the backward,
 // measured on ViT-g/14 shapes, cost more in its leftover-key kernel than the tiles it saved.)
+#include <cstdlib>
 #include "common.cuh"
 #include "api.h"
 
@@ -415,6 +416,350 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
+// ================================================================================ forward, pipelined
+// Persistent, warp-specialised forward.  One CTA per SM walks over (q tile, head, batch) work
+// items; its 6 warps have fixed roles:
+//   warp 0     TMA producer: Q of the item, then K / V tiles into a ring of ST stages; it runs
+//              ahead of the consumers, across item boundaries too
+//   warp 1     MMA issuer: S_j = Q K_j^T into one of two S buffers in TMEM, O (+)= P_j V_j into
+//              the O accumulator in TMEM.  S_{j+1} is issued BEFORE it waits for P_j, so the
+//              tensor core computes the next scores while the softmax warps work on this tile
+//   warps 2-5  softmax, thread <-> query row <-> TMEM lane: one read of S, running maximum,
+//              P = exp2(S c - m) written to shared memory in the layout the P V product reads
+// O stays in TMEM for the whole item.  The row maximum that scales P is only raised when the
+// true maximum has grown by more than 2^8 since it was last set; then the row of O (and the
+// running sum) is rescaled in place (tcgen05.ld / st).  P therefore stays below 2^8, which both
+// 16-bit formats hold, and most tiles need no rescaling at all.
+// TMEM: S0 [0,128) S1 [128,256) O [256, 256+DP) of 512 allocated columns.
+template <int DP>
+struct FwdCfg {
+  static constexpr int NBLK = (DP + 63) / 64;
+  static constexpr int TILE = NBLK * ATT_BLK;
+  static constexpr int ST = NBLK >= 2 ? 2 : 3;          // K/V ring stages
+  static constexpr int OFF_K = TILE;
+  static constexpr int OFF_V = OFF_K + ST * TILE;
+  static constexpr int OFF_P = OFF_V + ST * TILE;       // [128 q][128 kv] 16-bit, two blocks
+  static constexpr int OFF_BAR = OFF_P + 2 * ATT_BLK;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;     // barriers + alignment slack
+  static constexpr int THREADS = 192;
+};
+
+struct FwdItem {
+  int q0, h, b, n_tiles;
+};
+__device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, int w) {
+  FwdItem it;
+  // causal: the later query tiles see more keys; they go first so the long items start early
+  const int qt = p.causal ? (p.q_tiles - 1 - w % p.q_tiles) : (w % p.q_tiles);
+  it.q0 = qt * ATT_BM;
+  const int r = w / p.q_tiles;
+  it.h = r % p.H;
+  it.b = r / p.H;
+  int kv_end = p.Sk;
+  if (p.causal) kv_end = min(p.Sk, it.q0 + ATT_BM + (p.Sk - p.Sq));
+  it.n_tiles = kv_end > 0 ? (kv_end + ATT_BN - 1) / ATT_BN : 0;
+  return it;
+}
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(FwdCfg<DP>::THREADS, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const AttnParams p, const int n_items) {
+  using C = FwdCfg<DP>;
+  constexpr int NBLK = C::NBLK, TILE = C::TILE, ST = C::ST;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + C::OFF_K;
+  uint8_t* sV = smem + C::OFF_V;
+  uint8_t* sP = smem + C::OFF_P;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* bar_q_full = bars;            // TMA bytes of Q
+  uint64_t* bar_q_empty = bars + 1;       // last S product of the item has read Q
+  uint64_t* bar_k_full = bars + 2;        // [ST]
+  uint64_t* bar_v_full = bars + 2 + ST;   // [ST]
+  uint64_t* bar_k_empty = bars + 2 + 2 * ST;    // [ST] Q K^T of the tile has completed
+  uint64_t* bar_v_empty = bars + 2 + 3 * ST;    // [ST] P V of the tile has completed
+  uint64_t* bar_s_full = bars + 2 + 4 * ST;     // [2]
+  uint64_t* bar_s_empty = bar_s_full + 2;       // [2] the softmax warps hold S in registers
+  uint64_t* bar_p_full = bar_s_empty + 2;       // P is in shared memory (and O rescaled)
+  uint64_t* bar_pv_done = bar_p_full + 1;       // P V has completed: P free, O current
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv_done + 1);
+  constexpr int N_BARS = 2 + 4 * ST + 6;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&bar_s_empty[i], 4);   // lane 0 of each softmax warp
+    mbar_init(bar_p_full, 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_o = tmem + 256;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t g = 0, qc = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        const FwdItem it = fwd_item(p, w);
+        if (it.n_tiles == 0) continue;
+        ok = mbar_wait(bar_q_empty, (qc & 1) ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY);
+        if (!ok) break;
+        load_tile<NBLK>(sQ, &tq, bar_q_full, it.h, it.q0, it.b);
+        ++qc;
+        // K runs one tile ahead of V: a K stage is free as soon as its Q K^T has completed, a V
+        // stage only after its P V, and the next scores are wanted first
+        auto load_v = [&](int j, uint32_t gv) -> bool {
+          const int st = gv % ST;
+          if (!mbar_wait(&bar_v_empty[st], ((gv / ST) & 1) ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY))
+            return false;
+          load_tile<NBLK>(sV + st * TILE, &tv, &bar_v_full[st], it.h, j * ATT_BN, it.b);
+          return true;
+        };
+        for (int j = 0; j < it.n_tiles && ok; ++j) {
+          const uint32_t gk = g + j;
+          const int st = gk % ST;
+          ok = mbar_wait(&bar_k_empty[st], ((gk / ST) & 1) ^ 1, p.status, PF_ERR_TIMEOUT_EMPTY);
+          if (!ok) break;
+          load_tile<NBLK>(sK + st * TILE, &tk, &bar_k_full[st], it.h, j * ATT_BN, it.b);
+          if (j > 0) ok = load_v(j - 1, gk - 1);
+        }
+        if (ok) ok = load_v(it.n_tiles - 1, g + it.n_tiles - 1);
+        g += it.n_tiles;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
+      const uint32_t idesc_o = make_idesc_f16(128, DP, p.fmt, 0, 1);
+      uint32_t g = 0, qc = 0;
+      bool ok = true;
+      // S of global tile `gg` (tile j of the item)
+      auto issue_s = [&](uint32_t gg, int j) -> bool {
+        const int st = gg % ST, sb = gg & 1;
+        if (!mbar_wait(&bar_k_full[st], (gg / ST) & 1, p.status, PF_ERR_TIMEOUT_FULL)) return false;
+        if (!mbar_wait(&bar_s_empty[sb], ((gg >> 1) & 1) ^ 1, p.status, PF_ERR_TIMEOUT_TMEM_EMPTY))
+          return false;
+        tc_fence_after();
+        const int rem = min(ATT_BN, p.Sk - j * ATT_BN);
+        const int n_mma = (rem + 15) / 16 * 16;
+        const uint32_t id = (n_mma == ATT_BN) ? idesc_s : make_idesc_f16(128, n_mma, p.fmt, 0, 0);
+        mma_kk<DP / 16>(tmem + sb * 128, smem_u32(sQ), smem_u32(sK + st * TILE), id, false);
+        tc_commit(&bar_k_empty[st]);
+        tc_commit(&bar_s_full[sb]);
+        return true;
+      };
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        const FwdItem it = fwd_item(p, w);
+        if (it.n_tiles == 0) continue;
+        ok = mbar_wait(bar_q_full, qc & 1, p.status, PF_ERR_TIMEOUT_FULL);
+        ++qc;
+        ok = ok && issue_s(g, 0);
+        for (int j = 0; j < it.n_tiles && ok; ++j) {
+          const uint32_t gg = g + j;
+          if (j + 1 < it.n_tiles) ok = issue_s(gg + 1, j + 1);
+          else tc_commit(bar_q_empty);     // every S product of this item has been issued
+          if (!ok) break;
+          const int st = gg % ST;
+          ok = mbar_wait(bar_p_full, gg & 1, p.status, PF_ERR_TIMEOUT_FULL) &&
+               mbar_wait(&bar_v_full[st], (gg / ST) & 1, p.status, PF_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const int rem = min(ATT_BN, p.Sk - j * ATT_BN);
+          mma_k_mn(t_o, smem_u32(sP), smem_u32(sV + st * TILE), idesc_o, j > 0, (rem + 15) / 16);
+          tc_commit(&bar_v_empty[st]);
+          tc_commit(bar_pv_done);
+        }
+        g += it.n_tiles;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax (4 warps)
+    const int quad = warp & 3;                       // TMEM lane quadrant of this warp
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const float c2 = p.scale * LOG2E;
+    const int shift = p.Sk - p.Sq;
+    uint32_t g = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+      const FwdItem it = fwd_item(p, w);
+      const int qi = it.q0 + row;
+      T* dst = reinterpret_cast<T*>(p.o) + (((long long)it.b * p.Sq + qi) * p.H + it.h) * p.D;
+      float* lse_dst = p.lse + ((long long)it.b * p.H + it.h) * p.Sq + qi;
+      if (it.n_tiles == 0) {       // no key is visible to this query tile
+        if (qi < p.Sq) {
+          for (int c = 0; c < p.D / 8; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(0, 0, 0, 0);
+          *lse_dst = -INFINITY;
+        }
+        continue;
+      }
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < it.n_tiles && ok; ++j) {
+        const uint32_t gg = g + j;
+        const int sb = gg & 1;
+        const int k0 = j * ATT_BN;
+        const int rem = min(ATT_BN, p.Sk - k0);
+        const int n_chunks = ((rem + 15) / 16 * 16 + 31) / 32;
+        // a tile needs masks when it is ragged or crosses the causal diagonal of this q tile
+        const bool masked = rem < ATT_BN || (p.causal && k0 + ATT_BN - 1 > it.q0 + shift);
+        ok = mbar_wait(&bar_s_full[sb], (gg >> 1) & 1, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[4][32];
+        const uint32_t t_s = tmem + sb * 128 + lane_off;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (c < n_chunks) tmem_ld32(t_s + c * 32, s[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_s_empty[sb]);
+        float mx = -INFINITY;
+        if (!masked) {
+          // full tile: four independent chains, no visibility tests
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(s[c][i]));
+              m1 = fmaxf(m1, __uint_as_float(s[c][i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(s[c][i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(s[c][i + 3]));
+            }
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c < n_chunks) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int kj = k0 + c * 32 + i;
+                const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
+                if (vis) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+              }
+            }
+          }
+        }
+        mx *= c2;                                   // c2 > 0; -inf stays -inf
+        float alpha = 1.f;
+        if (j == 0) {
+          m_used = mx;
+        } else if (mx > m_used + 8.f) {             // also true when m_used is still -inf
+          alpha = exp2f(m_used - mx);               // exp2(-inf) = 0: nothing had accumulated
+          m_used = mx;
+        }
+        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+        if (j > 0) {
+          // P V of the previous tile has completed: the P buffer is free and O is current
+          ok = mbar_wait(bar_pv_done, (gg - 1) & 1, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < DP / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + lane_off + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(t_o + lane_off + c * 32, o);
+            }
+            tmem_st_wait();
+          }
+        }
+        float rs = 0.f;
+        if (!masked) {
+          float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+          const float nm = -m_sub;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float pv[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              pv[i] = exp2f(fmaf(__uint_as_float(s[c][i]), c2, nm));
+              pv[i + 1] = exp2f(fmaf(__uint_as_float(s[c][i + 1]), c2, nm));
+              pv[i + 2] = exp2f(fmaf(__uint_as_float(s[c][i + 2]), c2, nm));
+              pv[i + 3] = exp2f(fmaf(__uint_as_float(s[c][i + 3]), c2, nm));
+              r0 += pv[i]; r1 += pv[i + 1]; r2 += pv[i + 2]; r3 += pv[i + 3];
+            }
+            store_p_chunk<T>(sP, row, c * 32, pv);
+          }
+          rs = (r0 + r1) + (r2 + r3);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c < n_chunks) {
+              float pv[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int kj = k0 + c * 32 + i;
+                const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
+                pv[i] = vis ? exp2f(fmaf(__uint_as_float(s[c][i]), c2, -m_sub)) : 0.f;
+                rs += pv[i];
+              }
+              store_p_chunk<T>(sP, row, c * 32, pv);
+            }
+          }
+        }
+        l = l * alpha + rs;
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full);
+      }
+      if (!ok) break;
+      g += it.n_tiles;
+      // ---- epilogue of the item: O / l
+      ok = mbar_wait(bar_pv_done, (g - 1) & 1, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < DP / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + lane_off + c * 32, o);
+        tmem_ld_wait();
+        if (qi < p.Sq) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            if (c * 32 + v8 * 8 < p.D) {
+              uint4 q;
+              q.x = pack2<T>(__uint_as_float(o[v8 * 8 + 0]) * inv, __uint_as_float(o[v8 * 8 + 1]) * inv);
+              q.y = pack2<T>(__uint_as_float(o[v8 * 8 + 2]) * inv, __uint_as_float(o[v8 * 8 + 3]) * inv);
+              q.z = pack2<T>(__uint_as_float(o[v8 * 8 + 4]) * inv, __uint_as_float(o[v8 * 8 + 5]) * inv);
+              q.w = pack2<T>(__uint_as_float(o[v8 * 8 + 6]) * inv, __uint_as_float(o[v8 * 8 + 7]) * inv);
+              reinterpret_cast<uint4*>(dst)[c * 4 + v8] = q;
+            }
+          }
+        }
+      }
+      if (qi < p.Sq) *lse_dst = (l > 0.f) ? (m_used + log2f(l)) * LN2 : -INFINITY;
+      // the reads of O above have completed (tcgen05.wait::ld); the next item's first P V,
+      // which overwrites O, is ordered after them by this warp's next arrival on bar_p_full
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 // ================================================================================ backward
 // delta[b,h,i] = sum_d dO[b,i,h,d] * O[b,i,h,d]
 template <typename T>
@@ -560,26 +905,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
     }
     __syncwarp();
+    // the row statistics travel from global memory while the first two products run
+    const bool row_ok = qi < p.Sq;
+    const float lse2 = row_ok ? __ldg(p.lse + ((long long)b * p.H + h) * p.Sq + qi) * LOG2E : 0.f;
+    const float dl = row_ok ? __ldg(p.delta + ((long long)b * p.H + h) * p.Sq + qi) : 0.f;
     ok = mbar_wait(bar_mma1, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
     if (!ok) break;
     tc_fence_after();
-    const bool row_ok = qi < p.Sq;
-    const float lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * LOG2E : 0.f;
-    const float dl = row_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
+    // rows of P / dS that the products below read: the query rows that exist, rounded up to 16;
+    // a warp whose 32 rows all lie beyond them has nothing to write
+    const int q_rows = (min(ATT_BM, p.Sq - q0) + 15) / 16 * 16;
+    const bool warp_has_rows = (warp & 3) * 32 < q_rows;
+    const bool tile_masked = rem_k < ATT_BN || q0 + ATT_BM > p.Sq ||
+                             (p.causal && k0 + ATT_BN - 1 > q0 + shift);
 #pragma unroll 1
-    for (int c = half; c < nk_chunks; c += 2) {
+    for (int c = half; c < nk_chunks && warp_has_rows; c += 2) {
       uint32_t rs[32], rp[32];
       tmem_ld32(t_s + lane_off + c * 32, rs);
       tmem_ld32(t_dp + lane_off + c * 32, rp);
       tmem_ld_wait();
       float pv[32], ds[32];
+      if (!tile_masked) {       // full tile away from the causal diagonal: no visibility tests
+        const float nl = -lse2;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int kj = k0 + c * 32 + i;
-        const bool vis = row_ok && kj < p.Sk && !(p.causal && kj > qi + shift);
-        const float pr = vis ? exp2f(__uint_as_float(rs[i]) * c2 - lse2) : 0.f;
-        pv[i] = pr;
-        ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
+        for (int i = 0; i < 32; ++i) {
+          const float pr = exp2f(fmaf(__uint_as_float(rs[i]), c2, nl));
+          pv[i] = pr;
+          ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kj = k0 + c * 32 + i;
+          const bool vis = row_ok && kj < p.Sk && !(p.causal && kj > qi + shift);
+          const float pr = vis ? exp2f(__uint_as_float(rs[i]) * c2 - lse2) : 0.f;
+          pv[i] = pr;
+          ds[i] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
+        }
       }
       store_p_chunk<T>(sP, row_t, c * 32, pv);
       store_p_chunk<T>(sdS, row_t, c * 32, ds);
@@ -759,6 +1121,43 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return 0;
 }
 
+static int attn_sm_count() {
+  static int sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (!sms[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+template <typename T, int DP>
+static int launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const AttnParams& p, cudaStream_t st) {
+  using C = FwdCfg<DP>;
+  auto kern = attn_fwd_ws_kernel<T, DP>;
+  static bool done[64] = {};
+  int r = set_smem(kern, C::SMEM, done);
+  if (r) return r;
+  const int n_items = p.q_tiles * p.H * p.B;
+  if (n_items > 0) {
+    const int sms = attn_sm_count();
+    kern<<<n_items < sms ? n_items : sms, C::THREADS, C::SMEM, st>>>(tq, tk, tv, p, n_items);
+    PF_CHECK_LAUNCH();
+  }
+  if (p.q_tail > 0) {
+    // [q 128 | red 32 | scores max(Sk, 8 x 128 for the fold)] floats
+    const int bytes = (160 + (p.Sk > 1024 ? p.Sk : 1024)) * 4;
+    attn_fwd_tail_kernel<T><<<dim3(p.q_tail, p.H, p.B), 128, bytes, st>>>(p);
+    PF_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
 template <typename T, int DP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const CUtensorMap& tdo, const AttnParams& p, cudaStream_t st) {
@@ -845,7 +1244,10 @@ PF_API int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, voi
   set_views(p, q, k, v, sq, sk, sv);
   split_tail(Sq, Sk, &p.q_tiles, &p.q_tail);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  PF_ATTN_DISPATCH(launch_fwd, tq, tk, tv, p, st);
+  // PF_ATTN_SERIAL=1 selects the earlier one-role-at-a-time kernel (comparison runs)
+  static const bool serial = [] { const char* e = getenv("PF_ATTN_SERIAL"); return e && e[0] == '1'; }();
+  if (serial) PF_ATTN_DISPATCH(launch_fwd, tq, tk, tv, p, st);
+  PF_ATTN_DISPATCH(launch_fwd_ws, tq, tk, tv, p, st);
 }
 
 // dout / out: [B, Sq, H, D] contiguous; dq_accum fp32 [B,Sq,H,D] (zeroed here); dq, dk, dv

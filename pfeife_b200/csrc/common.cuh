@@ -90,11 +90,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (after recording `code`) when the limit runs out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64(), limit = wait_limit(status);
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > limit) {
-      report(status, code);
-      return false;
+  // The limit lives in global memory and the clock costs a few cycles to read: both are looked
+  // at only every 256 polls, so a wait that is satisfied soon pays for neither.
+  long long t0 = 0, limit = 0;
+  for (unsigned polls = 1; !mbar_try_wait(bar, parity); ++polls) {
+    if ((polls & 255u) == 0) {
+      if (limit == 0) { t0 = clock64(); limit = wait_limit(status); }
+      else if (clock64() - t0 > limit) {
+        report(status, code);
+        return false;
+      }
     }
   }
   return true;
@@ -236,11 +241,14 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* status,
                                                   int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64(), limit = wait_limit(status);
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if (clock64() - t0 > limit) {
-      report(status, code);
-      return false;
+  long long t0 = 0, limit = 0;
+  for (unsigned polls = 1; !mbar_try_wait_cluster(bar, parity); ++polls) {
+    if ((polls & 255u) == 0) {
+      if (limit == 0) { t0 = clock64(); limit = wait_limit(status); }
+      else if (clock64() - t0 > limit) {
+        report(status, code);
+        return false;
+      }
     }
   }
   return true;

@@ -71,7 +71,16 @@ struct DpArgs {
   int epoch;                   // epoch of this call's first barrier (same on every rank)
   int sync_base;               // arrivals at local_sync[0] before this call
   int* status;
+  long long* trace;            // optional: nanosecond timestamps of the phases (CTA 0)
 };
+
+__device__ __forceinline__ void dp_mark(const DpArgs& a, int slot) {
+  if (a.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    a.trace[slot] = t;
+  }
+}
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -147,7 +156,9 @@ dp_fused_kernel(const DpArgs a) {
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   int kbar = 0;
 
+  dp_mark(a, 0);
   bool ok = job_barrier(a, kbar++);            // every rank's gradients are complete
+  dp_mark(a, 1);
   if (!ok) { if (tid == 0 && a.found_inf) *a.found_inf = 1.f; return; }
 
   // ---- reduce-scatter into the local bucket.  One or two 16-byte vectors per thread from each
@@ -180,6 +191,7 @@ dp_fused_kernel(const DpArgs a) {
     }
   }
 
+  dp_mark(a, 2);
   bool skip = false;
   if (a.check_inf) {
     if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0)
@@ -192,19 +204,32 @@ dp_fused_kernel(const DpArgs a) {
   } else if (a.found_given) {
     skip = *reinterpret_cast<const volatile float*>(a.found_inf) != 0.f;
   }
+  dp_mark(a, 3);
   float gs = a.grad_scale;
   if (a.loss_scale) gs /= *a.loss_scale;
   const float step = (float)(a.applied_steps ? *a.applied_steps + 1 : a.host_step);
 
-  // ---- partitioned Adam/AdamW; new 16-bit weights go to every rank by P2P stores
+  // ---- partitioned Adam/AdamW; new 16-bit weights go to every rank by P2P stores.  A thread
+  //      updates 8 consecutive elements, so that every remote store carries 16 bytes (a warp
+  //      writes 512 contiguous bytes per peer; 8-byte stores reached a fifth of the link rate).
   int gi = 0;
   float lr = 0.f, b1 = 0.f, b2 = 0.f, eps = 0.f, wd = 0.f, inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
   bool adamw = true;
   long long g_lo = 0, g_hi = -1, local_below = 0, master_from = 0;
-  for (long long i = tid; i < nvec; i += stride) {
-    const long long e = lo + i * 4;
-    float4 g4 = *reinterpret_cast<const float4*>(a.grad[a.rank] + e);
-    *reinterpret_cast<float4*>(a.grad[a.rank] + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long nvec8 = (hi - lo) / 8;       // whole 8-element groups; a 4-element tail follows
+  const long long n_items = nvec8 + (((hi - lo) & 7) ? 1 : 0);
+  for (long long i = tid; i < n_items; i += stride) {
+    const long long e = lo + i * 8;
+    const bool two = i < nvec8;                // false: the trailing 4 elements of the shard
+    float4 g4[2], w4[2], m4[2], v4[2];
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h == 0 || two) {
+        g4[h] = *reinterpret_cast<const float4*>(a.grad[a.rank] + e + 4 * h);
+        *reinterpret_cast<float4*>(a.grad[a.rank] + e + 4 * h) = z4;
+      }
+    }
     if (skip) continue;
     if (e < g_lo || e >= g_hi) {               // entered another optimizer group
       for (gi = 0; gi < a.ngroups - 1 && !(e >= a.group[gi].lo && e < a.group[gi].hi); ++gi) {}
@@ -215,47 +240,79 @@ dp_fused_kernel(const DpArgs a) {
       inv_bc1 = 1.f / (1.f - powf(b1, step));
       inv_sqrt_bc2 = rsqrtf(1.f - powf(b2, step));
     }
-    float4 w4 = *reinterpret_cast<const float4*>(a.master[a.rank] + e);
-    float4 m4 = *reinterpret_cast<const float4*>(a.m + i * 4);
-    float4 v4 = *reinterpret_cast<const float4*>(a.v + i * 4);
-    float g[4] = {g4.x, g4.y, g4.z, g4.w}, w[4] = {w4.x, w4.y, w4.z, w4.w};
-    float m[4] = {m4.x, m4.y, m4.z, m4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float gr = g[j] * gs;
-      if (adamw) w[j] *= (1.f - lr * wd);
-      else gr += wd * w[j];
-      m[j] = b1 * m[j] + (1.f - b1) * gr;
-      v[j] = b2 * v[j] + (1.f - b2) * gr * gr;
-      w[j] -= lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + eps);
-    }
-    *reinterpret_cast<float4*>(a.m + i * 4) = make_float4(m[0], m[1], m[2], m[3]);
-    *reinterpret_cast<float4*>(a.v + i * 4) = make_float4(v[0], v[1], v[2], v[3]);
-    const float4 nw = make_float4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<float4*>(a.master[a.rank] + e) = nw;
-    uint2 q = make_uint2(0, 0);
-    if (a.lp[a.rank]) {
-      if (a.lp_dtype == PF_BF16) {
-        __nv_bfloat162 x = __floats2bfloat162_rn(w[0], w[1]), y = __floats2bfloat162_rn(w[2], w[3]);
-        q = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&y));
-      } else {
-        __half2 x = __floats2half2_rn(w[0], w[1]), y = __floats2half2_rn(w[2], w[3]);
-        q = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&y));
+    for (int h = 0; h < 2; ++h) {
+      if (h == 0 || two) {
+        w4[h] = *reinterpret_cast<const float4*>(a.master[a.rank] + e + 4 * h);
+        m4[h] = *reinterpret_cast<const float4*>(a.m + i * 8 + 4 * h);
+        v4[h] = *reinterpret_cast<const float4*>(a.v + i * 8 + 4 * h);
       }
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q;
     }
-    const bool push_lp = e >= local_below, push_master = e >= master_from;
+    uint32_t q[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int p = 0; p < WORLD; ++p) {
-      if (p == a.rank) continue;
-      if (push_master) *reinterpret_cast<float4*>(a.master[p] + e) = nw;
-      if (a.lp[p] && push_lp)
-        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q;
+    for (int h = 0; h < 2; ++h) {
+      if (h == 0 || two) {
+        float g[4] = {g4[h].x, g4[h].y, g4[h].z, g4[h].w};
+        float w[4] = {w4[h].x, w4[h].y, w4[h].z, w4[h].w};
+        float m[4] = {m4[h].x, m4[h].y, m4[h].z, m4[h].w};
+        float v[4] = {v4[h].x, v4[h].y, v4[h].z, v4[h].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float gr = g[j] * gs;
+          if (adamw) w[j] *= (1.f - lr * wd);
+          else gr += wd * w[j];
+          m[j] = b1 * m[j] + (1.f - b1) * gr;
+          v[j] = b2 * v[j] + (1.f - b2) * gr * gr;
+          w[j] -= lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + eps);
+        }
+        *reinterpret_cast<float4*>(a.m + i * 8 + 4 * h) = make_float4(m[0], m[1], m[2], m[3]);
+        *reinterpret_cast<float4*>(a.v + i * 8 + 4 * h) = make_float4(v[0], v[1], v[2], v[3]);
+        w4[h] = make_float4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<float4*>(a.master[a.rank] + e + 4 * h) = w4[h];
+        if (a.lp_dtype == PF_BF16) {
+          __nv_bfloat162 x = __floats2bfloat162_rn(w[0], w[1]), y = __floats2bfloat162_rn(w[2], w[3]);
+          q[2 * h] = *reinterpret_cast<uint32_t*>(&x); q[2 * h + 1] = *reinterpret_cast<uint32_t*>(&y);
+        } else {
+          __half2 x = __floats2half2_rn(w[0], w[1]), y = __floats2half2_rn(w[2], w[3]);
+          q[2 * h] = *reinterpret_cast<uint32_t*>(&x); q[2 * h + 1] = *reinterpret_cast<uint32_t*>(&y);
+        }
+      }
+    }
+    // group boundaries are multiples of 128 elements and shards of 4: an 8-element group never
+    // straddles a group, and its two halves share the push decisions
+    const bool push_lp = e >= local_below, push_master = e >= master_from;
+    if (two) {
+      const uint4 q8 = make_uint4(q[0], q[1], q[2], q[3]);
+      if (a.lp[a.rank])
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q8;
+#pragma unroll
+      for (int p = 0; p < WORLD; ++p) {
+        if (p == a.rank) continue;
+        if (push_master) {
+          *reinterpret_cast<float4*>(a.master[p] + e) = w4[0];
+          *reinterpret_cast<float4*>(a.master[p] + e + 4) = w4[1];
+        }
+        if (a.lp[p] && push_lp)
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q8;
+      }
+    } else {
+      const uint2 q4 = make_uint2(q[0], q[1]);
+      if (a.lp[a.rank])
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q4;
+#pragma unroll
+      for (int p = 0; p < WORLD; ++p) {
+        if (p == a.rank) continue;
+        if (push_master) *reinterpret_cast<float4*>(a.master[p] + e) = w4[0];
+        if (a.lp[p] && push_lp)
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q4;
+      }
     }
   }
 
+  dp_mark(a, 4);
   ok = job_barrier(a, kbar++);                  // all weights have landed everywhere
   if (!ok) return;
+  dp_mark(a, 5);
 
   // ---- every rank has read what it needed of this bucket: clear the part of it that other
   //      ranks own (local stores; the own shard was cleared by the update loop)
@@ -267,6 +324,7 @@ dp_fused_kernel(const DpArgs a) {
     for (long long i = tid; i < n_after; i += stride)
       *reinterpret_cast<float4*>(a.grad[a.rank] + hi + i * 4) = z4;
   }
+  dp_mark(a, 6);
 }
 
 }  // namespace pf
@@ -283,6 +341,9 @@ using namespace pf;
 // through *barriers_out; `arrivals_before` is the sum over earlier calls of barriers * grid
 // (*grid_out).  `applied_steps` (device int, may be null) counts the optimizer steps that were
 // not skipped; the bias correction uses it, so a step skipped on an overflow does not count.
+// `trace` (device int64[7], may be null) receives the global-timer value in nanoseconds when CTA 0
+// enters the kernel, leaves the entry barrier, finishes its share of the reduce, knows the skip
+// decision, finishes its share of the update, leaves the last barrier, and finishes clearing.
 PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const* master,
                             void* const* lp, void* const* flags, void* m, void* v,
                             void* local_sync, long long shard_lo, long long shard_hi,
@@ -291,7 +352,7 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
                             float grad_scale, int lp_dtype, int check_inf, int found_given,
                             const void* loss_scale, void* found_inf, int epoch,
                             int arrivals_before, int* barriers_out, int* grid_out, int* status,
-                            int sm_count, void* stream) {
+                            void* trace, int sm_count, void* stream) {
   if (world < 1 || world > DP_MAX || ngroups < 1 || ngroups > DP_MAX_GROUPS) return -3;
   if ((shard_lo % 4) || (shard_hi % 4) || (total % 4)) return -2;
   if (shard_lo < 0 || shard_hi < shard_lo || shard_hi > total) return -2;
@@ -318,7 +379,7 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   a.check_inf = check_inf; a.found_given = check_inf ? 0 : found_given;
   a.loss_scale = (const float*)loss_scale; a.found_inf = (float*)found_inf;
   a.applied_steps = (const int*)applied_steps; a.host_step = host_step;
-  a.epoch = epoch; a.status = status;
+  a.epoch = epoch; a.status = status; a.trace = (long long*)trace;
   // two 512-thread CTAs per SM: all CTAs are co-resident (the barriers rely on it; a CTA that
   // has to wait for an SM delays the barrier, within the wait limit)
   const int grid = 2 * (sm_count > 0 ? sm_count : 148);

@@ -127,6 +127,49 @@ embed_bwd_kernel(const T* __restrict__ dout, const long long* __restrict__ ids,
 
 // Rotary embedding on a (possibly strided) x[B, S, H, D] (half-split convention: pairs
 // (i, i + D/2)) into a contiguous output.  inverse != 0 applies the transpose rotation (the backward).
+// Rotary embedding, 16 bytes per access: a thread rotates 8 consecutive pairs (x[d], x[d+D/2]),
+// d = 8 * v .. 8 * v + 7.  Needs D/2 a multiple of 8 and 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cos_t,
+                const float* __restrict__ sin_t, long long B, int S, int H, int D,
+                long long stride_b, long long stride_s, long long stride_h, int inverse) {
+  const int half = D / 2, hv = half / 8;
+  const long long total = B * S * H * hv;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
+    const int v = (int)(i % hv);
+    long long r = i / hv;
+    const int h = (int)(r % H); r /= H;
+    const int s = (int)(r % S);
+    const long long b = r / S;
+    const T* src = x + b * stride_b + (long long)s * stride_s + (long long)h * stride_h + v * 8;
+    const uint4 u1 = *reinterpret_cast<const uint4*>(src);
+    const uint4 u2 = *reinterpret_cast<const uint4*>(src + half);
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + (long long)s * half + v * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + (long long)s * half + v * 8);
+    const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const T* e1 = reinterpret_cast<const T*>(&u1);
+    const T* e2 = reinterpret_cast<const T*>(&u2);
+    uint4 o1, o2;
+    T* q1 = reinterpret_cast<T*>(&o1);
+    T* q2 = reinterpret_cast<T*>(&o2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x1 = to_f32<T>(e1[j]), x2 = to_f32<T>(e2[j]);
+      const float sj = inverse ? -sn[j] : sn[j];
+      q1[j] = from_f32<T>(x1 * c[j] - x2 * sj);
+      q2[j] = from_f32<T>(x2 * c[j] + x1 * sj);
+    }
+    // the output is always contiguous [B, S, H, D]
+    T* dst = out + ((b * S + s) * H + h) * (long long)D + v * 8;
+    *reinterpret_cast<uint4*>(dst) = o1;
+    *reinterpret_cast<uint4*>(dst + half) = o2;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cos_t,
@@ -248,8 +291,31 @@ PF_API int pf_rope(const void* x, void* out, const void* cos_t, const void* sin_
   const long long total = B * S * H * (D / 2);
   if (total <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  long long blocks = (total + 255) / 256;
   const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 8;
+  const bool vec = dtype != PF_F32 && D % 16 == 0 && stride_b % 8 == 0 && stride_s % 8 == 0 &&
+                   stride_h % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0;
+  if (vec) {
+    long long vblocks = (total / 8 + 255) / 256;
+    if (vblocks > cap) vblocks = cap;
+    if (vblocks < 1) vblocks = 1;
+    switch (dtype) {
+      case PF_F16:
+        rope_vec_kernel<__half><<<(unsigned)vblocks, 256, 0, st>>>(
+            (const __half*)x, (__half*)out, (const float*)cos_t, (const float*)sin_t, B, S, H, D,
+            stride_b, stride_s, stride_h, inverse);
+        break;
+      default:
+        rope_vec_kernel<__nv_bfloat16><<<(unsigned)vblocks, 256, 0, st>>>(
+            (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (const float*)cos_t,
+            (const float*)sin_t, B, S, H, D, stride_b, stride_s, stride_h, inverse);
+    }
+    PF_CHECK_LAUNCH();
+    return 0;
+  }
+  long long blocks = (total + 255) / 256;
   if (blocks > cap) blocks = cap;
   PF_DISPATCH3(dtype, (rope_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
       (const T*)x, (T*)out, (const float*)cos_t, (const float*)sin_t, B, S, H, D, stride_b,

@@ -565,8 +565,9 @@ static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, co
   constexpr int V = 16 / sizeof(T);
   if (N % V) return -2;
   const int nvec = N / V;
-  if (sizeof(T) == 2 && nvec <= 32 * 8) {
-    // input gradient: warp per row; parameter gradients: column reduction over row slabs
+  if (sizeof(T) == 2 && nvec <= 32 * 16) {
+    // input gradient: warp per row (rows of up to 4096 16-bit elements: Llama's hidden size);
+    // parameter gradients: column reduction over row slabs
     const unsigned grid = (unsigned)((rows + 7) / 8);
 #define PF_NORM_BWD_DX(NV)                                                                   \
     norm_bwd_dx_kernel<T, NV><<<grid, 256, 0, st>>>((const T*)dy, (const T*)h, gamma, mean,  \
@@ -574,7 +575,9 @@ static int norm_bwd_launch(const void* dy, const void* h, const float* gamma, co
     if (nvec <= 32 * 2) PF_NORM_BWD_DX(2);
     else if (nvec <= 32 * 4) PF_NORM_BWD_DX(4);
     else if (nvec <= 32 * 6) PF_NORM_BWD_DX(6);
-    else PF_NORM_BWD_DX(8);
+    else if (nvec <= 32 * 8) PF_NORM_BWD_DX(8);
+    else if (nvec <= 32 * 12) PF_NORM_BWD_DX(12);
+    else PF_NORM_BWD_DX(16);
 #undef PF_NORM_BWD_DX
     // enough row slabs to fill the GPU once with (column blocks x slabs) CTAs, few enough
     // that folding them (norm_bwd_finish_kernel) stays negligible

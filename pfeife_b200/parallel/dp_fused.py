@@ -156,7 +156,8 @@ def launch_fused_step(rank: int, world: int, t_grad, t_master, t_lp, t_flags, m:
                       applied_steps: Optional[torch.Tensor], host_step: int, grad_scale: float,
                       lp_dtype: Optional[torch.dtype], check_inf: bool, found_given: bool,
                       loss_scale: Optional[torch.Tensor], found_inf: torch.Tensor, epoch: int,
-                      arrivals: int, device) -> Tuple[int, int]:
+                      arrivals: int, device, trace: Optional[torch.Tensor] = None
+                      ) -> Tuple[int, int]:
     """One launch of the fused kernel on the current stream.  `t_*` are pointer tables
     (``_table``) with one entry per rank; `groups` holds (lo, hi, local_below, master_from) and
     `hyper` (lr, beta1, beta2, eps, weight_decay, adamw) per optimizer group.  Returns
@@ -174,8 +175,8 @@ def launch_fused_step(rank: int, world: int, t_grad, t_master, t_lp, t_flags, m:
         ptr(applied_steps), int(host_step), c_f(grad_scale),
         dt(lp_dtype) if lp_dtype is not None else 0, int(check_inf), int(found_given),
         ptr(loss_scale), ptr(found_inf), int(epoch) & 0x7FFFFFFF, int(arrivals) & 0x7FFFFFFF,
-        ctypes.byref(nbar), ctypes.byref(grid), ptr(kx.status_word(device)), sm_count(device),
-        stream())
+        ctypes.byref(nbar), ctypes.byref(grid), ptr(kx.status_word(device)), ptr(trace),
+        sm_count(device), stream())
     check(code, "pf_dp_fused_step")
     return nbar.value, grid.value
 
@@ -215,6 +216,7 @@ class FusedDP(NcclDP):
         # barrier bookkeeping, identical on every rank: epoch of the next call's first barrier
         # and the arrivals counted so far (both wrap; the kernel compares modulo 2^32)
         self.epoch, self.arrivals = 1, 0
+        self.trace = torch.zeros(8, dtype=torch.int64, device=self.device)
         # fp32 masters are pushed to the peers only where some op reads them in fp32; without a
         # 16-bit shadow everything is read in fp32
         self.master_from = dict(params.master_from) if params.lp is not None else {}
@@ -258,13 +260,22 @@ class FusedDP(NcclDP):
             params.lp.dtype if params.lp is not None else None,
             check_inf=bool(fp16 and not found_agreed), found_given=bool(fp16 and found_agreed),
             loss_scale=scaler.scale_tensor, found_inf=params.found_inf, epoch=self.epoch,
-            arrivals=self.arrivals, device=self.device)
+            arrivals=self.arrivals, device=self.device, trace=self.trace)
         self.epoch += nbar
         self.arrivals += nbar * grid
         self.calls += 1
         kx.step_advance(params.applied_steps, params.found_inf if fp16 else None)
         if fp16:
             scaler.update(params.found_inf)
+
+    def phase_ms(self) -> Dict[str, float]:
+        """Durations of the last fused step's phases on this rank (device timer): waiting at the
+        entry barrier for the slowest replica, the reduce-scatter, the skip agreement, the
+        update with its pushes, the closing barrier, clearing the bucket."""
+        t = [int(v) for v in self.trace.cpu().tolist()]
+        names = ("entry_wait", "reduce_scatter", "agree", "update_and_push", "exit_wait", "clear")
+        return {n: round((t[i + 1] - t[i]) / 1e6, 3) for i, n in enumerate(names)
+                if t[i + 1] and t[i]}
 
     def gather_master(self) -> None:
         """Makes every replica's fp32 master buffer complete (for checkpoints): between steps a

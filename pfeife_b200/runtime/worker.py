@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import contextlib
 import enum
+import os
 import threading
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
@@ -213,6 +214,8 @@ class StageWorker:
         self.graph_pool = None
         self.slot_of: Dict[Tuple[int, int], int] = {}
         self.graph_key: Dict[Tuple[int, int], Tuple[int, int, int]] = {}
+        self._example_ins: Dict[int, List[Any]] = {}     # stage -> inputs of an eager forward
+        self._captured_upfront = False
         # stages whose row-sharded weights were completed since the last optimizer step
         self.gathered_stages: set = set()
         # True when the job has more ranks than this stage's replicas (set by the front-end)
@@ -402,6 +405,8 @@ class StageWorker:
                 self.fw_outputs[(stage, mb)] = gs.static_outs
                 return
         self.graph_key.pop((stage, mb), None)
+        if self.use_graphs and torch.is_grad_enabled() and stage not in self._example_ins:
+            self._example_ins[stage] = list(ins)     # shapes / dtypes for the capture phase
         if gather:
             from ..ops import functional as Fn
             Fn.gather_session(True)
@@ -430,21 +435,63 @@ class StageWorker:
             return None if gs.failed else gs
         gs = _GraphedStage()
         self.graphs[key] = gs
-        try:
-            if gather:
-                from ..ops import functional as Fn
-                Fn.gather_session(True)
+        # A capture can break on work that only happens the first time a process does it (a
+        # library handle or a kernel image created lazily inside the captured region): the
+        # broken attempt has then done that work, and a second attempt on a fresh memory pool
+        # goes through.  Only when that fails too does the stage stay on the eager path.
+        for attempt in (0, 1):
             try:
-                self._capture(gs, sp, stage, ins)
-            finally:
                 if gather:
-                    Fn.gather_session(False)
-        except Exception as e:   # the stage stays on the eager path
-            gs.failed = True
-            self.log.warning("CUDA graph capture of stage %d failed (%s: %s); running it eagerly",
-                             stage, type(e).__name__, e)
-            return None
-        return gs
+                    from ..ops import functional as Fn
+                    Fn.gather_session(True)
+                try:
+                    self._capture(gs, sp, stage, ins)
+                finally:
+                    if gather:
+                        Fn.gather_session(False)
+                return gs
+            except Exception as e:
+                import traceback
+                where = " <- ".join(f"{f.name}:{f.lineno}" for f in
+                                    reversed(traceback.extract_tb(e.__traceback__)[-4:]))
+                cause = e.__context__
+                self.log.log(20 if attempt == 0 else 30,
+                             "CUDA graph capture of stage %d failed (%s: %s) at %s%s; %s", stage,
+                             type(e).__name__, str(e).splitlines()[0], where,
+                             f" after {type(cause).__name__}: {str(cause).splitlines()[0]}"
+                             if cause is not None else "",
+                             "trying once more" if attempt == 0 else "running it eagerly")
+                # a capture that broke leaves its memory pool marked as recording
+                self.graph_pool = None
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize(self.device)
+        gs.failed = True
+        return None
+
+    def capture_all(self) -> None:
+        """Captures the graphs of every (stage, in-flight slot) of this rank's step program in
+        one go, between two steps, from the inputs an eager step left behind.  Nothing of the
+        step is in flight then: no transfer is posted, no front-end thread computes, and a
+        capture's device-wide synchronisation cannot wait for a peer.  (Capturing lazily inside
+        the step works for a single stage per job; with stage hand-offs in flight captures were
+        invalidated.)"""
+        self._captured_upfront = True
+        defers = self._defers_gather()
+        seen_stage: set = set()
+        for st in self.steps:
+            if st.work != StepWork.FORWARD:
+                continue
+            stage, mb = st.node_id, st.batch_id
+            ins = self._example_ins.get(stage)
+            if ins is None:
+                continue
+            gather = int(defers and stage not in seen_stage)
+            seen_stage.add(stage)
+            key = (stage, self.slot_of.get((stage, mb), 0), gather)
+            if key in self.graphs:
+                continue
+            self._graph_for(self.part.stages[stage], stage, mb, ins, gather)
+        self.graph_key.clear()
 
     def _capture(self, gs: _GraphedStage, sp: StageSpec, stage: int, ins: List[Any]) -> None:
         if self.graph_pool is None:
@@ -666,6 +713,10 @@ class StageWorker:
     def run(self, training: bool = True) -> None:
         steps = self.steps if training else self.eval_steps
         comm = self.comm if training else self.eval_comm
+        if training and self.use_graphs and not self._captured_upfront and \
+                self.train_steps_done >= self.graph_warmup_steps and \
+                os.environ.get("PF_GRAPH_CAPTURE", "upfront") != "lazy":
+            self.capture_all()
         if self.is_main:
             self.distribute_inputs(comm)
         ctx = contextlib.nullcontext() if training else torch.no_grad()

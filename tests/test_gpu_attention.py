@@ -32,6 +32,8 @@ CASES = [  # B, H, Sq, Sk, D, causal
     (1, 2, 256, 258, 64, False),
     (1, 2, 261, 261, 64, False),     # five leftover rows: a ragged tensor-core tile instead
     (1, 2, 258, 300, 64, True),      # causal with Sq != Sk: ragged key tiles in the backward
+    (1, 4, 1024, 1024, 128, True),   # several query tiles per head, many key tiles each
+    (3, 5, 384, 640, 64, False),     # more work items than one wave of a small grid
 ]
 
 
@@ -58,6 +60,29 @@ def test_attention_fwd_bwd(dtype, B, H, Sq, Sk, D, causal):
         err = (got.float() - want).abs().max().item()
         mag = want.abs().max().item()
         assert err <= tol * 4 * max(1.0, mag), f"{name}: err {err} (max |ref| {mag})"
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_forward_when_the_row_maximum_keeps_growing(D):
+    """Later key tiles carry much larger scores than earlier ones, so the maximum that scales
+    the probabilities has to be raised (and the accumulated output rescaled) several times
+    within one row; keys of the last tile are tiny again (no rescale there)."""
+    from pfeife_b200.ops import kernels as kx
+    B, H, Sq, Sk = 1, 2, 256, 768
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(B, Sq, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Sk, H, D, device="cuda", generator=g)
+    ramp = torch.tensor([0.1, 1.0, 4.0, 12.0, 30.0, 0.05], device="cuda").repeat_interleave(128)
+    k = (k * ramp[None, :, None, None]).to(torch.bfloat16)
+    v = torch.randn(B, Sk, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o, lse = kx.attn_fwd(q, k, v, False, scale)
+    torch.cuda.synchronize()
+    kx.check_status()
+    o_ref, lse_ref = ref_attn(q, k, v, False, scale)
+    assert torch.isfinite(o.float()).all()
+    assert (o.float() - o_ref).abs().max() <= 4e-2
+    assert ((lse - lse_ref).abs() / lse_ref.abs().clamp_min(1.0)).max() <= 1e-2
 
 
 def test_attention_on_fused_qkv_views():

@@ -40,9 +40,10 @@ def _launch(st, rank, world, shard, total, groups, hyper, m, v, **kw):
         arrivals=kw.get("arrivals", 0), device=torch.device("cuda", 0))
 
 
-def test_single_rank_two_groups_match_torch_adamw_over_three_steps():
+@pytest.mark.parametrize("n", [1 << 20, (1 << 20) + 4])      # whole 8-element groups / 4 left over
+def test_single_rank_two_groups_match_torch_adamw_over_three_steps(n):
     from pfeife_b200.ops import kernels as kx
-    n, cut = 1 << 20, 3 << 18
+    cut = 3 << 18
     st = _setup(n)
     m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
     ref = st["master"][0].clone()
