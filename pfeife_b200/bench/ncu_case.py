@@ -1,7 +1,7 @@
 """Small single-kernel workloads for Nsight Compute captures (a few launches, inputs larger than
 L2, a few hundred MB on the device at most).
 
-    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_plain_pair,gemm_wgrad,attn,norm,adamw,ce,unet,llama}
+    python -m pfeife_b200.bench.ncu_case {gemm,gemm_plain,gemm_plain_single,gemm_plain_pair,gemm_wgrad,attn,attn_unet,attn_llama,norm,adamw,ce,unet,llama}
 
 Each case launches its kernel(s) a handful of times and checks the kernel status word, so the
 same command can first be run plainly (must exit 0) and then under
@@ -54,6 +54,13 @@ def main(argv=None) -> int:
         for _ in range(reps):
             o, lse = kx.attn_fwd(q, k, v, False, 1 / math.sqrt(D))
             kx.attn_bwd(do, q, k, v, o, lse, False, 1 / math.sqrt(D), packed=True)
+    elif which in ("attn_unet", "attn_llama"):   # long sequences: many key tiles per query tile
+        B, S, H, D, causal = (2, 4096, 10, 64, False) if which == "attn_unet" else \
+            (1, 2048, 32, 128, True)
+        q, k, v, do = (torch.randn(B, S, H, D, device=dev).to(torch.bfloat16) for _ in range(4))
+        for _ in range(reps):
+            o, lse = kx.attn_fwd(q, k, v, causal, 1 / math.sqrt(D))
+            kx.attn_bwd(do, q, k, v, o, lse, causal, 1 / math.sqrt(D))
     elif which == "norm":
         rows, N = 49344, 1408
         x = torch.randn(rows, N, device=dev).to(torch.float16)

@@ -426,7 +426,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 //              tensor core computes the next scores while the softmax warps work on this tile
 //   warps 2-5  softmax, thread <-> query row <-> TMEM lane: one read of S, running maximum,
 //              P = exp2(S c - m) written to shared memory in the layout the P V product reads
-// O stays in TMEM for the whole item.  The row maximum that scales P is only raised when the
+// P has two buffers, so a tile's probabilities are computed and stored while the previous
+// tile's P V still runs.  O stays in TMEM for the whole item.  The row maximum that scales P is only raised when the
 // true maximum has grown by more than 2^8 since it was last set; then the row of O (and the
 // running sum) is rescaled in place (tcgen05.ld / st).  P therefore stays below 2^8, which both
 // 16-bit formats hold, and most tiles need no rescaling at all.
@@ -438,8 +439,9 @@ struct FwdCfg {
   static constexpr int ST = NBLK >= 2 ? 2 : 3;          // K/V ring stages
   static constexpr int OFF_K = TILE;
   static constexpr int OFF_V = OFF_K + ST * TILE;
-  static constexpr int OFF_P = OFF_V + ST * TILE;       // [128 q][128 kv] 16-bit, two blocks
-  static constexpr int OFF_BAR = OFF_P + 2 * ATT_BLK;
+  static constexpr int OFF_P = OFF_V + ST * TILE;       // two buffers of [128 q][128 kv] 16-bit
+  static constexpr int P_BYTES = 2 * ATT_BLK;           // (two swizzled blocks each)
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;     // barriers + alignment slack
   static constexpr int THREADS = 192;
 };
@@ -485,9 +487,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   uint64_t* bar_s_full = bars + 2 + 4 * ST;     // [2]
   uint64_t* bar_s_empty = bar_s_full + 2;       // [2] the softmax warps hold S in registers
   uint64_t* bar_p_full = bar_s_empty + 2;       // P is in shared memory (and O rescaled)
-  uint64_t* bar_pv_done = bar_p_full + 1;       // P V has completed: P free, O current
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv_done + 1);
-  constexpr int N_BARS = 2 + 4 * ST + 6;
+  uint64_t* bar_pv_done = bar_p_full + 1;       // [2], by tile parity: P V has completed (that P
+                                                // buffer is free, O holds every tile up to it)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv_done + 2);
+  constexpr int N_BARS = 2 + 4 * ST + 7;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -577,9 +580,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           if (!ok) break;
           tc_fence_after();
           const int rem = min(ATT_BN, p.Sk - j * ATT_BN);
-          mma_k_mn(t_o, smem_u32(sP), smem_u32(sV + st * TILE), idesc_o, j > 0, (rem + 15) / 16);
+          mma_k_mn(t_o, smem_u32(sP + (gg & 1) * C::P_BYTES), smem_u32(sV + st * TILE), idesc_o,
+                   j > 0, (rem + 15) / 16);
           tc_commit(&bar_v_empty[st]);
-          tc_commit(bar_pv_done);
+          tc_commit(&bar_pv_done[gg & 1]);
         }
         g += it.n_tiles;
       }
@@ -664,12 +668,22 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           m_used = mx;
         }
         const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-        if (j > 0) {
-          // P V of the previous tile has completed: the P buffer is free and O is current
-          ok = mbar_wait(bar_pv_done, (gg - 1) & 1, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+        // This tile's P buffer was last read by the P V of the tile before the previous one
+        // (any item): long done, so the probabilities below are computed while the previous
+        // tile's P V still runs.  (Parity of the phase before this tile's own on that barrier;
+        // on a fresh barrier the wait passes.)
+        uint8_t* sPj = sP + (gg & 1) * C::P_BYTES;
+        ok = mbar_wait(&bar_pv_done[gg & 1], ((gg >> 1) & 1) ^ 1, p.status,
+                       PF_ERR_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // rare: the row maximum grew by more than 2^8.  O must hold every earlier tile of
+          // the item before it is rescaled: wait for the previous tile's P V
+          ok = mbar_wait(&bar_pv_done[(gg - 1) & 1], ((gg - 1) >> 1) & 1, p.status,
+                         PF_ERR_TIMEOUT_TMEM_FULL);
           if (!ok) break;
           tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          {
 #pragma unroll
             for (int c = 0; c < DP / 32; ++c) {
               uint32_t o[32];
@@ -697,7 +711,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
               pv[i + 3] = exp2f(fmaf(__uint_as_float(s[c][i + 3]), c2, nm));
               r0 += pv[i]; r1 += pv[i + 1]; r2 += pv[i + 2]; r3 += pv[i + 3];
             }
-            store_p_chunk<T>(sP, row, c * 32, pv);
+            store_p_chunk<T>(sPj, row, c * 32, pv);
           }
           rs = (r0 + r1) + (r2 + r3);
         } else {
@@ -712,7 +726,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
                 pv[i] = vis ? exp2f(fmaf(__uint_as_float(s[c][i]), c2, -m_sub)) : 0.f;
                 rs += pv[i];
               }
-              store_p_chunk<T>(sP, row, c * 32, pv);
+              store_p_chunk<T>(sPj, row, c * 32, pv);
             }
           }
         }
@@ -725,7 +739,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       if (!ok) break;
       g += it.n_tiles;
       // ---- epilogue of the item: O / l
-      ok = mbar_wait(bar_pv_done, (g - 1) & 1, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait(&bar_pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, p.status,
+                     PF_ERR_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -829,16 +844,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
+  // Q / dO tiles: two stages when a tile is one block (head dim <= 64), so that the next query
+  // tile travels while this one is worked on; larger head dims leave room for one stage only
+  constexpr int QST = (NBLK == 1) ? 2 : 1;
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE;
-  uint8_t* sQ = sV + TILE;
-  uint8_t* sdO = sQ + TILE;
-  uint8_t* sP = sdO + TILE;                  // [q][kv] 16-bit, 2 blocks
+  uint8_t* sQ0 = sV + TILE;                  // [QST] tiles
+  uint8_t* sdO0 = sQ0 + QST * TILE;          // [QST] tiles
+  uint8_t* sP = sdO0 + QST * TILE;           // [q][kv] 16-bit, 2 blocks
   uint8_t* sdS = sP + 2 * ATT_BLK;           // [q][kv] 16-bit, 2 blocks
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * ATT_BLK);
-  uint64_t* bar_kv = bars, *bar_q = bars + 1, *bar_mma1 = bars + 2, *bar_mma2 = bars + 3,
-          *bar_dq = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_kv = bars, *bar_q = bars + 1 /* [2] */, *bar_mma1 = bars + 3, *bar_mma2 = bars + 4,
+          *bar_dq = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row_t = (warp & 3) * 32 + lane;     // TMEM lane / tile row of this thread
@@ -847,7 +865,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   if (tid == 0) {
     tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
     tma_prefetch_desc(&tdo);
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
     mbar_fence_init();
   }
   if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -883,20 +901,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   bool ok = true;
   uint32_t ph = 0;
   bool first = true;
-  for (int qt = q_begin / ATT_BM; qt < n_q && ok; ++qt) {
+  int it = 0;                                  // iteration count: stage and phase of Q / dO
+  auto load_q = [&](int stage, int q_row) {
+    mbar_expect_tx(&bar_q[stage], 2 * TILE);
+#pragma unroll
+    for (int i = 0; i < NBLK; ++i) {
+      tma_load_4d(sQ0 + stage * TILE + i * ATT_BLK, &tq, &bar_q[stage], i * 64, h, q_row, b);
+      tma_load_4d(sdO0 + stage * TILE + i * ATT_BLK, &tdo, &bar_q[stage], i * 64, h, q_row, b);
+    }
+  };
+  for (int qt = q_begin / ATT_BM; qt < n_q && ok; ++qt, ++it) {
     const int q0 = qt * ATT_BM;
     const int qi = q0 + row_t;
+    const int qs = (QST == 2) ? (it & 1) : 0;
+    uint8_t* sQ = sQ0 + qs * TILE;
+    uint8_t* sdO = sdO0 + qs * TILE;
     if (tid == 0) {
-      if (first) {   // later tiles were requested at the end of the previous iteration
-        mbar_expect_tx(bar_q, 2 * TILE);
-#pragma unroll
-        for (int i = 0; i < NBLK; ++i) {
-          tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0, b);
-          tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0, b);
-        }
-      }
+      if (first) load_q(qs, q0);   // later tiles are requested ahead (below)
+      // two stages: the other stage was last read by the products of the previous iteration,
+      // which have completed (this thread waited for them), so the next tile is requested now
+      if (QST == 2 && qt + 1 < n_q) load_q(qs ^ 1, q0 + ATT_BM);
       if (first) ok = mbar_wait(bar_kv, 0, p.status, PF_ERR_TIMEOUT_FULL);
-      ok = ok && mbar_wait(bar_q, ph, p.status, PF_ERR_TIMEOUT_FULL);
+      ok = ok && mbar_wait(&bar_q[qs], (QST == 2) ? ((it >> 1) & 1) : ph, p.status,
+                           PF_ERR_TIMEOUT_FULL);
       if (ok) {
         tc_fence_after();
         mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), idesc_sr, false);    // S  = Q K^T
@@ -966,15 +993,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     ok = mbar_wait(bar_dq, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
     if (!ok) break;
     tc_fence_after();
-    if (tid == 0 && qt + 1 < n_q) {
+    if (QST == 1 && tid == 0 && qt + 1 < n_q) {
       // every MMA that read sQ / sdO has completed (commits complete in issue order): the next
       // tile's loads overlap the dQ reduction below
-      mbar_expect_tx(bar_q, 2 * TILE);
-#pragma unroll
-      for (int i = 0; i < NBLK; ++i) {
-        tma_load_4d(sQ + i * ATT_BLK, &tq, bar_q, i * 64, h, q0 + ATT_BM, b);
-        tma_load_4d(sdO + i * ATT_BLK, &tdo, bar_q, i * 64, h, q0 + ATT_BM, b);
-      }
+      load_q(0, q0 + ATT_BM);
     }
     {
       // the TMEM loads are warp-collective: every lane executes them, only valid rows add
@@ -1162,7 +1184,7 @@ template <typename T, int DP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const CUtensorMap& tdo, const AttnParams& p, cudaStream_t st) {
   constexpr int NBLK = (DP + 63) / 64;
-  constexpr int SMEM = 4 * NBLK * ATT_BLK + 4 * ATT_BLK + 128 + 1024;
+  constexpr int SMEM = (NBLK == 1 ? 6 : 4) * NBLK * ATT_BLK + 4 * ATT_BLK + 128 + 1024;
   auto kern = attn_bwd_kernel<T, DP>;
   static bool done[64] = {};
   int r = set_smem(kern, SMEM, done);

@@ -18,6 +18,31 @@ from ..option import PipeOption
 from .partial import PartialRunner, partial_compiler
 
 
+def _leaves(v):
+    if isinstance(v, dict):
+        v = list(v.values())
+    if isinstance(v, (list, tuple)):
+        for e in v:
+            yield from _leaves(e)
+    elif hasattr(v, "values") and callable(v.values) and not torch.is_tensor(v):
+        try:
+            yield from _leaves(list(v.values()))      # HuggingFace output objects
+        except Exception:
+            return
+    else:
+        yield v
+
+
+def _to_device(v, dev):
+    if torch.is_tensor(v):
+        return v if v.device == dev else v.to(dev, non_blocking=True)
+    if isinstance(v, (list, tuple)):
+        return type(v)(_to_device(e, dev) for e in v)
+    if isinstance(v, dict):
+        return {k: _to_device(e, dev) for k, e in v.items()}
+    return v
+
+
 class PipeManager:
     runner_cls = PartialRunner
 
@@ -33,6 +58,11 @@ class PipeManager:
 
     def _exec(self, target, *args, **kwargs):
         out = self.model(*args, **kwargs)
+        # the first (profiling) call runs the whole model where its inputs are; the pipelined
+        # calls deliver the output on the last stage's device, where the target already is
+        dev = next((t.device for t in _leaves(out) if torch.is_tensor(t)), None)
+        if dev is not None:
+            target = _to_device(target, dev)
         loss = self.loss_fn(out, target, self.module)
         self.runner.scaler.scale(loss).backward()
         return loss.detach()
