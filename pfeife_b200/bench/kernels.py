@@ -173,8 +173,9 @@ def bench_groupnorm(timer, out):
         y, mean, rstd = kx.groupnorm_fwd(x, g, b, 32, 1e-5, True)
         ms_b = timer(lambda: kx.groupnorm_bwd(dy, x, mean, rstd, g, b, 32, True))
         xn = x.permute(0, 3, 1, 2).detach().requires_grad_()
-        ms_rf = timer(lambda: F.silu(F.group_norm(xn, 32, g, b, 1e-5)))
-        yr = F.silu(F.group_norm(xn, 32, g, b, 1e-5))
+        gh, bh = g.to(x.dtype), b.to(x.dtype)       # ATen wants the affine terms in x's dtype
+        ms_rf = timer(lambda: F.silu(F.group_norm(xn, 32, gh, bh, 1e-5)))
+        yr = F.silu(F.group_norm(xn, 32, gh, bh, 1e-5))
         dyn = dy.permute(0, 3, 1, 2)
         ms_rb = timer(lambda: torch.autograd.grad(yr, xn, dyn, retain_graph=True))
         nb = x.numel() * 2
@@ -211,6 +212,37 @@ def bench_adamw(timer, out):
          "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
 
 
+def bench_dp_local(timer, out):
+    """The fused data-parallel step with a world of one rank: its local part (read the
+    gradient, AdamW, write moments, master, 16-bit weights, clear the gradient) without any
+    peer traffic, against the stand-alone optimizer kernel's rate."""
+    from pfeife_b200.parallel.dp_fused import _table, launch_fused_step
+    hbm, tf, tag = peaks()
+    n = 256 << 20
+    g, w, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    local_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
+    found = torch.zeros(1, device="cuda")
+    applied = torch.zeros(1, dtype=torch.int32, device="cuda")
+    state = {"epoch": 1, "arrivals": 0}
+
+    def run():
+        nbar, grid = launch_fused_step(
+            0, 1, _table([g.data_ptr()]), _table([w.data_ptr()]), _table([lp.data_ptr()]),
+            _table([flags.data_ptr()]), m, v, local_sync, (0, n), n, [(0, n, 0, 0)],
+            [(1e-3, 0.9, 0.999, 1e-8, 0.01, True)], applied, 1, 1.0, lp.dtype, check_inf=False,
+            found_given=False, loss_scale=None, found_inf=found, epoch=state["epoch"],
+            arrivals=state["arrivals"], device=torch.device("cuda", 0))
+        state["epoch"] += nbar
+        state["arrivals"] += nbar * grid
+
+    ms = timer(run)
+    gb = n * (4 * 4 + 4 * 4 + 2) / 1e9
+    out({"kernel": "dp_fused_world1", "n": n, "ms": ms, "gbs": gb / ms * 1e3,
+         "frac_peak": gb / ms * 1e3 / hbm, "peak_ref": tag})
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--which", default="gemm,norm,adamw")
@@ -227,7 +259,8 @@ def main(argv=None):
 
     timer = Timer(a.iters)
     table = {"gemm": bench_gemm, "conv": bench_conv, "norm": bench_norm, "adamw": bench_adamw,
-             "attn": bench_attn, "groupnorm": bench_groupnorm, "rope": bench_rope}
+             "attn": bench_attn, "groupnorm": bench_groupnorm, "rope": bench_rope,
+             "dp_local": bench_dp_local}
     for k in a.which.split(","):
         table[k](timer, out)
     from pfeife_b200.ops import kernels as kx

@@ -33,6 +33,7 @@ namespace pf {
 constexpr int DP_MAX = 8;
 constexpr int DP_MAX_GROUPS = 8;
 constexpr int DP_THREADS = 512;
+constexpr int DP_CTAS_PER_SM = 2;
 // Ranks reach the first barrier of a step with the skew of a whole training step between them
 // (first-step compilation, graph capture), so that wait gets this multiple of the limit; the
 // later barriers only cover the kernel's own phases.
@@ -147,8 +148,36 @@ __device__ bool job_barrier(const DpArgs& a, int k) {
   return !s_failed;
 }
 
+// Eight consecutive floats of one thread.  With 32-byte alignment they move as one 256-bit
+// access, so that a warp touches 1 KB of whole sectors per instruction; two 16-byte accesses
+// per lane would leave every instruction with half-used sectors.
+struct F8 { float4 a, b; };
+__device__ __forceinline__ F8 ld8(const float* p, bool wide) {
+  F8 r;
+  if (wide) {
+    asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.a.x), "=f"(r.a.y), "=f"(r.a.z), "=f"(r.a.w),
+                   "=f"(r.b.x), "=f"(r.b.y), "=f"(r.b.z), "=f"(r.b.w)
+                 : "l"(p));
+  } else {
+    r.a = *reinterpret_cast<const float4*>(p);
+    r.b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  return r;
+}
+__device__ __forceinline__ void st8(float* p, const F8& r, bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::
+                 "l"(p), "f"(r.a.x), "f"(r.a.y), "f"(r.a.z), "f"(r.a.w),
+                 "f"(r.b.x), "f"(r.b.y), "f"(r.b.z), "f"(r.b.w) : "memory");
+  } else {
+    *reinterpret_cast<float4*>(p) = r.a;
+    *reinterpret_cast<float4*>(p + 4) = r.b;
+  }
+}
+
 template <int WORLD>
-__global__ void __launch_bounds__(DP_THREADS, 2)
+__global__ void __launch_bounds__(DP_THREADS, DP_CTAS_PER_SM)
 dp_fused_kernel(const DpArgs a) {
   const long long lo = a.shard_lo, hi = a.shard_hi;
   const long long nvec = (hi - lo) / 4;        // shards are multiples of 4 elements
@@ -218,17 +247,31 @@ dp_fused_kernel(const DpArgs a) {
   long long g_lo = 0, g_hi = -1, local_below = 0, master_from = 0;
   const long long nvec8 = (hi - lo) / 8;       // whole 8-element groups; a 4-element tail follows
   const long long n_items = nvec8 + (((hi - lo) & 7) ? 1 : 0);
+  // 256-bit accesses need 32-byte alignment of every stream at element e (and of m, v at i * 8)
+  const bool wide = ((lo & 7) == 0) &&
+      (((reinterpret_cast<uintptr_t>(a.grad[a.rank]) | reinterpret_cast<uintptr_t>(a.master[a.rank]) |
+         reinterpret_cast<uintptr_t>(a.m) | reinterpret_cast<uintptr_t>(a.v)) & 31) == 0);
+  const F8 z8 = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
   for (long long i = tid; i < n_items; i += stride) {
     const long long e = lo + i * 8;
     const bool two = i < nvec8;                // false: the trailing 4 elements of the shard
-    float4 g4[2], w4[2], m4[2], v4[2];
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 0 || two) {
-        g4[h] = *reinterpret_cast<const float4*>(a.grad[a.rank] + e + 4 * h);
-        *reinterpret_cast<float4*>(a.grad[a.rank] + e + 4 * h) = z4;
+    F8 g8 = z8, w8 = z8, m8 = z8, v8 = z8;
+    if (two) {
+      g8 = ld8(a.grad[a.rank] + e, wide);
+      if (!skip) {
+        w8 = ld8(a.master[a.rank] + e, wide);
+        m8 = ld8(a.m + i * 8, wide);
+        v8 = ld8(a.v + i * 8, wide);
       }
+      st8(a.grad[a.rank] + e, z8, wide);
+    } else {
+      g8.a = *reinterpret_cast<const float4*>(a.grad[a.rank] + e);
+      if (!skip) {
+        w8.a = *reinterpret_cast<const float4*>(a.master[a.rank] + e);
+        m8.a = *reinterpret_cast<const float4*>(a.m + i * 8);
+        v8.a = *reinterpret_cast<const float4*>(a.v + i * 8);
+      }
+      *reinterpret_cast<float4*>(a.grad[a.rank] + e) = z8.a;
     }
     if (skip) continue;
     if (e < g_lo || e >= g_hi) {               // entered another optimizer group
@@ -240,48 +283,40 @@ dp_fused_kernel(const DpArgs a) {
       inv_bc1 = 1.f / (1.f - powf(b1, step));
       inv_sqrt_bc2 = rsqrtf(1.f - powf(b2, step));
     }
+    float g[8] = {g8.a.x, g8.a.y, g8.a.z, g8.a.w, g8.b.x, g8.b.y, g8.b.z, g8.b.w};
+    float w[8] = {w8.a.x, w8.a.y, w8.a.z, w8.a.w, w8.b.x, w8.b.y, w8.b.z, w8.b.w};
+    float m[8] = {m8.a.x, m8.a.y, m8.a.z, m8.a.w, m8.b.x, m8.b.y, m8.b.z, m8.b.w};
+    float v[8] = {v8.a.x, v8.a.y, v8.a.z, v8.a.w, v8.b.x, v8.b.y, v8.b.z, v8.b.w};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 0 || two) {
-        w4[h] = *reinterpret_cast<const float4*>(a.master[a.rank] + e + 4 * h);
-        m4[h] = *reinterpret_cast<const float4*>(a.m + i * 8 + 4 * h);
-        v4[h] = *reinterpret_cast<const float4*>(a.v + i * 8 + 4 * h);
-      }
+    for (int j = 0; j < 8; ++j) {              // (the upper four are zeros in the 4-element tail)
+      float gr = g[j] * gs;
+      if (adamw) w[j] *= (1.f - lr * wd);
+      else gr += wd * w[j];
+      m[j] = b1 * m[j] + (1.f - b1) * gr;
+      v[j] = b2 * v[j] + (1.f - b2) * gr * gr;
+      w[j] -= lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + eps);
     }
-    uint32_t q[4] = {0, 0, 0, 0};
+    w8.a = make_float4(w[0], w[1], w[2], w[3]); w8.b = make_float4(w[4], w[5], w[6], w[7]);
+    m8.a = make_float4(m[0], m[1], m[2], m[3]); m8.b = make_float4(m[4], m[5], m[6], m[7]);
+    v8.a = make_float4(v[0], v[1], v[2], v[3]); v8.b = make_float4(v[4], v[5], v[6], v[7]);
+    uint32_t q[4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 0 || two) {
-        float g[4] = {g4[h].x, g4[h].y, g4[h].z, g4[h].w};
-        float w[4] = {w4[h].x, w4[h].y, w4[h].z, w4[h].w};
-        float m[4] = {m4[h].x, m4[h].y, m4[h].z, m4[h].w};
-        float v[4] = {v4[h].x, v4[h].y, v4[h].z, v4[h].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float gr = g[j] * gs;
-          if (adamw) w[j] *= (1.f - lr * wd);
-          else gr += wd * w[j];
-          m[j] = b1 * m[j] + (1.f - b1) * gr;
-          v[j] = b2 * v[j] + (1.f - b2) * gr * gr;
-          w[j] -= lr * (m[j] * inv_bc1) / (sqrtf(v[j]) * inv_sqrt_bc2 + eps);
-        }
-        *reinterpret_cast<float4*>(a.m + i * 8 + 4 * h) = make_float4(m[0], m[1], m[2], m[3]);
-        *reinterpret_cast<float4*>(a.v + i * 8 + 4 * h) = make_float4(v[0], v[1], v[2], v[3]);
-        w4[h] = make_float4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<float4*>(a.master[a.rank] + e + 4 * h) = w4[h];
-        if (a.lp_dtype == PF_BF16) {
-          __nv_bfloat162 x = __floats2bfloat162_rn(w[0], w[1]), y = __floats2bfloat162_rn(w[2], w[3]);
-          q[2 * h] = *reinterpret_cast<uint32_t*>(&x); q[2 * h + 1] = *reinterpret_cast<uint32_t*>(&y);
-        } else {
-          __half2 x = __floats2half2_rn(w[0], w[1]), y = __floats2half2_rn(w[2], w[3]);
-          q[2 * h] = *reinterpret_cast<uint32_t*>(&x); q[2 * h + 1] = *reinterpret_cast<uint32_t*>(&y);
-        }
+    for (int j = 0; j < 4; ++j) {
+      if (a.lp_dtype == PF_BF16) {
+        __nv_bfloat162 x = __floats2bfloat162_rn(w[2 * j], w[2 * j + 1]);
+        q[j] = *reinterpret_cast<uint32_t*>(&x);
+      } else {
+        __half2 x = __floats2half2_rn(w[2 * j], w[2 * j + 1]);
+        q[j] = *reinterpret_cast<uint32_t*>(&x);
       }
     }
     // group boundaries are multiples of 128 elements and shards of 4: an 8-element group never
     // straddles a group, and its two halves share the push decisions
     const bool push_lp = e >= local_below, push_master = e >= master_from;
     if (two) {
+      st8(a.m + i * 8, m8, wide);
+      st8(a.v + i * 8, v8, wide);
+      st8(a.master[a.rank] + e, w8, wide);
       const uint4 q8 = make_uint4(q[0], q[1], q[2], q[3]);
       if (a.lp[a.rank])
         *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q8;
@@ -289,20 +324,23 @@ dp_fused_kernel(const DpArgs a) {
       for (int p = 0; p < WORLD; ++p) {
         if (p == a.rank) continue;
         if (push_master) {
-          *reinterpret_cast<float4*>(a.master[p] + e) = w4[0];
-          *reinterpret_cast<float4*>(a.master[p] + e + 4) = w4[1];
+          *reinterpret_cast<float4*>(a.master[p] + e) = w8.a;
+          *reinterpret_cast<float4*>(a.master[p] + e + 4) = w8.b;
         }
         if (a.lp[p] && push_lp)
           *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q8;
       }
     } else {
+      *reinterpret_cast<float4*>(a.m + i * 8) = m8.a;
+      *reinterpret_cast<float4*>(a.v + i * 8) = v8.a;
+      *reinterpret_cast<float4*>(a.master[a.rank] + e) = w8.a;
       const uint2 q4 = make_uint2(q[0], q[1]);
       if (a.lp[a.rank])
         *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[a.rank]) + e) = q4;
 #pragma unroll
       for (int p = 0; p < WORLD; ++p) {
         if (p == a.rank) continue;
-        if (push_master) *reinterpret_cast<float4*>(a.master[p] + e) = w4[0];
+        if (push_master) *reinterpret_cast<float4*>(a.master[p] + e) = w8.a;
         if (a.lp[p] && push_lp)
           *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.lp[p]) + e) = q4;
       }

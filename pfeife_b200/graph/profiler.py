@@ -109,16 +109,17 @@ def _sum_outputs(out: Any) -> Optional[torch.Tensor]:
 
 
 def measure_optimizer(graph: CompGraph, option, device: torch.device) -> float:
-    """Times ``TIME_CHECK_ITER`` optimizer steps on the graph's parameters (gradients set to
-    zeros) and apportions the mean to segments by parameter bytes.  Returns the mean in ms."""
+    """Times ``TIME_CHECK_ITER`` optimizer steps on copies of the graph's parameters (gradients
+    set to zeros) and apportions the mean to segments by parameter bytes.  Returns the mean in ms."""
     params = [i.tensor for i in graph.captured.params if i.tensor.requires_grad]
     if not params:
         return 0.0
-    opt = option.make_optimizer(params)
-    for p in params:
-        if p.grad is None:
-            p.grad = torch.zeros_like(p)
-    saved = [p.detach().clone() for p in params]
+    # the steps run on stand-ins of the same shapes: the real parameters are saved for the
+    # backward of the probing call that is still in flight and must keep their versions
+    standins = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    for q in standins:
+        q.grad = torch.zeros_like(q)
+    opt = option.make_optimizer(standins)
     sync = torch.cuda.synchronize if device.type == "cuda" else (lambda: None)
     for _ in range(TIME_WARM_ITER):
         opt.step()
@@ -128,10 +129,7 @@ def measure_optimizer(graph: CompGraph, option, device: torch.device) -> float:
         opt.step()
     sync()
     ms = (time.perf_counter() - t0) * 1e3 / TIME_CHECK_ITER
-    with torch.no_grad():
-        for p, s in zip(params, saved):
-            p.copy_(s)
-            p.grad = None
+    del opt, standins
     total = sum(n.param_bytes for n in graph.nodes) or 1
     for n in graph.nodes:
         n.optim_time = ms * n.param_bytes / total

@@ -54,18 +54,24 @@ class LlamaBlock(nn.Module):
         self.gate_up = nn.Linear(d, 2 * cfg.intermediate_size, bias=False)
         self.down = nn.Linear(cfg.intermediate_size, d, bias=False)
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, delta, cos: torch.Tensor, sin: torch.Tensor):
+        """(x, delta) -> (x', delta'): the residual stream is x + delta, summed inside the next
+        RMSNorm launch so that every tensor of the stream has one consumer (its gradient is
+        then complete when the norm's backward has added the part arriving through the sum)."""
         B, S, d = x.shape
         H = self.num_heads
-        y = ops.rms_norm(x, self.input_norm, self.eps)
+        if delta is None:
+            y = ops.rms_norm(x, self.input_norm, self.eps)
+        else:
+            y, x = ops.rms_norm(delta, self.input_norm, self.eps, residual=x)
         qkv = ops.linear(y, self.qkv.weight).view(B, S, 3, H, d // H)
         q = ops.rope(qkv[:, :, 0], cos, sin)
         k = ops.rope(qkv[:, :, 1], cos, sin)
         a = ops.attention(q, k, qkv[:, :, 2], causal=True).view(B, S, d)
-        x = ops.linear(a, self.o_proj.weight, residual=x)
-        y = ops.rms_norm(x, self.post_norm, self.eps)
+        delta = ops.linear(a, self.o_proj.weight)
+        y, x = ops.rms_norm(delta, self.post_norm, self.eps, residual=x)
         g = ops.swiglu(ops.linear(y, self.gate_up.weight))
-        return ops.linear(g, self.down.weight, residual=x)
+        return x, ops.linear(g, self.down.weight)
 
 
 class Llama(nn.Module):
@@ -90,10 +96,14 @@ class Llama(nn.Module):
         S = input_ids.shape[1]
         x = ops.embedding(input_ids, self.embed.weight)
         cos, sin = self.rope_cos[:S], self.rope_sin[:S]
+        delta = None
         for layer in self.layers:
-            x = layer(x, cos, sin)
-        x = ops.rms_norm(x, self.norm, self.cfg.rms_eps)
-        return ops.linear(x, self.lm_head.weight)
+            x, delta = layer(x, delta, cos, sin)
+        if delta is None:
+            y = ops.rms_norm(x, self.norm, self.cfg.rms_eps)
+        else:
+            y, _ = ops.rms_norm(delta, self.norm, self.cfg.rms_eps, residual=x)
+        return ops.linear(y, self.lm_head.weight)
 
 
 def causal_lm_loss(logits: torch.Tensor, input_ids: torch.Tensor) -> torch.Tensor:

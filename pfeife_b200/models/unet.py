@@ -110,20 +110,26 @@ class TransformerLayer(nn.Module):
         self.ff1 = nn.Linear(dim, 8 * dim)      # GEGLU: gate | up, 4*dim each
         self.ff2 = nn.Linear(4 * dim, dim)
 
-    def forward(self, x, ctx):
+    def forward(self, x, delta, ctx):
+        """(x, delta) -> (x', delta'): the token stream is x + delta; the sum is formed inside
+        the next LayerNorm launch, so each tensor of the stream has a single consumer and its
+        gradient needs no separate add."""
         B, S, d = x.shape
         H = self.heads
-        y = ops.layer_norm(x, self.n1.weight, self.n1.bias, 1e-5)
+        if delta is None:
+            y = ops.layer_norm(x, self.n1.weight, self.n1.bias, 1e-5)
+        else:
+            y, x = ops.layer_norm(delta, self.n1.weight, self.n1.bias, 1e-5, residual=x)
         a = ops.attention_qkv(ops.linear(y, self.qkv.weight).view(B, S, 3, H, d // H))
-        x = ops.linear(a.view(B, S, d), self.o1.weight, self.o1.bias, residual=x)
-        y = ops.layer_norm(x, self.n2.weight, self.n2.bias, 1e-5)
+        delta = ops.linear(a.view(B, S, d), self.o1.weight, self.o1.bias)
+        y, x = ops.layer_norm(delta, self.n2.weight, self.n2.bias, 1e-5, residual=x)
         q = ops.linear(y, self.q2.weight).view(B, S, H, d // H)
         kv = ops.linear(ctx, self.kv2.weight).view(B, ctx.shape[1], 2, H, d // H)
         a = ops.attention(q, kv[:, :, 0], kv[:, :, 1])
-        x = ops.linear(a.view(B, S, d), self.o2.weight, self.o2.bias, residual=x)
-        y = ops.layer_norm(x, self.n3.weight, self.n3.bias, 1e-5)
+        delta = ops.linear(a.view(B, S, d), self.o2.weight, self.o2.bias)
+        y, x = ops.layer_norm(delta, self.n3.weight, self.n3.bias, 1e-5, residual=x)
         g = ops.geglu(ops.linear(y, self.ff1.weight, self.ff1.bias))
-        return ops.linear(g, self.ff2.weight, self.ff2.bias, residual=x)
+        return x, ops.linear(g, self.ff2.weight, self.ff2.bias)
 
 
 class SpatialTransformer(nn.Module):
@@ -138,8 +144,11 @@ class SpatialTransformer(nn.Module):
     def forward(self, x, ctx):
         B, Hh, Ww, C = x.shape
         h = ops.linear(self.norm(x).view(B, Hh * Ww, C), self.proj_in.weight, self.proj_in.bias)
+        delta = None
         for layer in self.layers:
-            h = layer(h, ctx)
+            h, delta = layer(h, delta, ctx)
+        if delta is not None:
+            h = h + delta
         h = ops.linear(h, self.proj_out.weight, self.proj_out.bias)
         return h.view(B, Hh, Ww, C) + x
 

@@ -4,8 +4,14 @@ Pre-norm encoder as in the reference's benchmark model (HF ``ViTForImageClassifi
 bench_models/models/train_vit.py:150-169): patch embedding, [CLS] token, learned position
 embedding, ``depth`` x (LN -> MHSA -> residual, LN -> MLP(GELU) -> residual), final LN, linear
 head on the [CLS] token.  Per block the hot path is 4 GEMM launches (fused QKV, attention
-output with the residual in its epilogue, and the two MLP GEMMs with bias+GELU and
-bias+residual epilogues), one flash-attention launch and two LayerNorm launches.
+output, and the two MLP GEMMs, the first with bias+GELU in its epilogue), one flash-attention
+launch and two LayerNorm launches.
+
+The residual stream travels between blocks as a pair (x, delta): the sum x + delta is formed
+inside the next LayerNorm launch, which returns both the sum and its normalised form.  Every
+tensor of the stream then has exactly one consumer, so the backward pass of the LayerNorm adds
+the gradient that arrives through the sum in the same launch and autograd never has to add two
+gradient contributions with a separate kernel.
 """
 from __future__ import annotations
 
@@ -65,16 +71,18 @@ class ViTBlock(nn.Module):
         self.fc1 = nn.Linear(d, cfg.mlp_dim)
         self.fc2 = nn.Linear(cfg.mlp_dim, d)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, delta: torch.Tensor):
+        """(x, delta) -> (x', delta'): the stream entering the block is x + delta, the stream
+        leaving it x' + delta'."""
         B, S, d = x.shape
         H = self.num_heads
-        y = ops.layer_norm(x, self.ln1.weight, self.ln1.bias, self.eps)
+        y, x = ops.layer_norm(delta, self.ln1.weight, self.ln1.bias, self.eps, residual=x)
         qkv = ops.linear(y, self.qkv.weight, self.qkv.bias).view(B, S, 3, H, d // H)
         a = ops.attention_qkv(qkv).view(B, S, d)
-        x = ops.linear(a, self.proj.weight, self.proj.bias, residual=x)
-        y = ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.eps)
-        return ops.mlp(y, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias,
-                       "gelu", residual=x)
+        delta = ops.linear(a, self.proj.weight, self.proj.bias)
+        y, x = ops.layer_norm(delta, self.ln2.weight, self.ln2.bias, self.eps, residual=x)
+        return x, ops.mlp(y, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias,
+                          "gelu")
 
 
 class ViT(nn.Module):
@@ -108,8 +116,10 @@ class ViT(nn.Module):
         x = ops.linear(self.patchify(pixel_values), self.patch.weight, self.patch.bias)
         B = x.shape[0]
         cls = self.cls_token.to(x.dtype).expand(B, -1, -1)
-        x = torch.cat([cls, x], dim=1) + self.pos_embed.to(x.dtype)
+        x = torch.cat([cls, x], dim=1)
+        delta = self.pos_embed.to(x.dtype).expand(B, -1, -1).contiguous()
         for blk in self.blocks:
-            x = blk(x)
-        x = ops.layer_norm(x, self.ln.weight, self.ln.bias, self.cfg.layer_norm_eps)
-        return ops.linear(x[:, 0], self.head.weight, self.head.bias)
+            x, delta = blk(x, delta)
+        y, _ = ops.layer_norm(delta, self.ln.weight, self.ln.bias, self.cfg.layer_norm_eps,
+                              residual=x)
+        return ops.linear(y[:, 0], self.head.weight, self.head.bias)

@@ -395,9 +395,10 @@ class StageWorker:
                 self.train_steps_done >= self.graph_warmup_steps:
             gs = self._graph_for(sp, stage, mb, ins, int(gather))
             if gs is not None:
-                for dst, src in zip(gs.static_ins, ins):
-                    if dst is not src and torch.is_tensor(dst):
-                        dst.copy_(src, non_blocking=True)
+                with torch.no_grad():       # the static inputs are leaves that require grad
+                    for dst, src in zip(gs.static_ins, ins):
+                        if dst is not src and torch.is_tensor(dst):
+                            dst.copy_(src, non_blocking=True)
                 gs.fwd.replay()
                 _lib_add(gs.fwd_kernels)
                 self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
@@ -455,6 +456,10 @@ class StageWorker:
                 where = " <- ".join(f"{f.name}:{f.lineno}" for f in
                                     reversed(traceback.extract_tb(e.__traceback__)[-4:]))
                 cause = e.__context__
+                if cause is not None and cause.__traceback__ is not None:
+                    where += " [first error at " + " <- ".join(
+                        f"{f.name}:{f.lineno}" for f in
+                        reversed(traceback.extract_tb(cause.__traceback__)[-6:])) + "]"
                 self.log.log(20 if attempt == 0 else 30,
                              "CUDA graph capture of stage %d failed (%s: %s) at %s%s; %s", stage,
                              type(e).__name__, str(e).splitlines()[0], where,
@@ -501,7 +506,11 @@ class StageWorker:
             if inp.kind == "state" or not torch.is_tensor(v):
                 static_ins.append(v)
                 continue
-            t = torch.empty_like(v).copy_(v)
+            # a fresh leaf: copying from a tensor that requires grad with autograd recording
+            # would hang a CopyBackwards node (made outside the capture, on the stream that is
+            # current here) under the captured backward
+            with torch.no_grad():
+                t = torch.empty_like(v).copy_(v)
             if v.requires_grad:
                 t.requires_grad_(True)
             static_ins.append(t)

@@ -198,6 +198,9 @@ def main():
     result["split_points"] = [list(m.plan.split_points) for m in runner.modules
                               if m.plan is not None]
     result["state_dict_keys"] = len(model.state_dict())
+    w = getattr(runner, "worker", None)
+    result["graphs"] = sum(1 for g in getattr(w, "graphs", {}).values() if not g.failed)
+    result["graphs_failed"] = sum(1 for g in getattr(w, "graphs", {}).values() if g.failed)
     if state.dp_size > 1:
         # replicas must hold identical parameters after training
         flat = torch.cat([p.detach().cpu().reshape(-1) for p in model.parameters()])

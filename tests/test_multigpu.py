@@ -28,13 +28,20 @@ def launch(tmp_path, world, script_args, dp_mesh=None, tag="r", timeout=420):
         return json.load(f), out
 
 
-def test_pp2_gpu_matches_single_process(tmp_path):
+@pytest.mark.parametrize("extra", [[], ["--cuda_graphs"], ["--cuda_graphs", "--loop_cnt", "2"]],
+                         ids=["eager", "graphs", "graphs_looped"])
+def test_pp2_gpu_matches_single_process(tmp_path, extra):
+    """Two pipeline ranks against the un-pipelined loop: eagerly, with every (stage, slot)
+    replayed from CUDA graphs (the gradients a replayed stage hands upstream come from its
+    static inputs), and with two stages per rank, where stages both receive and send."""
     res, _ = launch(tmp_path, 2, ["--model", "vit_small", "--device_cnt", "2", "--batch_size", "4",
-                                  "--batch_cnt", "4", "--steps", "3", "--optimizer", "adamw",
-                                  "--lr", "0.001", "--mixed_precision", "bf16"])
+                                  "--batch_cnt", "4", "--steps", "4", "--optimizer", "adamw",
+                                  "--lr", "0.001", "--mixed_precision", "bf16"] + extra)
     for a, b in zip(res["losses"], res["ref_losses"]):
         assert a == pytest.approx(b, rel=5e-2, abs=5e-2)
     assert res["param_diff"] < 2e-2
+    if extra:
+        assert res["graphs"] > 0 and res["graphs_failed"] == 0, res
 
 
 def test_fused_dp_equals_nccl_dp(tmp_path):
