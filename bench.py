@@ -176,7 +176,9 @@ def _planned_mesh(args, wl, world, rank, cpu):
             from pfeife_b200 import PipeOption
             from pfeife_b200.parallel.mesh_plan import NVSWITCH_LINK, plan_mesh
             torch.manual_seed(0)
-            model = wl.build_model().to(dev)
+            with torch.device(dev):
+                model = wl.build_model()
+            model = model.to(dev)
             extra = {k: v for k, v in wl.option.items() if k in ("prefetch_fwd", "loop_batch")}
             opt = PipeOption(device_cnt=1, batch_size=wl.micro_batch, batch_cnt=wl.batch_cnt,
                              mixed_precision=None if cpu else wl.precision, cpu_test=cpu,
@@ -262,7 +264,9 @@ def run_native(args) -> int:
         return 0
 
     torch.manual_seed(0)
-    model = wl.build_model().to(dev)
+    with torch.device(dev):     # initialised on the device: seconds instead of minutes at 7B
+        model = wl.build_model()
+    model = model.to(dev)
     optimizer = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01)
     runner = PartialRunner(option, optimizer)
     cmodel = torch.compile(model, backend=partial_compiler)
@@ -298,6 +302,7 @@ def run_native(args) -> int:
     # dtype on the device.  The reference arm loads its inputs the same way.
     copy_stream = None if cpu else torch.cuda.Stream(device=dev)
     pending = []
+    last_loss = [None]
 
     def fetch():
         if cpu:
@@ -310,7 +315,8 @@ def run_native(args) -> int:
 
     def one_step(e2e: bool, last: bool = False):
         if not e2e:
-            return runner.step(*resident)
+            last_loss[0] = runner.step(*resident)   # read back after the timed region
+            return 0.0
         batch, ev = pending.pop() if pending else fetch()
         if not last:
             pending.append(fetch())
@@ -319,6 +325,7 @@ def run_native(args) -> int:
             for t in batch:
                 t.record_stream(torch.cuda.current_stream(dev))
         losses = runner.step(*[to_compute(t) for t in batch])
+        last_loss[0] = losses
         return float(torch.stack([l.float() for l in losses]).sum().cpu())
 
     def sync():
@@ -401,7 +408,9 @@ def run_native(args) -> int:
                     clocks=clocks, launches=launches,
                     parallelism=f"pp{state.pp_size}xdp{state.dp_size}",
                     h2d=sum(t.numel() * t.element_size() for t in host), d2h=4, workload=wl,
-                    extra={"dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
+                    extra={"loss_mean_last_step": (None if last_loss[0] is None else float(
+                               torch.stack([l.float() for l in last_loss[0]]).mean().cpu())),
+                           "dp_impl": ("fused_p2p" if option.fused_dp else "nccl")
                            if state.dp_size > 1 else None,
                            "planner_mesh_table": table,
                            "planner_link": (planned or {}).get("link"),

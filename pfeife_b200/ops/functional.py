@@ -430,6 +430,8 @@ def norm_fwd(x: Tensor, gamma: Tensor, beta: Optional[Tensor], residual: Optiona
     """-> (y, h, mean, rstd) with h = x + residual (h aliases nothing: it is x's clone-free
     stand-in only on the fake/CPU path, always a fresh tensor when residual is given)."""
     N = x.shape[-1]
+    if residual is not None and residual.dtype != x.dtype:
+        residual = residual.to(x.dtype)      # the kernels read both streams as one type
     if _native(x) or (x.is_cuda and x.dtype == torch.float32 and N % 4 == 0):
         y, h, mean, rstd = kx.norm_fwd(x, gamma, beta, eps, rms, residual)
         if residual is None:

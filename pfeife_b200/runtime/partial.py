@@ -528,7 +528,8 @@ class PartialRunner:
                 return
             a, k = item
             try:
-                res = self.exec_fn(*a, **k)
+                with self._amp():
+                    res = self.exec_fn(*a, **k)
             except BaseException as e:   # surfaced by step()
                 self._return_queues[bid].put(e)
                 self.finalize_output(bid)
@@ -538,8 +539,17 @@ class PartialRunner:
 
     def _probe_forward(self, a, k) -> Any:
         _tls.mb = None
-        res = self.exec_fn(*a, **k)
+        with self._amp():
+            res = self.exec_fn(*a, **k)
         return res
+
+    def _amp(self):
+        """The user's step function runs under the same autocast state as the stages: the graph
+        is traced inside it, and dtypes that the trace bakes in (``t.to(x.dtype)``) must be the
+        ones the stages will see.  (The stages enter autocast themselves,
+        pfeife/mp/worker.py:677; tracing outside it gives fp32 where they produce 16 bits.)"""
+        from ..graph.profiler import gen_amp_context
+        return gen_amp_context(self.state.device, self.option.mixed_precision)
 
     # ---- checkpoint
     def gather_params(self, with_optimizer: bool = False):

@@ -34,6 +34,8 @@ CASES = [  # B, H, Sq, Sk, D, causal
     (1, 2, 258, 300, 64, True),      # causal with Sq != Sk: ragged key tiles in the backward
     (1, 4, 1024, 1024, 128, True),   # several query tiles per head, many key tiles each
     (3, 5, 384, 640, 64, False),     # more work items than one wave of a small grid
+    (4, 3, 17, 17, 64, False),       # far fewer rows than one tile (reduced ViT of the tests)
+    (2, 4, 16, 16, 32, True),
 ]
 
 
