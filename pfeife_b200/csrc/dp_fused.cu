@@ -230,8 +230,13 @@ dp_fused_kernel(const DpArgs a) {
     for (int r = 0; r < a.world; ++r)
       skip |= ld_acquire_sys(&a.flags[a.rank][DP_MAX + r]) == a.epoch;
     if (tid == 0) *a.found_inf = skip ? 1.f : 0.f;
-  } else if (a.found_given) {
-    skip = *reinterpret_cast<const volatile float*>(a.found_inf) != 0.f;
+  } else {
+    // the update loop below deals the reduced gradients to the threads in another order (eight
+    // consecutive elements per thread) than the loop above wrote them: every CTA must have
+    // finished its part of the reduce before any thread reads the sums
+    ok = job_barrier(a, kbar++);
+    if (!ok) { if (tid == 0 && a.found_inf) *a.found_inf = 1.f; return; }
+    if (a.found_given) skip = *reinterpret_cast<const volatile float*>(a.found_inf) != 0.f;
   }
   dp_mark(a, 3);
   float gs = a.grad_scale;
@@ -375,7 +380,7 @@ using namespace pf;
 // `groups` holds `ngroups` records of 4 long long (lo, hi, local_below, master_from) and
 // `hyper` `ngroups` records of 6 floats (lr, beta1, beta2, eps, weight_decay, adamw != 0).
 // `epoch` is the value of this call's first barrier: it must be identical on every rank and
-// grow by the number of barriers a call uses (2, or 3 with check_inf), which the call returns
+// grow by the number of barriers a call uses (3), which the call returns
 // through *barriers_out; `arrivals_before` is the sum over earlier calls of barriers * grid
 // (*grid_out).  `applied_steps` (device int, may be null) counts the optimizer steps that were
 // not skipped; the bias correction uses it, so a step skipped on an overflow does not count.
@@ -422,7 +427,7 @@ PF_API int pf_dp_fused_step(int rank, int world, void* const* grad, void* const*
   // has to wait for an SM delays the barrier, within the wait limit)
   const int grid = 2 * (sm_count > 0 ? sm_count : 148);
   a.sync_base = arrivals_before;
-  if (barriers_out) *barriers_out = check_inf ? 3 : 2;
+  if (barriers_out) *barriers_out = 3;
   if (grid_out) *grid_out = grid;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (world) {

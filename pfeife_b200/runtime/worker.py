@@ -211,7 +211,6 @@ class StageWorker:
         self.use_graphs = bool(getattr(option, "cuda_graphs", False)) and device.type == "cuda"
         self.graph_warmup_steps = 1       # eager steps before capture (lazy inits, autotune)
         self.graphs: Dict[Tuple[int, int, int], _GraphedStage] = {}
-        self.graph_pool = None
         self.slot_of: Dict[Tuple[int, int], int] = {}
         self.graph_key: Dict[Tuple[int, int], Tuple[int, int, int]] = {}
         self._example_ins: Dict[int, List[Any]] = {}     # stage -> inputs of an eager forward
@@ -466,8 +465,8 @@ class StageWorker:
                              f" after {type(cause).__name__}: {str(cause).splitlines()[0]}"
                              if cause is not None else "",
                              "trying once more" if attempt == 0 else "running it eagerly")
-                # a capture that broke leaves its memory pool marked as recording
-                self.graph_pool = None
+                # (a capture that broke leaves its memory pool marked as recording: the next
+                # attempt makes a pool of its own)
                 if self.device.type == "cuda":
                     torch.cuda.synchronize(self.device)
         gs.failed = True
@@ -499,8 +498,12 @@ class StageWorker:
         self.graph_key.clear()
 
     def _capture(self, gs: _GraphedStage, sp: StageSpec, stage: int, ins: List[Any]) -> None:
-        if self.graph_pool is None:
-            self.graph_pool = torch.cuda.graph_pool_handle()
+        # One memory pool per (stage, slot): its forward and backward graphs always replay in the
+        # order they were captured.  Graphs of different slots replay interleaved (forward of
+        # slot 1 between forward and backward of slot 0); in a shared pool the later capture
+        # would have been handed the blocks that the earlier backward capture freed -- the
+        # activations slot 0's forward saves for its backward -- and overwrite them on replay.
+        pool = torch.cuda.graph_pool_handle()
         static_ins: List[Any] = []
         for inp, v in zip(sp.inputs, ins):
             if inp.kind == "state" or not torch.is_tensor(v):
@@ -520,7 +523,7 @@ class StageWorker:
         from ..ops import _lib
         n0 = _lib.launch_count()
         fwd = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(fwd, pool=self.graph_pool, capture_error_mode="thread_local"):
+        with torch.cuda.graph(fwd, pool=pool, capture_error_mode="thread_local"):
             with gen_amp_context(self.device, self.option.mixed_precision):
                 outs = mod(*static_ins)
         if not isinstance(outs, (tuple, list)):
@@ -536,7 +539,7 @@ class StageWorker:
                         not self._is_param_view(t):
                     t.grad = None
             bwd = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(bwd, pool=self.graph_pool,
+            with torch.cuda.graph(bwd, pool=pool,
                                   capture_error_mode="thread_local"):
                 torch.autograd.backward([outs[j] for j, _ in grad_outs],
                                         [g for _, g in grad_outs])
