@@ -278,7 +278,7 @@ def run_native(args) -> int:
 
     runner.set_exec_fn(exec_fn)
     n = wl.micro_batch * wl.batch_cnt
-    g = torch.Generator(device="cpu").manual_seed(1 + state.dp_rank)
+    g = torch.Generator(device="cpu").manual_seed(args.data_seed + 1 + state.dp_rank)
     cd = _compute_dtype(torch, mp)
     # the host holds what a data loader would hand over: fp32 tensors in pinned memory
     host = list(wl.make_batch(n, g))
@@ -453,6 +453,8 @@ def main(argv=None) -> int:
     ap.add_argument("--scheduler", type=str, default=None)
     ap.add_argument("--device_bench", type=str, default=None,
                     help="link-model file (measured and written when it does not exist)")
+    ap.add_argument("--data_seed", type=int, default=0,
+                    help="offset of the synthetic batch's seed (replica r draws with seed + 1 + r)")
     ap.add_argument("--cpu", action="store_true", help="plumbing check without a GPU")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--workload", default="vitg",

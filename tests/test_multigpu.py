@@ -58,6 +58,24 @@ def test_fused_dp_equals_nccl_dp(tmp_path):
         assert a == pytest.approx(b, rel=2e-2, abs=2e-2)
 
 
+def test_fused_dp_on_four_replicas_equals_nccl_dp(tmp_path):
+    """The four-rank instantiation of the fused step (two vectors per peer in flight)."""
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 CUDA devices")
+    common = ["--model", "vit_small", "--device_cnt", "1", "--batch_size", "4", "--batch_cnt", "2",
+              "--steps", "4", "--optimizer", "adamw", "--lr", "0.001", "--mixed_precision", "bf16"]
+    fused, out_f = launch(tmp_path, 4, common, dp_mesh="-4,1", tag="fused4")
+    nccl, _ = launch(tmp_path, 4, common + ["--no_fused_dp"], dp_mesh="-4,1", tag="nccl4")
+    for r in (0, 1, 2):          # the main process is the last replica
+        with open(out_f + f".dp{r}") as f:
+            other = json.load(f)
+        assert fused["param_checksum"] == pytest.approx(other["param_checksum"], rel=1e-7)
+    assert fused["param_checksum"] == pytest.approx(nccl["param_checksum"], rel=1e-4, abs=1e-3)
+    for a, b in zip(fused["losses"], nccl["losses"]):
+        assert a == pytest.approx(b, rel=2e-2, abs=2e-2)
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 def test_row_sharded_weights_match_replicated_weights(tmp_path, graphs):
     """--use_fsdp with the fused data-parallel step: after the optimizer step every weight matrix
