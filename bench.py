@@ -182,7 +182,8 @@ def _planned_mesh(args, wl, world, rank, cpu):
             extra = {k: v for k, v in wl.option.items() if k in ("prefetch_fwd", "loop_batch")}
             opt = PipeOption(device_cnt=1, batch_size=wl.micro_batch, batch_cnt=wl.batch_cnt,
                              mixed_precision=None if cpu else wl.precision, cpu_test=cpu,
-                             no_bench_optimizer=True, verbosity="warning", **extra)
+                             no_bench_optimizer=True, verbosity="warning",
+                             cuda_graphs=not (cpu or args.no_graphs), **extra)
             cd = _compute_dtype(torch, None if cpu else wl.precision)
             mb = wl.make_batch(wl.micro_batch, torch.Generator().manual_seed(0))
             x = tuple(_to_compute(t, cd).to(dev) for t in mb[:wl.n_model_inputs])

@@ -6,15 +6,16 @@
 // (88 for ViT-g/14 runs as 96 with zero-filled tails: the tensor map's inner extent is D, so
 // the tail of the last 64-element block is filled with zeros by TMA, never with the next head).
 //
-// Forward, one CTA (128 threads, thread t <-> query row t <-> TMEM lane t) per (q tile of 128,
-// head, batch), looping over 128-row K/V tiles:
-//     S = Q K^T            tcgen05.mma, smem x smem -> TMEM
-//     online softmax       tcgen05.ld S -> registers (base-2 exponent, running max / sum)
-//     P -> smem            16-bit, written in the 128B-swizzled K-major layout the MMA reads
-//     O_tile = P V         tcgen05.mma, V used in place as an MN-major operand -> TMEM
-//     O = alpha O + O_tile in registers
-// The score matrix never exists in global memory.  Two CTAs fit per SM for D <= 96, which is
-// what overlaps one CTA's softmax with the other's MMAs.
+// Forward: a persistent kernel, one CTA per SM walking over (q tile of 128, head, batch) items,
+// with a TMA producer warp (K and V rings), an MMA issuer warp and four softmax warps (thread
+// <-> query row <-> TMEM lane); per 128-row K/V tile:
+//     S = Q K^T            tcgen05.mma, smem x smem -> one of two S buffers in TMEM; the next
+//                          tile's S is issued before this tile's probabilities are waited for
+//     online softmax       one tcgen05.ld of S -> registers (base-2 exponent, running max / sum)
+//     P -> smem            16-bit, in the 128B-swizzled K-major layout the MMA reads; two buffers
+//     O += P V             tcgen05.mma, V in place as an MN-major operand, O accumulated in TMEM
+//                          and rescaled there only when the row maximum grew by more than 2^8
+// The score matrix never exists in global memory.  (Details at attn_fwd_ws_kernel.)
 //
 // Backward, one CTA per (k/v tile of 128, head, batch), looping over q tiles, five MMAs per
 // tile pair with S/P and dP/dS in TMEM / smem and dK, dV accumulated in TMEM:
@@ -254,169 +255,6 @@ attn_fwd_tail_kernel(const AttnParams p) {
   attn_fwd_tail_row<T>(p, tail_smem, p.q_tiles * ATT_BM + (int)blockIdx.x, blockIdx.y, blockIdx.z);
 }
 // ================================================================================ forward
-template <typename T, int DP>
-__global__ void __launch_bounds__(128)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                const __grid_constant__ CUtensorMap tv, const AttnParams p) {
-  constexpr int NBLK = (DP + 63) / 64;
-  constexpr int TILE = NBLK * ATT_BLK;
-  constexpr uint32_t TMEM_COLS = 256;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
-  // P (two blocks) is written over the K tile once S = Q K^T has completed; with a one-block
-  // K tile (D <= 64) it gets room of its own
-  constexpr int PK = (NBLK >= 2) ? 0 : 2 * ATT_BLK;
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE;
-  uint8_t* sV = sK + TILE;
-  uint8_t* sP = (NBLK >= 2) ? sK : sV + TILE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + TILE + PK);
-  uint64_t* bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3,
-          *bar_o = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int q0 = blockIdx.x * ATT_BM, h = blockIdx.y, b = blockIdx.z;
-  if (tid == 0) {
-    tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem, t_o = tmem + 128;
-  const uint32_t lane_off = uint32_t(warp * 32) << 16;
-
-  const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-  const uint32_t idesc_o = make_idesc_f16(128, DP, p.fmt, 0, 1);
-  const float c2 = p.scale * LOG2E;
-
-  int kv_end = p.Sk;
-  const int shift = p.Sk - p.Sq;   // causal: key j visible to query i iff j <= i + shift
-  if (p.causal) kv_end = min(p.Sk, q0 + ATT_BM + shift);
-  const int n_tiles = (kv_end + ATT_BN - 1) / ATT_BN;
-
-  if (tid == 0) load_tile<NBLK>(sQ, &tq, bar_q, h, q0, b);
-
-  float o[DP];
-#pragma unroll
-  for (int i = 0; i < DP; ++i) o[i] = 0.f;
-  float m = -INFINITY, l = 0.f;
-  const int qi = q0 + tid;
-  bool ok = true;
-  uint32_t ph = 0;
-
-  for (int j = 0; j < n_tiles && ok; ++j) {
-    const int k0 = j * ATT_BN;
-    const int rem = min(ATT_BN, p.Sk - k0);
-    const int n_mma = (rem + 15) / 16 * 16;
-    const int n_chunks = (n_mma + 31) / 32;
-    if (tid == 0) {
-      load_tile<NBLK>(sK, &tk, bar_k, h, k0, b);
-      load_tile<NBLK>(sV, &tv, bar_v, h, k0, b);
-      if (j == 0) ok = mbar_wait(bar_q, 0, p.status, PF_ERR_TIMEOUT_FULL);
-      ok = ok && mbar_wait(bar_k, ph, p.status, PF_ERR_TIMEOUT_FULL);
-      if (ok) {
-        tc_fence_after();
-        // a ragged last tile only computes the key columns that exist (rounded up to 16)
-        const uint32_t id = (n_mma == ATT_BN) ? idesc_s : make_idesc_f16(128, n_mma, p.fmt, 0, 0);
-        mma_kk<DP / 16>(t_s, smem_u32(sQ), smem_u32(sK), id, false);
-        tc_commit(bar_s);
-      }
-    }
-    __syncwarp();
-    ok = mbar_wait(bar_s, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
-    if (!ok) break;
-    tc_fence_after();
-    // ---- softmax over this tile's 128 scores of row `tid` (two passes over TMEM: the row
-    //      maximum first, then exponentials; only 32 scores are live in registers at a time)
-    float mx = m;
-#pragma unroll 1
-    for (int c = 0; c < n_chunks; ++c) {
-      uint32_t raw[32];
-      tmem_ld32(t_s + lane_off + c * 32, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int kj = k0 + c * 32 + i;
-        const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
-        if (vis) mx = fmaxf(mx, __uint_as_float(raw[i]) * c2);
-      }
-    }
-    const float m_use = (mx == -INFINITY) ? 0.f : mx;
-    const float alpha = exp2f(m - m_use);     // m = -inf -> 0
-    float rs = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < n_chunks; ++c) {
-      uint32_t raw[32];
-      tmem_ld32(t_s + lane_off + c * 32, raw);
-      tmem_ld_wait();
-      float pv[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int kj = k0 + c * 32 + i;
-        const bool vis = kj < p.Sk && !(p.causal && kj > qi + shift);
-        pv[i] = vis ? exp2f(__uint_as_float(raw[i]) * c2 - m_use) : 0.f;
-        rs += pv[i];
-      }
-      store_p_chunk<T>(sP, tid, c * 32, pv);
-    }
-    l = l * alpha + rs;
-    m = mx;
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      ok = mbar_wait(bar_v, ph, p.status, PF_ERR_TIMEOUT_FULL);
-      if (ok) {
-        tc_fence_after();
-        mma_k_mn(t_o, smem_u32(sP), smem_u32(sV), idesc_o, false, n_mma / 16);
-        tc_commit(bar_o);
-      }
-    }
-    __syncwarp();
-    ok = mbar_wait(bar_o, ph, p.status, PF_ERR_TIMEOUT_TMEM_FULL);
-    if (!ok) break;
-    tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < DP / 32; ++c) {
-      uint32_t raw[32];
-      tmem_ld32(t_o + lane_off + c * 32, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(raw[i]);
-    }
-    ph ^= 1;
-    tc_fence_before();
-    __syncthreads();   // everyone is done with S, O_tile, sK, sV, sP before the next tile
-  }
-
-  if (ok && qi < p.Sq) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    T* dst = reinterpret_cast<T*>(p.o) + (((long long)b * p.Sq + qi) * p.H + h) * p.D;
-#pragma unroll
-    for (int c = 0; c < DP / 8; ++c) {
-      if (c * 8 < p.D) {
-        uint4 q;
-        q.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
-        q.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        q.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-        q.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        reinterpret_cast<uint4*>(dst)[c] = q;
-      }
-    }
-    p.lse[((long long)b * p.H + h) * p.Sq + qi] = (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
-}
-
-// ================================================================================ forward, pipelined
 // Persistent, warp-specialised forward.  One CTA per SM walks over (q tile, head, batch) work
 // items; its 6 warps have fixed roles:
 //   warp 0     TMA producer: Q of the item, then K / V tiles into a ring of ST stages; it runs
@@ -1122,27 +960,6 @@ static int set_smem(K kern, int bytes, bool* done) {
   return 0;
 }
 
-template <typename T, int DP>
-static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                      const AttnParams& p, cudaStream_t st) {
-  constexpr int NBLK = (DP + 63) / 64;
-  constexpr int SMEM = 3 * NBLK * ATT_BLK + (NBLK >= 2 ? 0 : 2 * ATT_BLK) + 128 + 1024;
-  auto kern = attn_fwd_kernel<T, DP>;
-  static bool done[64] = {};
-  int r = set_smem(kern, SMEM, done);
-  if (r) return r;
-  dim3 grid(p.q_tiles, p.H, p.B);
-  kern<<<grid, 128, SMEM, st>>>(tq, tk, tv, p);
-  PF_CHECK_LAUNCH();
-  if (p.q_tail > 0) {
-    // [q 128 | red 32 | scores max(Sk, 8 x 128 for the fold)] floats
-    const int bytes = (160 + (p.Sk > 1024 ? p.Sk : 1024)) * 4;
-    attn_fwd_tail_kernel<T><<<dim3(p.q_tail, p.H, p.B), 128, bytes, st>>>(p);
-    PF_CHECK_LAUNCH();
-  }
-  return 0;
-}
-
 static int attn_sm_count() {
   static int sms[64] = {};
   int dev = 0;
@@ -1266,9 +1083,6 @@ PF_API int pf_attn_fwd(const void* q, const void* k, const void* v, void* o, voi
   set_views(p, q, k, v, sq, sk, sv);
   split_tail(Sq, Sk, &p.q_tiles, &p.q_tail);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // PF_ATTN_SERIAL=1 selects the earlier one-role-at-a-time kernel (comparison runs)
-  static const bool serial = [] { const char* e = getenv("PF_ATTN_SERIAL"); return e && e[0] == '1'; }();
-  if (serial) PF_ATTN_DISPATCH(launch_fwd, tq, tk, tv, p, st);
   PF_ATTN_DISPATCH(launch_fwd_ws, tq, tk, tv, p, st);
 }
 

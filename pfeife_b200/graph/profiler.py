@@ -99,6 +99,36 @@ class SegmentExecutor:
         raise RuntimeError("graph has no output node")
 
 
+def _graph_replay_ms(ex: "SegmentExecutor", args: Sequence[Any], amp, device) -> Optional[float]:
+    """Device time of one forward of the whole graph replayed as a CUDA graph (mean of
+    ``TIME_CHECK_ITER`` replays), or None when the forward cannot be captured."""
+    try:
+        torch.cuda.synchronize(device)
+        g = torch.cuda.CUDAGraph()
+        with torch.no_grad(), amp():
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                ex.run(args)
+        for _ in range(TIME_WARM_ITER):
+            g.replay()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(TIME_CHECK_ITER):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize(device)
+        ms = s.elapsed_time(e) / TIME_CHECK_ITER
+        del g
+        return ms
+    except Exception as exc:     # an op that cannot be captured: keep the eager figures
+        get_logger().info("forward not captured as one graph (%s: %s)", type(exc).__name__,
+                          str(exc).splitlines()[0] if str(exc) else "")
+        try:
+            torch.cuda.synchronize(device)
+        except Exception:
+            pass
+        return None
+
+
 def _sum_outputs(out: Any) -> Optional[torch.Tensor]:
     total = None
     for t in _tensor_leaves(out if not isinstance(out, dict) else list(out.values())):
@@ -216,6 +246,19 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
                                                  if timed else acc[s]))
     for s in range(n_seg):
         graph.nodes[s].comp_time = max(acc[s] / TIME_CHECK_ITER, 1e-4)
+    if is_cuda and getattr(option, "cuda_graphs", False):
+        # The run replays CUDA graphs, the pass above launched eagerly: with kernels of a few
+        # microseconds it measured the host's launch rate, not the device.  The whole forward
+        # replayed as one graph gives the device time; the segment times keep their
+        # proportions and are scaled to it.
+        replay = _graph_replay_ms(ex, args, amp, device)
+        eager = sum(n.comp_time for n in graph.nodes)
+        if replay is not None and 0.0 < replay < eager:
+            k = replay / eager
+            for n in graph.nodes:
+                n.comp_time = max(n.comp_time * k, 1e-4)
+            log.info("forward as one CUDA graph: %.3f ms against %.3f ms launched eagerly; "
+                     "segment times scaled by %.3f", replay, eager, k)
 
     # ---- pass 3: forward vs backward wall clock
     sync = (lambda: torch.cuda.synchronize(device)) if is_cuda else (lambda: None)
