@@ -129,6 +129,34 @@ def _graph_replay_ms(ex: "SegmentExecutor", args: Sequence[Any], amp, device) ->
         return None
 
 
+def _kernel_busy_ms(ex: "SegmentExecutor", args: Sequence[Any], amp, device
+                    ) -> Optional[Tuple[float, float]]:
+    """Sums of the kernel durations (ms) of one forward and of one backward (activity records of
+    the profiler: launch gaps do not count), or None when no records could be had."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        def busy(fn):
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                r = fn()
+                torch.cuda.synchronize(device)
+            return r, sum(float(getattr(ev, "device_time_total", 0) or 0) for ev in prof.events())
+
+        def fwd():
+            with amp():
+                return ex.run(args)
+
+        out, f_us = busy(fwd)
+        loss = _sum_outputs(out)
+        if loss is None or f_us <= 0:
+            return None
+        _, b_us = busy(loss.backward)
+        return (f_us / 1e3, b_us / 1e3) if b_us > 0 else None
+    except Exception as exc:
+        get_logger().info("no kernel activity records (%s)", type(exc).__name__)
+        return None
+
+
 def _sum_outputs(out: Any) -> Optional[torch.Tensor]:
     total = None
     for t in _tensor_leaves(out if not isinstance(out, dict) else list(out.values())):
@@ -225,6 +253,7 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
         log.info("segments re-ordered by the %s linearizer", option.linearizer)
 
     # ---- pass 2: per-segment forward timing
+    graph_fwd_ms = None
     n_seg = len(graph.nodes)
     acc = [0.0] * n_seg
     for it in range(TIME_WARM_ITER + TIME_CHECK_ITER):
@@ -253,6 +282,7 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
         # proportions and are scaled to it.
         replay = _graph_replay_ms(ex, args, amp, device)
         eager = sum(n.comp_time for n in graph.nodes)
+        graph_fwd_ms = replay if (replay is not None and replay > 0.0) else None
         if replay is not None and 0.0 < replay < eager:
             k = replay / eager
             for n in graph.nodes:
@@ -278,9 +308,25 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
         if it >= TIME_WARM_ITER:
             fwd_ms += (t1 - t0) * 1e3
             bwd_ms += (t2 - t1) * 1e3
+    graph.fb_ratio = max(1.0, bwd_ms / fwd_ms) if fwd_ms > 0 else 2.0
+    if is_cuda and getattr(option, "cuda_graphs", False):
+        # under graph replay the ratio is one of device times; the wall clock above is the
+        # host's launch rate in both directions when the kernels are short
+        busy = _kernel_busy_ms(ex, args, amp, device)
+        if busy is not None:
+            # Two bounds.  The wall-clock ratio is too low when both directions ran at the host's
+            # launch rate.  The backward's kernel time against the forward as it replays is too
+            # high: this probing backward still writes every parameter gradient to a tensor of
+            # its own and lets autograd accumulate it, where the stages add into the gradient
+            # bucket from the GEMM epilogue.  The geometric mean of the two is used.
+            f_ms, b_ms = busy
+            upper = b_ms / graph_fwd_ms if graph_fwd_ms else b_ms / f_ms
+            ratio = (max(graph.fb_ratio, 1.0) * max(upper, 1.0)) ** 0.5
+            log.info("backward / forward: %.3f (wall clock %.3f, device time %.3f; kernels "
+                     "%.3f / %.3f ms)", ratio, graph.fb_ratio, upper, b_ms, f_ms)
+            graph.fb_ratio = max(1.0, ratio)
     for i in captured.params:
         i.tensor.grad = None
-    graph.fb_ratio = max(1.0, bwd_ms / fwd_ms) if fwd_ms > 0 else 2.0
     log.info("forward: %.4f ms, backward: %.4f ms", fwd_ms / TIME_CHECK_ITER,
              bwd_ms / TIME_CHECK_ITER)
 
