@@ -244,7 +244,8 @@ def run_native(args) -> int:
     dev = state.device
     mp = None if cpu else wl.precision
     extra_opt = dict(wl.option)
-    for k in ("loop_cnt", "loop_batch", "prefetch_fwd", "split_points", "scheduler"):
+    for k in ("loop_cnt", "loop_batch", "prefetch_fwd", "split_points", "scheduler",
+              "schedule_picture"):
         if getattr(args, k, None) is not None:
             extra_opt[k] = getattr(args, k)
     if state.pp_size == 1:
@@ -454,6 +455,8 @@ def main(argv=None) -> int:
     ap.add_argument("--scheduler", type=str, default=None)
     ap.add_argument("--device_bench", type=str, default=None,
                     help="link-model file (measured and written when it does not exist)")
+    ap.add_argument("--schedule_picture", type=str, default=None,
+                    help="write the planned schedule as an SVG chart to FILE")
     ap.add_argument("--data_seed", type=int, default=0,
                     help="offset of the synthetic batch's seed (replica r draws with seed + 1 + r)")
     ap.add_argument("--cpu", action="store_true", help="plumbing check without a GPU")

@@ -113,6 +113,8 @@ _FLAGS: List[_Flag] = [
           help="accepted for compatibility: this runtime posts transfers from the stage "
                "thread itself and has no sender threads to merge"),
     _Flag("no_bench_optimizer", False, "--no_bench_optimizer", dict(action="store_true")),
+    _Flag("schedule_picture", None, "--schedule_picture", dict(type=str),
+          help="write the planned schedule as an SVG chart (one lane per pipeline rank) to FILE"),
     # ---- additions of this framework
     _Flag("dp_mesh", None, "--dp_mesh_opt", dict(type=str),
           help='signed PPxDP mesh "-2,4", or "auto" to let the planner choose'),

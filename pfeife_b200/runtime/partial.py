@@ -290,6 +290,9 @@ class PartialModule(torch.nn.Module):
             points, sched_key = r.ctrl.share_with_replicas(None)
             plan = gen.plan_from(points, sched_key, max_mem)
         self.plan = plan
+        if getattr(opt, "schedule_picture", None) and state.is_main_process:
+            from ..parallel.gantt import save_schedule_svg
+            save_schedule_svg(plan.pipe_graph, plan.sched, opt.schedule_picture, plan.sim)
         part = partition_module(self.comp_graph, plan.split_points, pp)
         self.part = part
         sched_cls = get_scheduler_class(opt.scheduler)

@@ -220,3 +220,32 @@ def test_plan_mesh_profiles_a_model_and_ranks_every_factorisation():
     best = max(choice.table, key=lambda r: (r[4], r[3]))
     assert (choice.pp, choice.dp) == (best[0], best[1])
     assert choice.dp_mesh == (f"-{choice.dp},{choice.pp}" if choice.dp > 1 else f"{choice.pp}")
+
+
+def test_schedule_picture_places_every_item_without_overlap(tmp_path):
+    """The chart's boxes are the schedule's items at their simulated start times: every item
+    appears once, boxes of one rank do not overlap, a backward never starts before its forward
+    has ended, and the SVG and text forms carry all of them."""
+    from pfeife_b200.parallel.gantt import save_schedule_svg, schedule_rows, schedule_table
+    rng = random.Random(5)
+    pg = _random_graph(rng, 4, 2)
+    sched = S.PipeSchedParams(2, 4, 4, 2, 0)
+    rows = schedule_rows(pg, sched)
+    assert len(rows) == 4 * 4 * 2
+    assert len({(x.stage, x.batch, x.is_fwd) for x in rows}) == len(rows)
+    sim = pg.simulate(sched, record=True)
+    for r in range(2):
+        lane = [x for x in rows if x.rank == r]
+        for a, b in zip(lane, lane[1:]):
+            assert a.start + a.dur <= b.start + 1e-9
+    when = {(x.stage, x.batch, x.is_fwd): x for x in rows}
+    for (s, b, f), x in when.items():
+        if not f:
+            fw = when[(s, b, True)]
+            assert fw.start + fw.dur <= x.start + 1e-9
+    # (the makespan also holds the optimizer step that follows a rank's last backward)
+    assert max(x.start + x.dur for x in rows) <= sim.makespan + 1e-9
+    path = save_schedule_svg(pg, sched, str(tmp_path / "sched.svg"))
+    svg = open(path).read()
+    assert svg.startswith("<svg") and svg.count("<title>") == len(rows)
+    assert len(schedule_table(pg, sched).splitlines()) == len(rows) + 1
