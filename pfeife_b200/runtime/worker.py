@@ -276,6 +276,7 @@ class StageWorker:
     # ------------------------------------------------------------------ per-step state
     def _reset_step_state(self) -> None:
         self.sends: List[Handle] = []
+        self.send_of: Dict[int, Handle] = {}       # source address -> its latest send
         self.recv_handles: Dict[MsgKey, Handle] = {}
         self.recv_cursor: Dict[int, int] = {}
         self.local_vals: Dict[MsgKey, torch.Tensor] = {}       # same-rank hand-offs
@@ -328,7 +329,19 @@ class StageWorker:
             t = t.contiguous()
         if t.dtype != msg.meta.dtype:
             t = t.to(msg.meta.dtype)
-        self.sends.append(self.transport.isend(t, self.global_ranks[msg.dst_rank]))
+        h = self.transport.isend(t, self.global_ranks[msg.dst_rank])
+        self.sends.append(h)
+        self.send_of[t.data_ptr()] = h      # see _wait_sends_from
+
+    def _wait_sends_from(self, tensors) -> None:
+        """Before a graph replay overwrites its static buffers: the stream waits for the
+        transfers that still read them (a send is only posted when it is issued; the peer may
+        match it much later)."""
+        for t in tensors:
+            if torch.is_tensor(t):
+                h = self.send_of.pop(t.data_ptr(), None)
+                if h is not None:
+                    h.wait()
 
     def _take(self, msg: _Msg) -> torch.Tensor:
         if msg.src_rank == msg.dst_rank:
@@ -398,6 +411,7 @@ class StageWorker:
                     for dst, src in zip(gs.static_ins, ins):
                         if dst is not src and torch.is_tensor(dst):
                             dst.copy_(src, non_blocking=True)
+                self._wait_sends_from(gs.static_outs)
                 gs.fwd.replay()
                 _lib_add(gs.fwd_kernels)
                 self.recorder.append_fw(stage, start, self.recorder.record_event(self.device))
@@ -614,6 +628,8 @@ class StageWorker:
                         buf.zero_()
                     else:
                         buf.copy_(g.reshape(buf.shape), non_blocking=True)
+                self._wait_sends_from([getattr(t, "grad", None) for t in gs.static_ins
+                                       if torch.is_tensor(t) and t.is_leaf])
                 gs.bwd.replay()
                 _lib_add(gs.bwd_kernels)
         elif tensors:
