@@ -63,7 +63,7 @@ def run(args) -> int:
     import subprocess
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    budget = float(os.environ.get("PFEIFE_REF_TIMEOUT", "780"))
+    time_limit = float(os.environ.get("PFEIFE_REF_TIMEOUT", "780"))
     t_begin = time.time()
     base_port = int(os.environ.get("MASTER_PORT", "24446"))
     forced = os.environ.get("PFEIFE_REF_MESH")
@@ -74,7 +74,7 @@ def run(args) -> int:
     root = os.path.dirname(HERE)
     results = []
     for i, mesh in enumerate(meshes):
-        left = budget - (time.time() - t_begin)
+        left = time_limit - (time.time() - t_begin)
         share = left / (len(meshes) - i)
         if share < 60:
             results.append({"mesh": _mesh_name(mesh), "unavailable": "no time left in the arm"})

@@ -202,3 +202,20 @@ def test_compile_hook_wraps_a_stage_module():
     assert torch.allclose(wrapped(x), mod(x))
     single = WrapperModule(lambda *a: (a[0] * 2,), unwrap_singleton_tuple=True)
     assert torch.equal(single(x), x * 2)
+
+
+def test_optimizer_timing_leaves_the_probing_graph_usable():
+    """The optimizer is timed while the probing forward's autograd graph is still alive (its
+    backward runs afterwards, in the caller): the real parameters must keep their values and
+    their version counters, so the measurement steps stand-ins."""
+    model = DeepMLP(16, 4, 4)
+    cap, args, _ = capture(model, torch.randn(5, 16))
+    opt = PipeOption(device_cnt=2, cpu_test=True, optimizer={"type": "adam", "lr": 0.1})
+    before = [(p.detach().clone(), p._version) for p in model.parameters()]
+    cg, out = gen_local_comp_graph(cap, args, torch.device("cpu"), opt)
+    assert sum(n.optim_time for n in cg.nodes) > 0.0        # the optimizer was measured
+    for p, (val, ver) in zip(model.parameters(), before):
+        assert p._version == ver and torch.equal(p.detach(), val) and p.grad is None
+    first = out[0] if isinstance(out, (tuple, list)) else out
+    first.sum().backward()                                   # the caller's backward still works
+    assert all(p.grad is not None for p in model.parameters())
