@@ -16,6 +16,7 @@ gradient for the weight), which is what the fused data-parallel reduce consumes.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import threading
 from dataclasses import dataclass
@@ -24,6 +25,7 @@ from typing import Dict, Optional, Tuple
 import torch
 import torch.nn.functional as F
 from torch import Tensor
+from torch._subclasses.fake_tensor import FakeTensor
 
 from . import kernels as kx
 
@@ -117,11 +119,32 @@ def _grad_bucket(t: Optional[Tensor]) -> Optional[Tensor]:
     return s.main_grad.view(-1)
 
 
+_trace_tls = threading.local()
+
+
+@contextlib.contextmanager
+def stage_precision(dtype: Optional[torch.dtype]):
+    """Declares the autocast dtype the stages will run in, for the time a graph is traced.
+    Shape-and-dtype inference of a trace runs the ops' meta functions with autocast switched
+    off, so they would report x's dtype where the real op returns the autocast dtype, and a
+    ``t.to(y.dtype)`` in the model would be baked into the graph with the wrong type."""
+    prev = getattr(_trace_tls, "dtype", None)
+    _trace_tls.dtype = dtype
+    try:
+        yield
+    finally:
+        _trace_tls.dtype = prev
+
+
 def compute_dtype(x: Tensor) -> torch.dtype:
-    """dtype GEMM-like ops run in: the autocast dtype when autocast is on, else x's dtype."""
+    """dtype GEMM-like ops run in: the autocast dtype when autocast is on (or, while a graph is
+    traced, the one declared by ``stage_precision``), else x's dtype."""
     dev = "cuda" if x.is_cuda else "cpu"
     if torch.is_autocast_enabled(dev):
         return torch.get_autocast_dtype(dev)
+    hint = getattr(_trace_tls, "dtype", None)
+    if hint is not None and isinstance(x, FakeTensor):
+        return hint
     return x.dtype
 
 

@@ -22,6 +22,7 @@ script (``mp_launch.py`` does this for them).
 from __future__ import annotations
 
 import atexit
+import contextlib
 import copy
 import os
 import queue
@@ -552,7 +553,12 @@ class PartialRunner:
         ones the stages will see.  (The stages enter autocast themselves,
         pfeife/mp/worker.py:677; tracing outside it gives fp32 where they produce 16 bits.)"""
         from ..graph.profiler import gen_amp_context
-        return gen_amp_context(self.state.device, self.option.mixed_precision)
+        from ..ops import functional as Fn
+        stack = contextlib.ExitStack()
+        stack.enter_context(gen_amp_context(self.state.device, self.option.mixed_precision))
+        # meta functions of a trace run with autocast off: tell them the stages' precision
+        stack.enter_context(Fn.stage_precision(self.option.mixed_precision))
+        return stack
 
     # ---- checkpoint
     def gather_params(self, with_optimizer: bool = False):

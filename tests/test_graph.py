@@ -219,3 +219,36 @@ def test_optimizer_timing_leaves_the_probing_graph_usable():
     first = out[0] if isinstance(out, (tuple, list)) else out
     first.sum().backward()                                   # the caller's backward still works
     assert all(p.grad is not None for p in model.parameters())
+
+
+def test_declared_stage_precision_reaches_the_trace():
+    """Meta functions of a trace run with autocast off.  With the stages' precision declared,
+    the linear op reports the 16-bit output it will really produce, and a ``.to(y.dtype)`` of
+    the model is baked into the graph with that type (it was float32 before, and the stages
+    then mixed fp32 and 16-bit tensors)."""
+    from pfeife_b200 import ops
+    from pfeife_b200.ops import functional as Fn
+    w, b = torch.randn(8, 8), torch.zeros(8)
+
+    def f(x):
+        y = ops.linear(x, w, b)
+        return y + torch.ones(8).to(y.dtype)
+
+    def trace(declared):
+        box = {}
+
+        def backend(gm, example_inputs):
+            box["code"] = gm.code
+            return gm.forward
+
+        torch._dynamo.reset()
+        with Fn.stage_precision(declared), torch.autocast("cpu", torch.bfloat16,
+                                                          enabled=declared is not None):
+            out = torch.compile(f, backend=backend)(torch.randn(4, 8))
+        return box["code"], out
+
+    code, out = trace(torch.bfloat16)
+    assert "torch.bfloat16" in code and "torch.float32" not in code
+    assert out.dtype == torch.bfloat16
+    code, out = trace(None)
+    assert "torch.bfloat16" not in code and out.dtype == torch.float32
