@@ -62,7 +62,9 @@ class SegmentExecutor:
         self.frees = _last_uses(self.gm)
         self.nodes = list(self.gm.graph.nodes)
 
-    def run(self, args: Sequence[Any], on_start=None, on_end=None, keep_all: bool = False) -> Any:
+    def run(self, args: Sequence[Any], on_start=None, on_end=None, keep_all: bool = False,
+            on_value=None) -> Any:
+        """``on_value(segment, value)`` sees every value a node produces (for hooks)."""
         env: Dict[str, Any] = {}
         it = iter(args)
         cur_seg = -1
@@ -95,6 +97,8 @@ class SegmentExecutor:
                 for atom in n.target.split("."):
                     obj = getattr(obj, atom)
                 env[n.name] = obj
+            if on_value is not None and n.name in env:
+                on_value(seg, env[n.name])
             if not keep_all:
                 for v in self.frees.get(n.name, ()):
                     if v in env and self.gm.graph is not None:
@@ -157,6 +161,69 @@ def _kernel_busy_ms(ex: "SegmentExecutor", args: Sequence[Any], amp, device
         return (f_us / 1e3, b_us / 1e3) if b_us > 0 else None
     except Exception as exc:
         get_logger().info("no kernel activity records (%s)", type(exc).__name__)
+        return None
+
+
+def segment_backward_times(ex: "SegmentExecutor", args: Sequence[Any], amp, device,
+                           total_ms: float) -> Optional[List[float]]:
+    """Backward time of every segment, from one eager backward: a gradient hook on every value a
+    segment produces stamps the moment that value's gradient is complete; the latest stamp of a
+    segment is when the backward reaches it, and a segment's backward lasts until the backward
+    reaches the segment before it.  Only the proportions are kept: the list is scaled to sum to
+    ``total_ms`` (the backward total the planner already uses), so an eager pass that ran at the
+    host's launch rate still cannot change the predicted step, only how it is split.
+
+    (The reference applies one backward/forward ratio to every segment,
+    pfeife/local/graph_bench.py; attention, GEMM and norm segments differ by a factor of two.)"""
+    is_cuda = device.type == "cuda"
+    n_seg = len(ex.graph.nodes)
+    stamps: Dict[int, list] = {}
+
+    def now():
+        if is_cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+        return time.perf_counter()
+
+    def attach(seg, value):
+        for t in _tensor_leaves(value):
+            if torch.is_tensor(t) and t.requires_grad and t.dtype.is_floating_point:
+                t.register_hook(lambda g, s=seg: stamps.setdefault(s, []).append(now()))
+
+    try:
+        with amp():
+            out = ex.run(args, on_value=attach)
+        loss = _sum_outputs(out)
+        if loss is None:
+            return None
+        if is_cuda:
+            torch.cuda.synchronize(device)
+        begin = now()
+        loss.backward()
+        end = now()
+        if is_cuda:
+            torch.cuda.synchronize(device)
+        at = (lambda x: begin.elapsed_time(x)) if is_cuda else (lambda x: (x - begin) * 1e3)
+        reached = [max((at(x) for x in stamps[k]), default=None) if k in stamps else None
+                   for k in range(n_seg)]
+        # a segment without a differentiable value of its own is reached when the next one is
+        nxt = 0.0
+        for k in range(n_seg - 1, -1, -1):
+            if reached[k] is None:
+                reached[k] = nxt
+            nxt = reached[k]
+        times = []
+        for k in range(n_seg):
+            until = at(end) if k == 0 else reached[k - 1]
+            times.append(max(0.0, until - reached[k]))
+        total = sum(times)
+        if total <= 0.0:
+            return None
+        return [t * total_ms / total for t in times]
+    except Exception as exc:
+        get_logger().info("per-segment backward timing unavailable (%s: %s)",
+                          type(exc).__name__, str(exc).splitlines()[0] if str(exc) else "")
         return None
 
 
@@ -335,6 +402,12 @@ def gen_local_comp_graph(captured: CapturedGraph, args: Sequence[Any], device: t
             log.info("backward / forward: %.3f (wall clock %.3f, device time %.3f; kernels "
                      "%.3f / %.3f ms)", ratio, graph.fb_ratio, upper, b_ms, f_ms)
             graph.fb_ratio = max(1.0, ratio)
+    # per-segment backward times (proportions of one more eager backward, total unchanged)
+    back = segment_backward_times(ex, args, amp, device,
+                                  graph.fb_ratio * sum(n.comp_time for n in graph.nodes))
+    if back is not None:
+        for n, b in zip(graph.nodes, back):
+            n.back_time = max(b, 1e-4)
     for i in captured.params:
         i.tensor.grad = None
     log.info("forward: %.4f ms, backward: %.4f ms", fwd_ms / TIME_CHECK_ITER,

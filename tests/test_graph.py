@@ -252,3 +252,35 @@ def test_declared_stage_precision_reaches_the_trace():
     assert out.dtype == torch.bfloat16
     code, out = trace(None)
     assert "torch.bfloat16" not in code and out.dtype == torch.float32
+
+
+def test_backward_times_are_per_segment_and_keep_the_total():
+    """Every segment gets a backward time of its own (proportions of one eager backward), and
+    the times add up to the backward total the planner used before (ratio x forward total)."""
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(64, 64)
+            self.big = torch.nn.Linear(64, 4096)
+            self.big2 = torch.nn.Linear(4096, 64)
+            self.c = torch.nn.Linear(64, 8)
+
+        def forward(self, x):
+            h = torch.relu(self.a(x))
+            h = torch.relu(self.big2(torch.relu(self.big(h))))
+            return self.c(h)
+
+    torch.manual_seed(0)
+    cap, args, _ = capture(Net(), torch.randn(512, 64))
+    opt = PipeOption(device_cnt=2, no_bench_optimizer=True, cpu_test=True)
+    cg, _ = gen_local_comp_graph(cap, args, torch.device("cpu"), opt)
+    back = [n.back_time for n in cg.nodes]
+    assert all(b is not None and b > 0 for b in back)
+    fwd_total = sum(n.comp_time for n in cg.nodes)
+    assert sum(back) == pytest.approx(cg.fb_ratio * fwd_total, rel=1e-3)
+    # the two wide layers dominate the backward as they dominate the forward
+    wide = sorted(range(len(back)), key=lambda i: -back[i])[:3]
+    heavy_fwd = sorted(range(len(back)), key=lambda i: -cg.nodes[i].comp_time)[:3]
+    assert set(wide) & set(heavy_fwd)
+    ratios = [b / n.comp_time for b, n in zip(back, cg.nodes)]
+    assert max(ratios) > 1.5 * min(ratios)          # not one ratio for all
