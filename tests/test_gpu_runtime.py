@@ -98,3 +98,5 @@ def test_bench_workloads_run_natively(workload):
     assert rec["value"] > 0 and rec["e2e"]["value"] > 0
     assert rec["gpu_launches"] > 0
     assert rec["e2e"]["h2d_bytes_per_step"] > 0
+    assert rec["loss_mean_last_step"] is not None and \
+        rec["loss_mean_last_step"] == rec["loss_mean_last_step"]      # finite, not NaN
