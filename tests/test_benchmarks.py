@@ -66,3 +66,19 @@ def test_a_failed_first_step_ends_the_job():
     assert p.returncode != 0
     assert "no captured graph is eligible for pipelining" in p.stderr + p.stdout
     assert time.time() - t0 < 200
+
+
+def test_reference_arm_sweeps_the_reference_meshes_best_first():
+    """The reference arm tries the reference's own PP x DP layouts for the world size (short
+    pipelines replicated first, one pipeline over everything last) and names them like the
+    native arm names its parallelism."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "reference_arm", os.path.join(root, "baseline", "reference_arm.py"))
+    arm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(arm)
+    assert arm._candidate_meshes(8) == ["-4,2", "-2,4", "8"]
+    assert arm._candidate_meshes(4) == ["-2,2", "4"]
+    assert arm._candidate_meshes(2) == ["2"]
+    assert [arm._mesh_name(m) for m in arm._candidate_meshes(8)] == ["pp2xdp4", "pp4xdp2", "pp8"]
