@@ -262,6 +262,12 @@ class StageWorker:
         self.recv_bufs: Dict[MsgKey, torch.Tensor] = {}
         self.zero_bufs: Dict[MsgKey, torch.Tensor] = {}
         self.slot_of, _ = inflight_slots(self.steps)
+        # the orderings the buffers of this rank rely on (cheap: one pass over the program)
+        from .hazards import program_hazards
+        problems = program_hazards(self.steps, self.slot_of)
+        if problems:
+            raise RuntimeError("step program of pipeline rank %d is unsafe: %s"
+                               % (self.pp_rank, "; ".join(problems[:5])))
         if self.transport is not None:
             g = self.global_ranks
             self.transport.warm_up([(g[a], g[b]) for a, b in self.comm.channels])

@@ -249,3 +249,45 @@ def test_schedule_picture_places_every_item_without_overlap(tmp_path):
     svg = open(path).read()
     assert svg.startswith("<svg") and svg.count("<title>") == len(rows)
     assert len(schedule_table(pg, sched).splitlines()) == len(rows) + 1
+
+
+@pytest.mark.parametrize("name", ["single_comm", "beam", "bfs", "dfs", "pipeless", "noskew"])
+@pytest.mark.parametrize("D,B,N", [(2, 4, 2), (2, 4, 4), (3, 6, 6), (4, 8, 4), (4, 8, 8)])
+def test_step_programs_keep_the_orderings_their_buffers_rely_on(name, D, B, N):
+    """Every scheduler's per-rank programs, replayed on the host: receives precede their
+    consumers, sends follow their producers, two micro-batches share a graph slot only when the
+    first one's backward precedes the second one's forward, and all ranks together terminate
+    under the transports' semantics (also with a skip connection across ranks)."""
+    from pfeife_b200.runtime.hazards import program_hazards, replay_job
+    from pfeife_b200.runtime.worker import inflight_slots
+    params = S.PipeSchedParams(D, B, N, min(B, D) if N > D else B, 0)
+    sched = S.get_scheduler_class(name)(params)
+    stage_rank = {s: s % D for s in range(N)}
+    for r in range(D):
+        steps = sched.steps[r]
+        slots, n_slots = inflight_slots(steps)
+        assert program_hazards(steps, slots) == []
+        assert n_slots <= B
+    edges = [(i, i + 1) for i in range(N - 1)]
+    assert replay_job(sched.steps, stage_rank, edges) == []
+    if N >= 3:
+        assert replay_job(sched.steps, stage_rank, edges + [(0, N - 1)]) == []
+
+
+def test_hazard_checker_reports_broken_programs():
+    from pfeife_b200.runtime.hazards import program_hazards, replay_job
+    St, W = S.Step, S.StepWork
+    ok = [St(W.RECV_ACT, 1, 0), St(W.FORWARD, 1, 0), St(W.RECV_ACT, 1, 1), St(W.FORWARD, 1, 1),
+          St(W.BACKWARD, 1, 0), St(W.SEND_GRAD, 1, 0), St(W.BACKWARD, 1, 1), St(W.SEND_GRAD, 1, 1),
+          St(W.OPTIMIZER_STEP, -1, -1)]
+    assert program_hazards(ok, {(1, 0): 0, (1, 1): 1}) == []
+    # both micro-batches in one slot while both are in flight
+    assert any("slot" in p for p in program_hazards(ok, {(1, 0): 0, (1, 1): 0}))
+    # a forward ahead of its receive, a send ahead of its backward
+    bad = [ok[1], ok[0]] + ok[2:4] + [ok[5], ok[4]] + ok[6:]
+    msgs = program_hazards(bad, {(1, 0): 0, (1, 1): 1})
+    assert any("inputs are not there" in p for p in msgs) and any("nothing to send" in p for p in msgs)
+    # two ranks that each wait for the other's message first
+    r0 = [St(W.RECV_GRAD, 0, 0), St(W.FORWARD, 0, 0), St(W.SEND_ACT, 0, 0)]
+    r1 = [St(W.RECV_ACT, 1, 0), St(W.FORWARD, 1, 0), St(W.BACKWARD, 1, 0), St(W.SEND_GRAD, 1, 0)]
+    assert any("waits for ever" in p for p in replay_job([r0, r1], {0: 0, 1: 1}, [(0, 1)]))
